@@ -1,0 +1,89 @@
+"""ctypes binding of libflyb200.so (the C ABI in include/flyb200.h).
+
+There is no fallback: if the library cannot be loaded every operator of this
+package raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+
+from . import build as _build
+
+OK = 0
+E_BAD_ARG, E_BAD_ALIGN, E_CUDA, E_TIMEOUT, E_UNSUPPORTED, E_SMEM_ALIGN, E_WORKSPACE = range(1, 8)
+
+DT_FP8, DT_INT8, DT_FP16, DT_BF16 = range(4)
+OUT_BF16, OUT_FP16 = range(2)
+EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_SILU, EPI_BIAS_GELU = range(5)
+SRC_ROW_MAJOR, SRC_MFMA_16x16 = range(2)
+
+IN_DTYPES = {"fp8": DT_FP8, "int8": DT_INT8, "fp16": DT_FP16, "bf16": DT_BF16}
+OUT_DTYPES = {"bf16": OUT_BF16, "fp16": OUT_FP16}
+EPILOGUES = {
+    "none": EPI_NONE,
+    "bias": EPI_BIAS,
+    "bias_relu": EPI_BIAS_RELU,
+    "bias_silu": EPI_BIAS_SILU,
+    "bias_gelu": EPI_BIAS_GELU,
+}
+
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+
+# name -> (restype, argtypes): one row per declaration in include/flyb200.h
+SIGNATURES = {
+    "flyb200_gemm_a8w8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "flyb200_gemm_a8w8_acc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "flyb200_shuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
+    "flyb200_unshuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "flyb200_layout_kind": (_i, [_i, _i, _i]),
+    "flyb200_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "flyb200_read_status": (_i, [ctypes.POINTER(_i)]),
+    "flyb200_strerror": (ctypes.c_char_p, [_i]),
+    "flyb200_last_cuda_error": (ctypes.c_char_p, []),
+    "flyb200_version": (_i, []),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+class FlyB200Error(RuntimeError):
+    def __init__(self, code: int, what: str):
+        self.code = code
+        super().__init__(what)
+
+
+def load() -> ctypes.CDLL:
+    """Load (building first if the in-tree library is missing or stale)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = _build.build_library()
+            lib = ctypes.CDLL(path)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+                fn.restype = res
+                fn.argtypes = args
+            _lib = lib
+    return _lib
+
+
+def check(code: int, what: str = "libflyb200") -> None:
+    if code == OK:
+        return
+    lib = load()
+    msg = lib.flyb200_strerror(code).decode()
+    if code == E_CUDA:
+        msg += ": " + lib.flyb200_last_cuda_error().decode()
+    raise FlyB200Error(code, f"{what}: {msg} (code {code})")
+
+
+def read_status() -> int:
+    """Synchronise the current device and return (and clear) its status word."""
+    out = _i(0)
+    check(load().flyb200_read_status(ctypes.byref(out)), "read_status")
+    return out.value

@@ -1,0 +1,442 @@
+// libflyb200: host side of the C ABI declared in include/flyb200.h — argument
+// checks, tensor-map encoding, kernel selection and launch.  No allocation, no
+// synchronisation and no memcpy on the launch path.
+#include "../../include/flyb200.h"
+#include "gemm_kernels.cuh"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+using namespace flyb200;
+
+namespace {
+
+thread_local char g_cuda_err[256] = "";
+
+int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+  return FLYB200_E_CUDA;
+}
+#define CUDA_TRY(expr)                                   \
+  do {                                                   \
+    cudaError_t _e = (expr);                             \
+    if (_e != cudaSuccess) return cuda_fail(_e, #expr);  \
+  } while (0)
+
+// Device status word: kernels record the first failed bounded wait here.
+__device__ int g_status_word = 0;
+
+constexpr int MAX_DEVICES = 64;
+struct DeviceState {
+  std::once_flag once;
+  int sms = 0;
+  int* status = nullptr;
+  cudaError_t err = cudaSuccess;
+};
+DeviceState g_dev[MAX_DEVICES];
+
+int device_state(DeviceState** out) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return FLYB200_E_UNSUPPORTED;
+  DeviceState& st = g_dev[dev];
+  std::call_once(st.once, [&]() {
+    st.err = cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev);
+    if (st.err == cudaSuccess) st.err = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.status), g_status_word);
+  });
+  if (st.err != cudaSuccess) return cuda_fail(st.err, "device setup");
+  *out = &st;
+  return FLYB200_OK;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup, so
+// the library does not link libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D row-major byte/half matrix, 128-byte swizzled boxes.
+int make_map(CUtensorMap* m, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner_elems,
+             uint64_t rows, uint32_t box_inner_elems, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
+    return FLYB200_E_CUDA;
+  }
+  cuuint64_t dims[2] = {inner_elems, rows};
+  cuuint64_t strides[1] = {inner_elems * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {box_inner_elems, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    return FLYB200_E_CUDA;
+  }
+  return FLYB200_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int elem_bytes_of(int in_dtype) { return (in_dtype == FLYB200_DT_FP8 || in_dtype == FLYB200_DT_INT8) ? 1 : 2; }
+
+// One-time (per device) opt-in to large dynamic shared memory for a kernel.
+template <typename KernelT>
+int ensure_smem(KernelT kernel, int bytes, std::atomic<uint64_t>& done) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  const uint64_t bit = 1ull << dev;
+  if (done.load(std::memory_order_acquire) & bit) return FLYB200_OK;
+  CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  done.fetch_or(bit, std::memory_order_release);
+  return FLYB200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// kernel launch helpers
+// ---------------------------------------------------------------------------
+constexpr int ROWS_BN = 256;
+constexpr int ROWS_STAGES = 4;
+constexpr size_t TICKET_BYTES = 16384;  // 4096 channel tiles
+constexpr int MAX_SPLIT_K = 32;
+
+template <int KIND, int OUTMODE>
+int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams& p, int sms, cudaStream_t s) {
+  using L = RowsSmem<ROWS_BN, ROWS_STAGES>;
+  static std::atomic<uint64_t> done{0};
+  auto kernel = gemm_rows_kernel<KIND, ROWS_BN, ROWS_STAGES, OUTMODE>;
+  int rc = ensure_smem(kernel, L::TOTAL, done);
+  if (rc) return rc;
+  const int tiles = ((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * ((p.N + ROWS_BN - 1) / ROWS_BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, NUM_THREADS, L::TOTAL, s>>>(tmA, tmC, p);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+template <int BN>
+struct DecodeStages {
+  static constexpr int value = BN <= 32 ? 8 : (BN <= 128 ? 6 : 4);
+};
+
+template <int KIND, int BN, int OUTMODE>
+int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
+  constexpr int STAGES = DecodeStages<BN>::value;
+  using L = DecodeSmem<BN, STAGES>;
+  static std::atomic<uint64_t> done{0};
+  auto kernel = gemm_decode_kernel<KIND, BN, STAGES, OUTMODE>;
+  int rc = ensure_smem(kernel, L::TOTAL, done);
+  if (rc) return rc;
+  dim3 grid((p.N + BLOCK_ROWS - 1) / BLOCK_ROWS, p.split_k, 1);
+  kernel<<<grid, NUM_THREADS, L::TOTAL, s>>>(tmA, p);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+template <int KIND, int OUTMODE>
+int launch_decode_bn(int bn, const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch_decode<KIND, 16, OUTMODE>(tmA, p, s);
+    case 32: return launch_decode<KIND, 32, OUTMODE>(tmA, p, s);
+    case 64: return launch_decode<KIND, 64, OUTMODE>(tmA, p, s);
+    case 128: return launch_decode<KIND, 128, OUTMODE>(tmA, p, s);
+    case 256: return launch_decode<KIND, 256, OUTMODE>(tmA, p, s);
+  }
+  return FLYB200_E_UNSUPPORTED;
+}
+
+inline int decode_bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
+
+// Split-K factor of the small-M kernel when the caller does not force one:
+// enough CTAs to cover the SMs, at least four k-blocks per CTA.
+int auto_split_k(int N, int K_bytes, int sms) {
+  const int n_tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
+  const int kb = K_bytes / KBLOCK_BYTES;
+  if (n_tiles >= sms || n_tiles > static_cast<int>(TICKET_BYTES / sizeof(int))) return 1;
+  int split = sms / n_tiles;
+  if (split > kb / 4) split = kb / 4;
+  if (split > MAX_SPLIT_K) split = MAX_SPLIT_K;
+  return split < 1 ? 1 : split;
+}
+
+size_t partial_bytes(int split, int N, int bn) {
+  const size_t n_tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
+  return static_cast<size_t>(split) * n_tiles * bn * BLOCK_ROWS * sizeof(uint32_t);
+}
+
+struct Plan {
+  bool decode;
+  int bn;
+  int split_k;
+  int kb_per_split;
+  int group_m;
+};
+
+int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t workspace_bytes, bool have_ws, int sms) {
+  const int want_kernel = (variant_hint >> 8) & 0xF;
+  const int want_split = variant_hint & 0xFF;
+  const int want_group = (variant_hint >> 16) & 0xFF;
+  plan->decode = want_kernel == 1 ? true : want_kernel == 2 ? false : (M <= 256);
+  if (plan->decode && M > 256) return FLYB200_E_UNSUPPORTED;
+  plan->bn = plan->decode ? decode_bn_for(M) : ROWS_BN;
+  plan->group_m = want_group > 0 ? want_group : 16;
+  plan->split_k = 1;
+  const int kb = K_bytes / KBLOCK_BYTES;
+  plan->kb_per_split = kb;
+  if (plan->decode) {
+    int split = want_split > 0 ? want_split : auto_split_k(N, K_bytes, sms);
+    if (split > kb) split = kb;
+    if (split > 1) {
+      const bool fits = have_ws && workspace_bytes >= TICKET_BYTES + partial_bytes(split, N, plan->bn) &&
+                        (N + BLOCK_ROWS - 1) / BLOCK_ROWS <= static_cast<int>(TICKET_BYTES / sizeof(int));
+      if (!fits) {
+        if (want_split > 0) return FLYB200_E_WORKSPACE;  // an explicit request is not silently changed
+        while (split > 1 && !(have_ws && workspace_bytes >= TICKET_BYTES + partial_bytes(split, N, plan->bn))) --split;
+      }
+    }
+    plan->kb_per_split = (kb + split - 1) / split;
+    plan->split_k = (kb + plan->kb_per_split - 1) / plan->kb_per_split;
+  }
+  return FLYB200_OK;
+}
+
+template <int KIND, int OUTMODE>
+int run_kind(const Plan& plan, const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams& p, int sms,
+             cudaStream_t s) {
+  if (plan.decode) return launch_decode_bn<KIND, OUTMODE>(plan.bn, tmA, p, s);
+  return launch_rows<KIND, OUTMODE>(tmA, tmC, p, sms, s);
+}
+
+int gemm_common(void* c, const void* a, const void* w, const float* sa, const float* sb, const void* bias, int M,
+                int N, int K, int in_dtype, int outmode, int epilogue, int variant_hint, void* workspace,
+                size_t workspace_bytes, void* stream) {
+  if (!c || !a || !w || M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (in_dtype < FLYB200_DT_FP8 || in_dtype > FLYB200_DT_BF16) return FLYB200_E_BAD_ARG;
+  if (epilogue < FLYB200_EPI_NONE || epilogue > FLYB200_EPI_BIAS_GELU) return FLYB200_E_BAD_ARG;
+  if (epilogue != FLYB200_EPI_NONE && !bias) return FLYB200_E_BAD_ARG;
+  const int eb = elem_bytes_of(in_dtype);
+  if (eb == 1 && outmode != OUT_RAW32 && ((sa == nullptr) != (sb == nullptr))) return FLYB200_E_BAD_ARG;
+  if (!flyb200_layout_kind(N, K, eb)) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(c) || !aligned16(a) || !aligned16(w)) return FLYB200_E_BAD_ALIGN;
+  if (workspace && !aligned16(workspace)) return FLYB200_E_BAD_ALIGN;
+  if (M == 0) return FLYB200_OK;
+  if (in_dtype == FLYB200_DT_FP16 || in_dtype == FLYB200_DT_BF16) {
+    if (outmode == OUT_RAW32) return FLYB200_E_UNSUPPORTED;
+  }
+
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc) return rc;
+  const int K_bytes = K * eb;
+
+  Plan plan;
+  rc = make_plan(&plan, M, N, K_bytes, variant_hint, workspace_bytes, workspace != nullptr, st->sms);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.w = static_cast<const uint8_t*>(w);
+  p.sa = sa;
+  p.sb = sb;
+  p.bias = bias;
+  p.c = c;
+  p.M = M;
+  p.N = N;
+  p.K_bytes = K_bytes;
+  p.epilogue = epilogue;
+  p.group_m = plan.group_m;
+  p.split_k = plan.split_k;
+  p.kb_per_split = plan.kb_per_split;
+  p.ws_tickets = static_cast<int*>(workspace);
+  p.ws_partials = workspace ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + TICKET_BYTES) : nullptr;
+  p.status = st->status;
+
+  CUtensorMap tmA, tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  rc = make_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, static_cast<uint64_t>(K_bytes), static_cast<uint64_t>(M),
+                KBLOCK_BYTES, plan.decode ? plan.bn : BLOCK_ROWS);
+  if (rc) return rc;
+  if (!plan.decode && outmode != OUT_RAW32) {
+    rc = make_map(&tmC, outmode == OUT_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c,
+                  static_cast<uint64_t>(N), static_cast<uint64_t>(M), 64, 32);
+    if (rc) return rc;
+  }
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (in_dtype) {
+    case FLYB200_DT_FP8:
+      if (outmode == OUT_BF16) return run_kind<KIND_F8, OUT_BF16>(plan, tmA, tmC, p, st->sms, s);
+      if (outmode == OUT_FP16) return run_kind<KIND_F8, OUT_FP16>(plan, tmA, tmC, p, st->sms, s);
+      return run_kind<KIND_F8, OUT_RAW32>(plan, tmA, tmC, p, st->sms, s);
+    case FLYB200_DT_INT8:
+      if (outmode == OUT_BF16) return run_kind<KIND_I8, OUT_BF16>(plan, tmA, tmC, p, st->sms, s);
+      if (outmode == OUT_FP16) return run_kind<KIND_I8, OUT_FP16>(plan, tmA, tmC, p, st->sms, s);
+      return run_kind<KIND_I8, OUT_RAW32>(plan, tmA, tmC, p, st->sms, s);
+    case FLYB200_DT_FP16:
+      if (outmode == OUT_BF16) return run_kind<KIND_F16, OUT_BF16>(plan, tmA, tmC, p, st->sms, s);
+      return run_kind<KIND_F16, OUT_FP16>(plan, tmA, tmC, p, st->sms, s);
+    case FLYB200_DT_BF16:
+      if (outmode == OUT_BF16) return run_kind<KIND_BF16, OUT_BF16>(plan, tmA, tmC, p, st->sms, s);
+      return run_kind<KIND_BF16, OUT_FP16>(plan, tmA, tmC, p, st->sms, s);
+  }
+  return FLYB200_E_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------
+// weight preshuffle: a pure byte permutation in 16-byte chunks
+// ---------------------------------------------------------------------------
+// chunk (row n, k-block blk, chunk c of 8) of the row-major matrix
+//   row-major source offset : n*Kb + blk*128 + c*16
+//   MFMA 16x16 source offset: ((n/16)*(Kb/16) + blk*8 + c)*256 + (n%16)*16
+//   B200 image offset       : ((blk*N + n)*8 + (c ^ (n&7)))*16
+template <int SRC_LAYOUT, bool INVERSE>
+__global__ void shuffle_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int N, int Kb) {
+  const size_t total = static_cast<size_t>(N) * (Kb / 16);
+  for (size_t g = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; g < total;
+       g += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(g & 7);
+    const size_t rest = g >> 3;
+    const int n = static_cast<int>(rest % N);
+    const size_t blk = rest / N;
+    const size_t img = (blk * N + n) * 8 + (c ^ (n & 7));
+    size_t plain;
+    if (SRC_LAYOUT == FLYB200_SRC_ROW_MAJOR) {
+      plain = (static_cast<size_t>(n) * Kb + blk * 128) / 16 + c;
+    } else {
+      plain = ((static_cast<size_t>(n >> 4) * (Kb / 16) + blk * 8 + c) * 256 + (n & 15) * 16) / 16;
+    }
+    if (INVERSE) {
+      dst[plain] = src[img];
+    } else {
+      dst[img] = src[plain];
+    }
+  }
+}
+
+template <int SRC_LAYOUT, bool INVERSE>
+int launch_shuffle(void* dst, const void* src, int N, int Kb, cudaStream_t s) {
+  const size_t total = static_cast<size_t>(N) * (Kb / 16);
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  shuffle_kernel<SRC_LAYOUT, INVERSE>
+      <<<static_cast<unsigned>(blocks), threads, 0, s>>>(static_cast<uint4*>(dst), static_cast<const uint4*>(src), N, Kb);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+bool ranges_overlap(const void* a, const void* b, size_t bytes) {
+  const uintptr_t x = reinterpret_cast<uintptr_t>(a), y = reinterpret_cast<uintptr_t>(b);
+  return x < y + bytes && y < x + bytes;
+}
+
+}  // namespace
+
+extern "C" {
+
+int flyb200_gemm_a8w8(void* c, const void* a, const void* w_shuf, const float* scale_a, const float* scale_b,
+                      const void* bias, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
+                      int variant_hint, void* workspace, size_t workspace_bytes, void* stream) {
+  if (out_dtype != FLYB200_OUT_BF16 && out_dtype != FLYB200_OUT_FP16) return FLYB200_E_BAD_ARG;
+  const int eb = elem_bytes_of(in_dtype);
+  if (eb == 1 && (!scale_a || !scale_b)) return FLYB200_E_BAD_ARG;
+  if (eb == 2 && (scale_a || scale_b)) return FLYB200_E_BAD_ARG;
+  return gemm_common(c, a, w_shuf, scale_a, scale_b, bias, M, N, K, in_dtype,
+                     out_dtype == FLYB200_OUT_FP16 ? OUT_FP16 : OUT_BF16, epilogue, variant_hint, workspace,
+                     workspace_bytes, stream);
+}
+
+int flyb200_gemm_a8w8_acc(void* acc, const void* a, const void* w_shuf, int M, int N, int K, int in_dtype,
+                          int variant_hint, void* workspace, size_t workspace_bytes, void* stream) {
+  if (in_dtype != FLYB200_DT_FP8 && in_dtype != FLYB200_DT_INT8) return FLYB200_E_UNSUPPORTED;
+  return gemm_common(acc, a, w_shuf, nullptr, nullptr, nullptr, M, N, K, in_dtype, OUT_RAW32, FLYB200_EPI_NONE,
+                     variant_hint, workspace, workspace_bytes, stream);
+}
+
+int flyb200_shuffle_weight(void* dst, const void* src, int N, int K, int elem_bytes, int src_layout, void* stream) {
+  if (!dst || !src || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (!flyb200_layout_kind(N, K, elem_bytes)) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(dst) || !aligned16(src)) return FLYB200_E_BAD_ALIGN;
+  const size_t bytes = static_cast<size_t>(N) * K * elem_bytes;
+  if (ranges_overlap(dst, src, bytes)) return FLYB200_E_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (src_layout == FLYB200_SRC_ROW_MAJOR) return launch_shuffle<FLYB200_SRC_ROW_MAJOR, false>(dst, src, N, K * elem_bytes, s);
+  if (src_layout == FLYB200_SRC_MFMA_16x16) return launch_shuffle<FLYB200_SRC_MFMA_16x16, false>(dst, src, N, K * elem_bytes, s);
+  return FLYB200_E_BAD_ARG;
+}
+
+int flyb200_unshuffle_weight(void* dst, const void* src, int N, int K, int elem_bytes, void* stream) {
+  if (!dst || !src || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (!flyb200_layout_kind(N, K, elem_bytes)) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(dst) || !aligned16(src)) return FLYB200_E_BAD_ALIGN;
+  const size_t bytes = static_cast<size_t>(N) * K * elem_bytes;
+  if (ranges_overlap(dst, src, bytes)) return FLYB200_E_BAD_ARG;
+  return launch_shuffle<FLYB200_SRC_ROW_MAJOR, true>(dst, src, N, K * elem_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int flyb200_layout_kind(int N, int K, int elem_bytes) {
+  if (elem_bytes != 1 && elem_bytes != 2) return 0;
+  if (N <= 0 || K <= 0) return 0;
+  if (N % 16 != 0) return 0;
+  const long long kb = static_cast<long long>(K) * elem_bytes;
+  if (kb % 128 != 0) return 0;
+  if (kb > 0x7fffffffLL) return 0;
+  return 1;
+}
+
+size_t flyb200_workspace_bytes(int M, int N, int K, int in_dtype) {
+  if (M <= 0 || M > 256 || N <= 0 || K <= 0) return 0;
+  const int eb = elem_bytes_of(in_dtype);
+  if (!flyb200_layout_kind(N, K, eb)) return 0;
+  DeviceState* st = nullptr;
+  if (device_state(&st)) return 0;
+  const int split = auto_split_k(N, K * eb, st->sms);
+  if (split <= 1) return 0;
+  return TICKET_BYTES + partial_bytes(split, N, decode_bn_for(M));
+}
+
+int flyb200_read_status(int* out_status) {
+  if (!out_status) return FLYB200_E_BAD_ARG;
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc) return rc;
+  CUDA_TRY(cudaDeviceSynchronize());
+  int v = 0;
+  CUDA_TRY(cudaMemcpy(&v, st->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0) {
+    int zero = 0;
+    CUDA_TRY(cudaMemcpy(st->status, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  }
+  *out_status = v;
+  return FLYB200_OK;
+}
+
+const char* flyb200_strerror(int code) {
+  switch (code) {
+    case FLYB200_OK: return "ok";
+    case FLYB200_E_BAD_ARG: return "bad argument";
+    case FLYB200_E_BAD_ALIGN: return "pointer not 16-byte aligned";
+    case FLYB200_E_CUDA: return "CUDA call failed";
+    case FLYB200_E_TIMEOUT: return "bounded device-side wait expired";
+    case FLYB200_E_UNSUPPORTED: return "unsupported shape or dtype (need N % 16 == 0 and K*elem_bytes % 128 == 0)";
+    case FLYB200_E_SMEM_ALIGN: return "shared memory base not 1024-byte aligned";
+    case FLYB200_E_WORKSPACE: return "workspace missing or too small for the requested split-K";
+  }
+  return "unknown error";
+}
+
+const char* flyb200_last_cuda_error(void) { return g_cuda_err; }
+int flyb200_version(void) { return 1; }
+
+}  // extern "C"

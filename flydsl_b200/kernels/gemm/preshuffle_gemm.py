@@ -1,0 +1,197 @@
+"""``compile_preshuffle_gemm``: the operator surface of the reference's
+``kernels/gemm/preshuffle_gemm.py`` (:108-124 builder, :717-806 launcher) bound
+to the B200 kernels of libflyb200.
+
+    launch = compile_preshuffle_gemm(N=N, K=K, tile_m=.., tile_n=.., tile_k=.., in_dtype="fp8")
+    launch(c, a, b_shuffled, scale_a, scale_b, bias, M, N, stream)   # -> None, writes c
+
+The builder specialises on (N, K, dtypes, epilogue) and validates its
+arguments exactly where the reference raises ``ValueError``.  ``tile_*`` and
+the AMD scheduling knobs are accepted and validated but are hints only: the
+library picks the kernel variant per call from M (weight-stationary split-K
+kernel for M <= 256, persistent 128x256 tile kernel above), so one launcher
+serves every M without recompiling, as the reference's runtime ``M`` does.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ... import _lib
+
+_IN_DTYPES = ("fp8", "int8", "fp16", "bf16")
+_EPILOGUES = ("none", "bias", "bias_relu", "bias_silu", "bias_gelu")
+_TORCH_OUT = {"bf16": torch.bfloat16, "fp16": torch.float16}
+
+# scratch for split-K partial sums, one per (device, stream); its ticket area
+# must start zeroed and is left zeroed by every completed launch
+_workspaces: dict = {}
+
+
+def _stream_handle(stream) -> int:
+    """torch.cuda.Stream, a raw cudaStream_t integer, or None (default stream):
+    the three forms the reference launcher takes (python/flydsl/expr/typing.py:1254-1285)."""
+    if stream is None:
+        return 0
+    if isinstance(stream, int):
+        return stream
+    handle = getattr(stream, "cuda_stream", None)
+    if handle is None:
+        raise TypeError(f"stream must be a torch.cuda.Stream, an int or None, got {type(stream).__name__}")
+    return int(handle)
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int):
+    if nbytes == 0:
+        return 0, 0
+    key = (device.index, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws.data_ptr(), ws.numel()
+
+
+class PreshuffleGemm:
+    """The callable returned by :func:`compile_preshuffle_gemm`."""
+
+    def __init__(self, N, K, in_dtype, out_dtype, epilogue, tile, variant_hint=0):
+        self.N, self.K = int(N), int(K)
+        self.in_dtype, self.out_dtype, self.epilogue = in_dtype, out_dtype, epilogue
+        self.tile = tile
+        self.variant_hint = int(variant_hint)
+        self._dt = _lib.IN_DTYPES[in_dtype]
+        self._out = _lib.OUT_DTYPES[out_dtype]
+        self._epi = _lib.EPILOGUES[epilogue]
+        self._is_8bit = in_dtype in ("fp8", "int8")
+        self._elem_bytes = 1 if self._is_8bit else 2
+        self._ws_bytes: dict = {}
+
+    def _check_tensors(self, c, a, b, sa, sb, bias, M):
+        N, K = self.N, self.K
+        for name, t in (("c", c), ("a", a), ("b", b)):
+            if not isinstance(t, torch.Tensor) or not t.is_cuda:
+                raise ValueError(f"{name} must be a CUDA tensor")
+            if not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+        if c.dtype != _TORCH_OUT[self.out_dtype]:
+            raise ValueError(f"c must be {self.out_dtype}, got {c.dtype}")
+        if a.element_size() != self._elem_bytes or b.element_size() != self._elem_bytes:
+            raise ValueError(f"a and b must hold {self._elem_bytes}-byte elements for in_dtype={self.in_dtype!r}")
+        if c.numel() < M * N or a.numel() < M * K or b.numel() != N * K:
+            raise ValueError(
+                f"buffer sizes do not match M={M}, N={N}, K={K}: c {c.numel()}, a {a.numel()}, b {b.numel()}"
+            )
+        if self._is_8bit:
+            if sa is None or sb is None or sa.numel() < M or sb.numel() < N:
+                raise ValueError("scale_a [M] and scale_b [N] (fp32) are required for fp8/int8 inputs")
+            if sa.dtype != torch.float32 or sb.dtype != torch.float32:
+                raise ValueError("scales must be float32")
+        if self.epilogue != "none":
+            if bias is None or bias.numel() < N or bias.dtype != c.dtype:
+                raise ValueError(f"epilogue={self.epilogue!r} needs a bias [N] in the output dtype")
+        if a.device != c.device or b.device != c.device:
+            raise ValueError("all tensors must live on the same device")
+
+    def __call__(self, arg_c, arg_a, arg_b, arg_scale_a, arg_scale_b, arg_bias, i32_m, i32_n, stream=None):
+        M, n_rt = int(i32_m), int(i32_n)
+        if n_rt != self.N:
+            raise ValueError(f"N passed at call time ({n_rt}) differs from the N the launcher was built for ({self.N})")
+        if M < 0:
+            raise ValueError("M must be non-negative")
+        self._check_tensors(arg_c, arg_a, arg_b, arg_scale_a, arg_scale_b, arg_bias, M)
+        if M == 0:
+            return None
+        lib = _lib.load()
+        dev = arg_c.device
+        s = _stream_handle(stream)
+        use_scales = self._is_8bit
+        sa = arg_scale_a.data_ptr() if use_scales else None
+        sb = arg_scale_b.data_ptr() if use_scales else None
+        bias = arg_bias.data_ptr() if self.epilogue != "none" else None
+
+        def run():
+            nbytes = self._ws_bytes.get((dev.index, M))
+            if nbytes is None:
+                nbytes = int(lib.flyb200_workspace_bytes(M, self.N, self.K, self._dt))
+                self._ws_bytes[(dev.index, M)] = nbytes
+            ws_ptr, ws_len = _workspace(dev, s, nbytes)
+            rc = lib.flyb200_gemm_a8w8(
+                arg_c.data_ptr(), arg_a.data_ptr(), arg_b.data_ptr(), sa, sb, bias,
+                M, self.N, self.K, self._dt, self._out, self._epi, self.variant_hint,
+                ws_ptr or None, ws_len, s or None,
+            )  # fmt: skip
+            _lib.check(rc, "preshuffle_gemm")
+
+        if torch.cuda.current_device() != dev.index:
+            with torch.cuda.device(dev):
+                run()
+        else:
+            run()
+        return None
+
+
+def compile_preshuffle_gemm(
+    *,
+    N: int,
+    K: int,
+    tile_m: int,
+    tile_n: int,
+    tile_k: int,
+    in_dtype: str = "fp8",
+    out_dtype: str = "bf16",
+    epilogue: str = "none",
+    waves_per_eu: Optional[int] = None,
+    enable_scheduler: bool = True,
+    use_async_copy: bool = False,
+    xcd_swizzle: int = 0,
+    lds_stage: int = 2,
+    preload: Optional[tuple] = None,
+    variant_hint: int = 0,
+):
+    """Build the GEMM launcher ``fn(C, A, B, scale_a, scale_b, bias, M, N, stream)``.
+
+    A is [M, K] (fp8 e4m3fn / int8 / fp16 / bf16; 8-bit tensors may be passed
+    viewed as int8), B the weights [N, K] preshuffled by ``shuffle_weight``,
+    scale_a [M] / scale_b [N] fp32 (empty tensors for fp16/bf16), bias [N] in
+    the output dtype (ignored when ``epilogue == "none"``), C [>=M, N] bf16/fp16
+    written in place.  Raises ``ValueError`` for the configurations the
+    reference rejects (kernels/gemm/preshuffle_gemm.py:129-136,188-196,200-203)
+    and for shapes the B200 weight image cannot hold.  ``waves_per_eu``,
+    ``enable_scheduler``, ``use_async_copy``, ``xcd_swizzle``, ``lds_stage`` and
+    ``preload`` steer AMD code generation in the reference; here they are
+    validated and otherwise ignored.  ``variant_hint`` (not in the reference)
+    forwards a tuning override to the library; 0 = automatic.
+    """
+    if in_dtype not in _IN_DTYPES:
+        raise ValueError(f"in_dtype must be fp8/int8/fp16/bf16, got {in_dtype!r}")
+    if tile_k <= 0 or K % tile_k != 0:
+        raise ValueError(f"tile_k must be a positive divisor of K; got tile_k={tile_k}, K={K}")
+    if epilogue not in _EPILOGUES:
+        raise ValueError(f"epilogue must be none/bias/bias_relu/bias_silu/bias_gelu, got {epilogue!r}")
+    if lds_stage not in (1, 2):
+        raise ValueError(f"lds_stage must be 1 or 2, got {lds_stage}")
+    if out_dtype not in _TORCH_OUT:
+        raise ValueError(f"out_dtype must be bf16 or fp16, got {out_dtype!r}")
+    elem_bytes = 1 if in_dtype in ("fp8", "int8") else 2
+    # The reference copies the A tile with 256 threads x 16 bytes and rejects
+    # tiles that leave a partial copy; kept so that configuration files are
+    # validated identically on both implementations.
+    granule = 256 * 16
+    a_tile_bytes = tile_m * tile_k * elem_bytes
+    if a_tile_bytes % granule != 0:
+        raise ValueError(
+            f"tile_m * tile_k * elem_bytes must be a multiple of {granule}; got tile_m={tile_m}, "
+            f"tile_k={tile_k}, elem_bytes={elem_bytes} -> {a_tile_bytes} bytes"
+        )
+    if preload is not None:
+        if len(preload) != 2 or any(not isinstance(v, int) or v < 0 for v in preload):
+            raise ValueError(f"preload must be a pair of non-negative ints, got {preload!r}")
+    if N <= 0 or N % 16 != 0 or (K * elem_bytes) % 128 != 0:
+        raise ValueError(
+            f"the B200 weight image needs N % 16 == 0 and K*elem_bytes % 128 == 0; got N={N}, K={K}, "
+            f"elem_bytes={elem_bytes}"
+        )
+    return PreshuffleGemm(N, K, in_dtype, out_dtype, epilogue, (tile_m, tile_n, tile_k), variant_hint)

@@ -1,0 +1,119 @@
+/* C ABI of libflyb200: the B200 (sm_100a) implementation of the quantised
+ * A8W8 "preshuffle" GEMM operator of ROCm/FlyDSL.
+ *
+ * Every entry point takes plain pointers and sizes, launches asynchronously on
+ * the given CUDA stream (a cudaStream_t passed as void*; NULL = default stream),
+ * allocates nothing and never synchronises, so calls can be captured into a CUDA
+ * graph.  All pointers are device pointers on the current device unless stated
+ * otherwise.  Return value: 0 on success, else one of the FLYB200_E_* codes
+ * (flyb200_strerror() gives text).  Reference citations below are paths inside
+ * the FlyDSL project.
+ */
+#ifndef FLYB200_H_
+#define FLYB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define FLYB200_OK 0
+#define FLYB200_E_BAD_ARG 1     /* inconsistent sizes, null pointers, unknown enum */
+#define FLYB200_E_BAD_ALIGN 2   /* a pointer is not 16-byte aligned */
+#define FLYB200_E_CUDA 3        /* a CUDA runtime/driver call failed (see flyb200_last_cuda_error) */
+#define FLYB200_E_TIMEOUT 4     /* a bounded device-side wait expired (read via flyb200_read_status) */
+#define FLYB200_E_UNSUPPORTED 5 /* shape or dtype outside what the kernels cover */
+#define FLYB200_E_SMEM_ALIGN 6  /* device reported misaligned shared memory (read via flyb200_read_status) */
+#define FLYB200_E_WORKSPACE 7   /* workspace missing or too small for the requested split */
+
+/* in_dtype: element type of A and of the preshuffled weights
+ * (compile_preshuffle_gemm(in_dtype=...), kernels/gemm/preshuffle_gemm.py:117,129-130) */
+#define FLYB200_DT_FP8 0  /* float8 e4m3fn */
+#define FLYB200_DT_INT8 1
+#define FLYB200_DT_FP16 2
+#define FLYB200_DT_BF16 3
+
+/* out_dtype (kernels/gemm/preshuffle_gemm.py:118,168) */
+#define FLYB200_OUT_BF16 0
+#define FLYB200_OUT_FP16 1
+
+/* epilogue (kernels/gemm/preshuffle_gemm.py:119,133-134,672-692) */
+#define FLYB200_EPI_NONE 0
+#define FLYB200_EPI_BIAS 1
+#define FLYB200_EPI_BIAS_RELU 2
+#define FLYB200_EPI_BIAS_SILU 3
+#define FLYB200_EPI_BIAS_GELU 4
+
+/* source layouts accepted by flyb200_shuffle_weight */
+#define FLYB200_SRC_ROW_MAJOR 0 /* plain [N, K] */
+#define FLYB200_SRC_MFMA_16x16 1 /* already permuted by the reference's shuffle_weight(layout=(16,16)) */
+
+/* variant_hint: 0 = choose automatically.  Otherwise a bit field used for
+ * tuning sweeps: bits 0-7 split-K factor (decode kernel), bits 8-11 kernel
+ * (1 = small-M weight-stationary kernel, 2 = large-M persistent kernel),
+ * bits 16-23 rasterisation group (row tiles per group, large-M kernel). */
+
+/* The GEMM: c[M,N] = epilogue((a[M,K] . w[N,K]^T) * scale_a[m] * scale_b[n]).
+ * Replaces the launcher returned by compile_preshuffle_gemm and the kernel
+ * behind it (kernels/gemm/preshuffle_gemm.py:717-806 launch_gemm,
+ * :220-714 kernel_gemm; call convention pinned by
+ * tests/kernels/test_preshuffle_gemm.py:240-256).
+ *   c        [>=M, N] row-major, out_dtype; rows >= M are never written
+ *   a        [M, K] row-major, in_dtype
+ *   w_shuf   weights [N, K] in the layout written by flyb200_shuffle_weight
+ *   scale_a  [M] fp32 per-token scale, scale_b [N] fp32 per-channel scale; both
+ *            NULL for FP16/BF16 inputs (no scaling)
+ *   bias     [N] in out_dtype; NULL when epilogue == FLYB200_EPI_NONE
+ *   workspace/workspace_bytes  scratch for split-K partial sums, sized by
+ *            flyb200_workspace_bytes(); its first 16 KiB must be zero before the
+ *            first use and are left zero by every completed call; may be NULL
+ *            (then no split-K is used).  Two calls that overlap on the GPU must
+ *            not share a workspace.
+ * Requirements: N % 16 == 0, K * elem_bytes % 128 == 0, pointers 16-byte aligned. */
+int flyb200_gemm_a8w8(void* c, const void* a, const void* w_shuf, const float* scale_a, const float* scale_b,
+                      const void* bias, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
+                      int variant_hint, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Raw 32-bit accumulators acc[M,N] (int32 for INT8, fp32 bit patterns for FP8)
+ * before any scaling: what the reference holds in its MFMA accumulators at
+ * kernels/gemm/preshuffle_gemm.py:538,699-702.  Used to prove the INT8 path
+ * bit-exact.  Same kernels, same dispatch as flyb200_gemm_a8w8. */
+int flyb200_gemm_a8w8_acc(void* acc, const void* a, const void* w_shuf, int M, int N, int K, int in_dtype,
+                          int variant_hint, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Weight preshuffle: dst = B200 image of the [N, K] matrix src.  Replaces
+ * shuffle_weight (tests/utils.py:76-96) and the layout it encodes
+ * (kernels/gemm/preshuffle_gemm.py:765-780).  dst and src must not overlap;
+ * both hold N*K*elem_bytes bytes.  Image: [K*elem_bytes/128][N][128 bytes] with
+ * the 16-byte chunks of each row XOR-ed by (row % 8). */
+int flyb200_shuffle_weight(void* dst, const void* src, int N, int K, int elem_bytes, int src_layout, void* stream);
+
+/* Inverse of flyb200_shuffle_weight: row-major [N, K] from the B200 image. */
+int flyb200_unshuffle_weight(void* dst, const void* src, int N, int K, int elem_bytes, void* stream);
+
+/* 1 when (N, K, elem_bytes) can be preshuffled into the B200 image, else 0.
+ * A pure function of its arguments: the helper and the GEMM evaluate the same
+ * predicate because the `is_shuffled` attribute does not survive the flat views
+ * the call convention uses (tests/kernels/test_preshuffle_gemm.py:234-245). */
+int flyb200_layout_kind(int N, int K, int elem_bytes);
+
+/* Bytes of workspace that flyb200_gemm_a8w8 can make use of for this shape on
+ * the current device (0 when the shape never uses split-K). */
+size_t flyb200_workspace_bytes(int M, int N, int K, int in_dtype);
+
+/* Device-side status word of the current device (0 = no failure since the last
+ * read).  Synchronises the device; not for the launch path.  The reference only
+ * prints runtime errors (lib/Runtime/ROCm/FlyRocmRuntimeWrappers.cpp:23-31). */
+int flyb200_read_status(int* out_status);
+
+const char* flyb200_strerror(int code);
+const char* flyb200_last_cuda_error(void);
+int flyb200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLYB200_H_ */
