@@ -1,0 +1,499 @@
+#!/usr/bin/env python3
+"""Benchmark of the A8W8 preshuffle GEMM on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c5|c3|...]
+
+Prints ONE JSON line.  A "step" is one pass of the hot path over one batch of
+synthetic, seeded input.  Default workload: the column-parallel FP8 GEMM
+M=16384, N=57344, K=8192 with N split over the GPUs (N/world output channels
+per GPU, strong scaling, no collective on the data path); at one GPU the
+whole problem runs on that GPU.  The metric is aggregate TFLOP/s
+(2*M*N*K per step / max-over-ranks device time).
+
+`value`     device-timed, operands resident in HBM.
+`e2e`       the same step through the Python operator with HOST buffers: the
+            step's activations and token scales go pinned-host -> device and
+            the output shard comes back device -> pinned-host inside the timed
+            region (weights are model state: preshuffled and resident).
+`roofline`  the GEMM kernel's own launch time from CUDA events.
+`cpu_baseline` / `--impl reference`  the reference's torch dequantise-and-matmul
+            check on the host cores, on a bounded sample of the same workload.
+`extras`    the single-GPU decode / prefill configurations (HBM- or
+            tensor-bound), timed after the main region (not part of `value`).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FP8 = torch.float8_e4m3fn
+NOMINAL_FP8_TFLOPS = 4500.0  # dense, datasheet
+WORKLOADS = {
+    # name: (M, N, K, in_dtype, weight_scale, seed)
+    "c5": (16384, 57344, 8192, "fp8", 1.0, 1005),
+    "c3": (8192, 28672, 8192, "fp8", 0.02, 1003),
+    "c2": (32, 8192, 8192, "int8", 1.0, 1002),
+    "c1": (128, 4096, 4096, "fp8", 1.0, 1001),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def gemm_bytes(m, n, k):
+    return m * k + n * k + 2 * m * n + 4 * (m + n)
+
+
+# ---------------------------------------------------------------------------
+# clocks (read-only NVML sampling during the timed region)
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x8: "hw_slowdown",
+        0x40: "hw_thermal_slowdown",
+        0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, device_index: int, period_s: float = 0.02):
+        self.samples, self.reasons, self.power = [], set(), []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self.h = None
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # NVML missing: report no clocks rather than fail the run
+            self.err = repr(e)
+            self.h = None
+        self.period = period_s
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {
+            "sm_mhz": statistics.median(self.samples),
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+            "power_w_max": max(self.power) if self.power else None,
+        }
+
+
+# ---------------------------------------------------------------------------
+# the reference's CPU path (torch dequantise-and-matmul) on a bounded sample
+# ---------------------------------------------------------------------------
+def cpu_reference_rate(m, n, k, in_dtype, seconds_budget, steps=1, warmup=0):
+    """Time oracle.run_torch on a [ms, k] x [ns, k] sample of the workload on all
+    host threads.  Returns (TFLOP/s, sample description, seconds per step, threads)."""
+    from oracle import a8w8_oracle as oracle
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    threads = torch.get_num_threads()
+    # calibrate on a small probe, then size the sample for the time budget
+    pm, pn = min(m, 256), min(n, 2048)
+    a_q, b_q, sa, sb = oracle.make_inputs(pm, pn, k, in_dtype, seed=1)
+    oracle.run_torch(a_q, b_q, sa, sb)
+    t0 = time.perf_counter()
+    oracle.run_torch(a_q, b_q, sa, sb)
+    probe = time.perf_counter() - t0
+    rate = 2.0 * pm * pn * k / max(probe, 1e-6)
+    per_step = seconds_budget / max(1, steps + warmup)
+    target_flops = rate * per_step
+    ms = min(m, 2048)
+    ns = int(min(n, max(256, target_flops / (2.0 * ms * k))))
+    ns = max(16, ns // 16 * 16)
+    a_q, b_q, sa, sb = oracle.make_inputs(ms, ns, k, in_dtype, seed=2)
+    for _ in range(warmup):
+        oracle.run_torch(a_q, b_q, sa, sb)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.run_torch(a_q, b_q, sa, sb)
+    dt = (time.perf_counter() - t0) / steps
+    tflops = 2.0 * ms * ns * k / dt / 1e12
+    sample = f"rows[0:{ms}] x channels[0:{ns}] x K={k} of the workload, fp32 dequantise + torch.mm, {steps} timed pass(es)"
+    return tflops, sample, dt, threads
+
+
+def run_reference_arm(args, m, n, k, in_dtype, workload):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tflops, sample, dt, threads = cpu_reference_rate(m, n, k, in_dtype, seconds_budget=90.0, steps=args.steps,
+                                                     warmup=args.warmup)
+    line = {
+        "impl": "reference",
+        "metric": "fp8_gemm_tflops",
+        "value": tflops,
+        "unit": "TFLOP/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": dt * 1e3,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": workload, "M": m, "N": n, "K": k, "in_dtype": in_dtype},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def quantised_on_gpu(m, n, k, in_dtype, dev, seed, weight_scale):
+    from flydsl_b200 import pertoken_quant
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    a = torch.randn(m, k, generator=g, device=dev)
+    a_q, sa = pertoken_quant(a, quant_dtype=FP8 if in_dtype == "fp8" else torch.int8)
+    del a
+    # weights in row chunks to bound the fp32 temporary
+    w_q = torch.empty(n, k, dtype=a_q.dtype, device=dev)
+    sb = torch.empty(n, 1, dtype=torch.float32, device=dev)
+    step = 8192
+    for i in range(0, n, step):
+        w = torch.randn(min(step, n - i), k, generator=g, device=dev) * weight_scale
+        if in_dtype == "int8":  # round to nearest, as the INT8 configuration states
+            s = w.abs().amax(dim=-1, keepdim=True) / 127.0
+            s.masked_fill_(s == 0, 1.0)
+            q = torch.round(w / s).clamp_(-127, 127).to(torch.int8)
+        else:
+            q, s = pertoken_quant(w, quant_dtype=FP8)
+        w_q[i : i + q.shape[0]] = q
+        sb[i : i + q.shape[0]] = s
+    return a_q, sa.view(-1), w_q, sb.view(-1)
+
+
+def time_config(m, n, k, in_dtype, dev, iters=40, hint=0):
+    """Device time of one single-GPU configuration with operand copies rotated
+    so that consecutive launches do not find their weights in L2."""
+    from flydsl_b200 import compile_preshuffle_gemm, shuffle_weight
+
+    per = m * k + n * k + 2 * m * n
+    copies = max(1, min(8, int(400e6 // per) + 1))
+    qd = FP8 if in_dtype == "fp8" else torch.int8
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=128, tile_n=256, tile_k=128, in_dtype=in_dtype, variant_hint=hint)
+    A, W, C = [], [], []
+    for i in range(copies):
+        if in_dtype == "fp8":
+            A.append((torch.randn(m, k, device=dev) * 64).clamp_(-448, 448).to(qd).view(torch.int8))
+            W.append(shuffle_weight((torch.randn(n, k, device=dev) * 64).clamp_(-448, 448).to(qd)).view(torch.int8))
+        else:
+            A.append(torch.randint(-127, 128, (m, k), device=dev, dtype=torch.int8))
+            W.append(shuffle_weight(torch.randint(-127, 128, (n, k), device=dev, dtype=torch.int8)))
+        C.append(torch.empty(m, n, dtype=torch.bfloat16, device=dev))
+    sa = torch.rand(m, device=dev) + 0.5
+    sb = torch.rand(n, device=dev) + 0.5
+    bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    st = torch.cuda.Stream()
+
+    def launch(i):
+        j = i % copies
+        fn(C[j].view(-1), A[j].view(-1), W[j].view(-1), sa, sb, bias, m, n, st)
+
+    with torch.cuda.stream(st):
+        for i in range(3):
+            launch(i)
+        st.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(iters):
+                launch(i)
+        g.replay()
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        g.replay()
+        e1.record(st)
+        st.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    return us, copies
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-GPU decode/prefill side measurements")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    m, n, k, in_dtype, wscale, seed = WORKLOADS[args.workload]
+    workload = f"{args.workload}: {in_dtype} A8W8 preshuffle GEMM M={m} N={n} K={k}, N split over GPUs"
+
+    if args.impl == "reference":
+        run_reference_arm(args, m, n, k, in_dtype, workload)
+        return
+
+    import torch.distributed as dist
+
+    from flydsl_b200 import _lib
+    from flydsl_b200.column_parallel import ColumnParallelGemm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    _lib.load()  # fail loudly if the CUDA library is missing
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    cpu_group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        cpu_group = dist.new_group(backend="gloo")
+
+    peaks = measured_peaks()
+    op = ColumnParallelGemm(n, k, in_dtype=in_dtype, rank=rank, world=world, cpu_group=cpu_group)
+    nl = op.spec.n_local
+    # every rank: replicated activations, its own weight shard (seeded per shard)
+    a_q, sa, w_q, sb = quantised_on_gpu(m, nl, k, in_dtype, dev, seed + 17 * rank, wscale)
+    if world > 1:  # identical activations on all ranks
+        dist.broadcast(a_q.view(torch.int8), src=0)
+        dist.broadcast(sa, src=0)
+    op.load_weight_shard(w_q, sb)
+    del w_q
+    c = torch.empty(m, nl, dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed region: K steps, inputs resident ---------------------
+    for _ in range(args.warmup):
+        op.forward(a_q, sa, out=c)
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    evs[0].record(stream)
+    for i in range(args.steps):
+        op.forward(a_q, sa, out=c)
+        evs[i + 1].record(stream)
+    barrier()
+    total_ms = evs[0].elapsed_time(evs[-1])
+    kernel_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    clocks = sampler.stop() if sampler else None
+    status = _lib.read_status()
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    flops_step = 2.0 * m * n * k
+    value = flops_step / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end: host buffers in, host buffer out ------------------------
+    a_host = torch.empty(a_q.shape, dtype=torch.int8).pin_memory()
+    a_host.copy_(a_q.view(torch.int8))
+    sa_host = sa.cpu().pin_memory()
+    c_host = torch.empty(m, nl, dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty_like(a_q.view(torch.int8))
+    sa_dev = torch.empty_like(sa)
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        a_dev.copy_(a_host, non_blocking=True)
+        sa_dev.copy_(sa_host, non_blocking=True)
+        op.forward(a_dev, sa_dev, out=c)
+        c_host.copy_(c, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    s1.record(stream)
+    barrier()
+    t = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / e2e_steps
+    e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
+    h2d = a_host.numel() + sa_host.numel() * 4
+    d2h = c_host.numel() * 2
+
+    # ---- optional: with the all-gather of the shards (full output on every rank)
+    gathered = None
+    if world > 1:
+        for _ in range(2):
+            op.forward_full(a_q, sa, row_major=False)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        reps = max(3, min(args.steps, 10))
+        for _ in range(reps):
+            op.forward_full(a_q, sa, row_major=False)
+        g1.record(stream)
+        barrier()
+        t = torch.tensor([g0.elapsed_time(g1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        g_ms = float(t.item()) / reps
+        gathered = {"ms_per_step": g_ms, "tflops": flops_step / (g_ms * 1e-3) / 1e12,
+                    "what": "GEMM shard + NCCL all-gather of bf16 shards (shard-major result)"}
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- rank 0: roofline, extras, CPU baseline, the JSON line ----------------
+    med_ms = statistics.median(kernel_ms)
+    flops_launch = 2.0 * m * nl * k
+    achieved = flops_launch / (med_ms * 1e-3) / 1e12
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    roofline = {
+        "bound": "tensor",
+        "kernel": "gemm_rows_kernel<fp8, BN=256, 4 stages> (tcgen05 kind::f8f6f4, 128x256 tiles)",
+        "achieved": achieved,
+        "peak": fp8_peak,
+        "unit": "TFLOP/s",
+        "frac": achieved / fp8_peak,
+        "peak_source": f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no FP8 figure is measured",
+        "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+        "traffic": None,
+        "algorithmic_bytes": gemm_bytes(m, nl, k),
+        "launch_ms_median": med_ms,
+    }
+    extras = {}
+    if not args.no_extras:
+        for name, (em, en, ek, edt) in {
+            "c1_fp8_128x4096x4096": (128, 4096, 4096, "fp8"),
+            "c2_int8_32x8192x8192": (32, 8192, 8192, "int8"),
+            "c4_fp8_1x8192x8192": (1, 8192, 8192, "fp8"),
+            "c4_fp8_16x8192x8192": (16, 8192, 8192, "fp8"),
+            "c4_fp8_64x8192x8192": (64, 8192, 8192, "fp8"),
+            "c4_fp8_256x8192x8192": (256, 8192, 8192, "fp8"),
+            "c4_fp8_1024x8192x8192": (1024, 8192, 8192, "fp8"),
+            "c4_fp8_4096x8192x8192": (4096, 8192, 8192, "fp8"),
+            "c3_fp8_8192x28672x8192": (8192, 28672, 8192, "fp8"),
+        }.items():
+            us, copies = time_config(em, en, ek, edt, dev, iters=20 if em <= 4096 and en <= 8192 else 5)
+            by = gemm_bytes(em, en, ek)
+            extras[name] = {
+                "us": round(us, 2),
+                "tflops": round(2.0 * em * en * ek / us / 1e6, 1),
+                "hbm_gbs": round(by / us / 1e3, 1),
+                "hbm_frac_of_measured": round(by / us / 1e3 / peaks["hbm_gbs"], 3),
+                "frac_of_nominal_fp8": round(2.0 * em * en * ek / us / 1e6 / NOMINAL_FP8_TFLOPS, 3),
+                "rotating_copies": copies,
+            }
+    cpu = None
+    if not args.no_cpu_baseline and world == 1:
+        tf, sample, dt, threads = cpu_reference_rate(m, n, k, in_dtype, seconds_budget=15.0, steps=1, warmup=0)
+        cpu = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}
+
+    line = {
+        "metric": "fp8_gemm_tflops",
+        "value": value,
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 accumulate -> bf16" if in_dtype == "fp8" else "s8 x s8 -> s32 -> bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": workload,
+            "M": m, "N": n, "K": k, "n_per_gpu": nl, "in_dtype": in_dtype, "out_dtype": "bf16",
+            "parallelism": f"column-parallel x{world} (no collective on the data path)",
+            "l2": "operands per GPU exceed L2 (126 MB); no flush needed",
+            "per_gpu_tflops": value / world,
+            "per_gpu_frac_of_nominal_fp8_4500": value / world / NOMINAL_FP8_TFLOPS,
+        },
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+        "device_status": status,
+    }
+    if gathered:
+        line["with_allgather"] = gathered
+    if extras:
+        line["extras"] = extras
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,144 @@
+"""Column-parallel use of the preshuffle GEMM across the GPUs of one machine.
+
+The output channels (N) are split into contiguous, equal shards, one per
+rank; every rank holds the activations A (replicated), its own weight shard
+preshuffled locally, and computes C[:, n0:n1] with the single-GPU kernel.
+There is no reduction across ranks (K is never split), so the data path has no
+collective unless the caller asks for the full output, in which case the bf16
+shards are all-gathered with NCCL.
+
+The reference has no multi-GPU form of this operator; the only collective in
+its tree that matches is the ``all_gather_into_tensor`` fallback of
+kernels/comm/custom_all_reduce.py:929-938.  One process per GPU, as in
+tests/kernels/test_allreduce.py:267,629-644.
+"""
+
+from __future__ import annotations
+
+import datetime
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class ShardSpec:
+    n_total: int
+    world: int
+    rank: int
+
+    @property
+    def n_local(self) -> int:
+        return self.n_total // self.world
+
+    @property
+    def n0(self) -> int:
+        return self.rank * self.n_local
+
+    @property
+    def n1(self) -> int:
+        return self.n0 + self.n_local
+
+
+def shard_spec(n_total: int, world: int, rank: int) -> ShardSpec:
+    """Equal contiguous shards of the output channels; each must itself be a
+    valid weight image (a multiple of 16 channels)."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad rank/world: {rank}/{world}")
+    if n_total % world != 0 or (n_total // world) % 16 != 0:
+        raise ValueError(f"N={n_total} cannot be split into {world} shards that are multiples of 16 channels")
+    return ShardSpec(n_total, world, rank)
+
+
+def check_agreement(desc: dict, group=None, timeout_s: float = 60.0) -> None:
+    """Host-side handshake before any GPU collective: every rank publishes its
+    view of the problem (shape, dtypes, shard) and all must match, so a missing
+    or mismatched rank surfaces as a Python error on the CPU instead of a hung
+    NCCL kernel.  Uses the object collectives of ``group`` (pass a gloo group
+    to keep the handshake off the GPU)."""
+    world = dist.get_world_size(group)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, desc, group=group)
+    ref = {k: v for k, v in gathered[0].items() if k != "rank"}
+    for r, d in enumerate(gathered):
+        if d is None:
+            raise RuntimeError(f"rank {r} did not answer the handshake")
+        other = {k: v for k, v in d.items() if k != "rank"}
+        if other != ref:
+            raise RuntimeError(f"rank {r} disagrees on the problem: {other} vs {ref}")
+    ranks = sorted(d["rank"] for d in gathered)
+    if ranks != list(range(world)):
+        raise RuntimeError(f"ranks present {ranks}, expected 0..{world - 1}")
+
+
+def gather_columns(local: torch.Tensor, world: int, group=None, row_major: bool = True) -> torch.Tensor:
+    """All-gather the [M, N/world] shards.  NCCL concatenates along dim 0, so
+    the natural result is shard-major [world, M, N/world]; ``row_major=True``
+    adds one local copy into [M, N]."""
+    m, nl = local.shape
+    out = torch.empty(world, m, nl, dtype=local.dtype, device=local.device)
+    try:
+        dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+    except (RuntimeError, NotImplementedError):  # backends without the fused form (old gloo)
+        parts = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(parts, local.contiguous(), group=group)
+        out = torch.stack(parts)
+    if not row_major:
+        return out
+    return out.permute(1, 0, 2).reshape(m, world * nl)
+
+
+class ColumnParallelGemm:
+    """One rank's share of C = A . W^T split on the output channels."""
+
+    def __init__(self, N: int, K: int, in_dtype: str = "fp8", out_dtype: str = "bf16", group=None, cpu_group=None,
+                 rank: int | None = None, world: int | None = None):
+        from .kernels.gemm.preshuffle_gemm import compile_preshuffle_gemm
+
+        self.group = group
+        self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
+        self.spec = shard_spec(N, self.world, self.rank)
+        self.N, self.K, self.in_dtype, self.out_dtype = N, K, in_dtype, out_dtype
+        if dist.is_initialized() and self.world > 1:
+            check_agreement(
+                dict(rank=self.rank, N=N, K=K, in_dtype=in_dtype, out_dtype=out_dtype, n_local=self.spec.n_local),
+                group=cpu_group if cpu_group is not None else group,
+            )
+        self.launch = compile_preshuffle_gemm(
+            N=self.spec.n_local, K=K, tile_m=128, tile_n=256, tile_k=128, in_dtype=in_dtype, out_dtype=out_dtype
+        )
+        self.w_shuf = None
+        self.sb = None
+        self._bias = None
+
+    def load_weight_shard(self, w_q_local: torch.Tensor, sb_local: torch.Tensor) -> None:
+        """Take this rank's rows [n0, n1) of the quantised weights (row-major)
+        and preshuffle them locally: the weight image is not contiguous in N,
+        so shards are shuffled after the split, never before."""
+        from .utils import shuffle_weight
+
+        if tuple(w_q_local.shape) != (self.spec.n_local, self.K):
+            raise ValueError(f"weight shard must be [{self.spec.n_local}, {self.K}], got {tuple(w_q_local.shape)}")
+        self.w_shuf = shuffle_weight(w_q_local).view(torch.int8 if w_q_local.element_size() == 1 else w_q_local.dtype)
+        self.sb = sb_local.contiguous().view(-1)
+        self._bias = torch.empty(0, dtype=torch.bfloat16 if self.out_dtype == "bf16" else torch.float16,
+                                 device=w_q_local.device)
+
+    def forward(self, a_q: torch.Tensor, sa: torch.Tensor, out: torch.Tensor | None = None, stream=None):
+        """C[:, n0:n1] for this rank (bf16 [M, N/world]); asynchronous."""
+        m = a_q.shape[0]
+        if out is None:
+            out = torch.empty(m, self.spec.n_local, dtype=self._bias.dtype, device=a_q.device)
+        a = a_q.view(torch.int8) if a_q.element_size() == 1 else a_q
+        self.launch(out.view(-1), a.view(-1), self.w_shuf.view(-1), sa.view(-1), self.sb, self._bias, m,
+                    self.spec.n_local, stream if stream is not None else torch.cuda.current_stream())
+        return out
+
+    def forward_full(self, a_q, sa, row_major: bool = True):
+        """Full [M, N] on every rank: local shard, then an NCCL all-gather."""
+        local = self.forward(a_q, sa)
+        if self.world == 1:
+            return local
+        return gather_columns(local, self.world, self.group, row_major=row_major)

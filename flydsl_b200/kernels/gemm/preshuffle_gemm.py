@@ -116,6 +116,10 @@ class PreshuffleGemm:
             nbytes = self._ws_bytes.get((dev.index, M))
             if nbytes is None:
                 nbytes = int(lib.flyb200_workspace_bytes(M, self.N, self.K, self._dt))
+                forced_split = self.variant_hint & 0xFF
+                if forced_split > 1 and M <= 256:  # a tuning override may ask for more than the default
+                    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+                    nbytes = max(nbytes, 16384 + forced_split * ((self.N + 127) // 128) * bn * 128 * 4)
                 self._ws_bytes[(dev.index, M)] = nbytes
             ws_ptr, ws_len = _workspace(dev, s, nbytes)
             rc = lib.flyb200_gemm_a8w8(

@@ -165,9 +165,13 @@ def run_torch(a, b, scale_a, scale_b, bias=None, dtype=torch.float32):
 def int32_acc(a_i8: torch.Tensor, b_i8: torch.Tensor) -> torch.Tensor:
     """Exact int32 accumulators of the INT8 path: what the reference's MFMA
     int32 accumulation holds before scaling
-    (kernels/gemm/preshuffle_gemm.py:538,739).  Computed exactly; an fp32
-    matmul would not be exact because |acc| may pass 2**24."""
-    return a_i8.to(torch.int32) @ b_i8.to(torch.int32).T
+    (kernels/gemm/preshuffle_gemm.py:538,739).  Computed exactly: every partial
+    sum is an integer below 2**53, so a float64 matmul is exact (an fp32 matmul
+    would not be: |acc| may pass 2**24) and much faster than an integer one."""
+    k = a_i8.shape[-1]
+    assert k * 128 * 128 < 2**31, "int32 accumulators would overflow"
+    acc = a_i8.to(torch.float64) @ b_i8.to(torch.float64).T
+    return acc.to(torch.int64).to(torch.int32)
 
 
 def epilogue(acc, scale_a, scale_b, bias=None, kind="none", out_dtype=torch.bfloat16):

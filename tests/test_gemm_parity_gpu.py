@@ -1,0 +1,237 @@
+"""GPU parity: the CUDA path (through the C ABI) against the CPU oracle.
+
+Bars: INT8 int32 accumulators bit-exact; FP8/INT8 bf16 outputs with every
+element within rtol 1e-2 / atol 1e-2 of the fp32 dequantise-and-matmul
+reference; guard rows past M untouched; CUDA-graph replay == eager.
+Shapes follow the reference's test matrix
+(tests/kernels/test_preshuffle_gemm.py:119-126,779-883) and the benchmark
+configurations.
+"""
+
+import pytest
+import torch
+
+from flydsl_b200 import _lib, compile_preshuffle_gemm, shuffle_weight, unshuffle_weight
+from flydsl_b200 import compiler as flyc
+from oracle import a8w8_oracle as oracle
+from tests.helpers import as_i8, device_status, gpu_acc, make_workspace
+
+pytestmark = pytest.mark.gpu
+
+RTOL = ATOL = 1e-2  # stated tolerance for fp8 / scaled outputs against the fp32 reference
+SENTINEL = -8192.0
+DEC, ROWS = 1 << 8, 2 << 8
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda:0")
+
+
+def run_gemm(dev, a_q, b_q, sa, sb, m, n, k, in_dtype, hint=0, tile=(128, 128, 128), use_compile=True):
+    fn = compile_preshuffle_gemm(
+        N=n, K=k, tile_m=tile[0], tile_n=tile[1], tile_k=tile[2], in_dtype=in_dtype, variant_hint=hint
+    )
+    rows = ((m + 127) // 128) * 128 + 8
+    c_alloc = torch.full((rows, n), SENTINEL, dtype=torch.bfloat16, device=dev)
+    b_shuf = shuffle_weight(b_q.to(dev), layout=(16, 16))
+    args = (
+        c_alloc.view(-1),
+        as_i8(a_q.to(dev)).contiguous().view(-1),
+        as_i8(b_shuf).contiguous().view(-1),
+        sa.to(dev).contiguous().view(-1),
+        sb.to(dev).contiguous().view(-1),
+        torch.empty(0, dtype=torch.bfloat16, device=dev),
+        m,
+        n,
+        torch.cuda.current_stream(),
+    )
+    f = flyc.compile(fn, *args) if use_compile else fn
+    assert f(*args) is None
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    return c_alloc
+
+
+def check_scaled(c_alloc, a_q, b_q, sa, sb, m):
+    ref = oracle.run_torch(a_q, b_q, sa, sb)
+    got = c_alloc[:m].float().cpu()
+    bad = oracle.strict_mismatches(got, ref, RTOL, ATOL)
+    assert bad == 0, f"{bad} of {got.numel()} elements outside rtol/atol {RTOL}; max abs diff {(got - ref).abs().max()}"
+    assert oracle.verify_output(got, ref, rtol=0.1, atol=0.1)  # the reference's own (looser) rule
+    n_guard = int((c_alloc[m:] != SENTINEL).sum().item())
+    assert n_guard == 0, f"{n_guard} element(s) written past row M={m}"
+
+
+# --- the reference's small shapes + ragged M, both 8-bit dtypes, both kernels
+
+
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+@pytest.mark.parametrize(
+    "m,n,k,tile",
+    [
+        (16, 5120, 8192, (16, 64, 512)),
+        (33, 1024, 2048, (32, 64, 512)),
+        (1, 8192, 8192, (16, 64, 256)),
+        (128, 4096, 4096, (128, 128, 128)),  # benchmark config 1
+        (257, 1024, 1152, (128, 128, 128)),  # just past the small-M kernel; K = 9 * 128
+        (513, 2064, 2048, (64, 256, 128)),  # N not a multiple of the tile
+    ],
+)
+def test_scaled_output_matches_reference_check(dev, in_dtype, m, n, k, tile):
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=1000 + m)
+    c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, in_dtype, tile=tile)
+    check_scaled(c, a_q, b_q, sa, sb, m)
+
+
+@pytest.mark.parametrize("hint", [DEC | 1, DEC | 2, DEC | 5, ROWS])
+@pytest.mark.parametrize("m", [1, 16, 17, 64, 100, 256])
+def test_every_kernel_variant_small_m(dev, hint, m):
+    n, k = 1040, 2048
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "fp8", seed=77 + m)
+    c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, "fp8", hint=hint)
+    check_scaled(c, a_q, b_q, sa, sb, m)
+
+
+# --- INT8: accumulators bit-exact before scaling
+
+
+@pytest.mark.parametrize(
+    "m,n,k,hint,split",
+    [
+        (32, 8192, 8192, 0, 0),  # benchmark config 2, automatic variant
+        (32, 8192, 8192, DEC, 1),
+        (32, 8192, 8192, DEC, 4),
+        (7, 144, 1024, DEC, 3),
+        (200, 512, 1024, DEC, 2),
+        (300, 784, 1024, ROWS, 0),
+        (1024, 2048, 8320, ROWS, 0),  # K = 65 * 128 as in the reference's large shapes
+    ],
+)
+def test_int8_accumulators_bit_exact(dev, m, n, k, hint, split):
+    a_q, b_q, _, _ = oracle.make_inputs(m, n, k, "int8", seed=5 + m + n, rne_int8=True)
+    ws = make_workspace(m, n, k, "int8", dev, split_k=split)
+    acc = gpu_acc(a_q.to(dev), shuffle_weight(b_q.to(dev)), m, n, k, "int8", variant_hint=hint | split, workspace=ws)
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    want = oracle.int32_acc(a_q, b_q)
+    assert torch.equal(acc.cpu(), want)
+    assert int(ws[:16384].any().item()) == 0, "split-K tickets must be left at zero"
+
+
+def test_int8_extreme_values_exact(dev):
+    """All-(-128) x all-(-128) and mixed signs: the largest accumulators int32 can be asked to hold here."""
+    m, n, k = 16, 256, 8192
+    a = torch.full((m, k), -128, dtype=torch.int8)
+    b = torch.full((n, k), -128, dtype=torch.int8)
+    b[1::2] = 127
+    acc = gpu_acc(a.to(dev), shuffle_weight(b.to(dev)), m, n, k, "int8", variant_hint=DEC | 1)
+    assert torch.equal(acc.cpu(), oracle.int32_acc(a, b))
+
+
+def test_fp8_accumulators_close_to_fp32(dev):
+    m, n, k = 64, 512, 8192
+    a_q, b_q, _, _ = oracle.make_inputs(m, n, k, "fp8", seed=9)
+    acc = gpu_acc(a_q.to(dev), shuffle_weight(b_q.to(dev)), m, n, k, "fp8").view(torch.float32).cpu()
+    ref = a_q.float() @ b_q.float().T
+    assert torch.allclose(acc, ref, rtol=1e-4, atol=ref.abs().max().item() * 1e-6)
+
+
+# --- weight preshuffle on the GPU against its CPU statement
+
+
+@pytest.mark.parametrize("dtype", [torch.int8, torch.float8_e4m3fn, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(16, 128), (1024, 2048), (2, 48, 384), (5120, 8320)])
+def test_shuffle_weight_kernel(dev, dtype, shape):
+    g = torch.Generator().manual_seed(11)
+    x = torch.randint(-120, 120, shape, generator=g).to(torch.float32).to(dtype)
+    img = shuffle_weight(x.to(dev))
+    assert getattr(img, "is_shuffled", False) and img.shape == x.shape and img.dtype == x.dtype
+    want = oracle.shuffle_weight_b200(x)
+    assert torch.equal(img.cpu().view(torch.uint8), want.view(torch.uint8))
+    assert torch.equal(unshuffle_weight(img).cpu().view(torch.uint8), x.view(torch.uint8))
+    from_ref = shuffle_weight(oracle.shuffle_weight_mfma(x).to(dev), src_layout="mfma")
+    assert torch.equal(from_ref.cpu().view(torch.uint8), want.view(torch.uint8))
+
+
+# --- call conventions
+
+
+def test_cudagraph_capture_and_stream_forms(dev):
+    """Launch on the current stream is captured; replay == eager
+    (tests/kernels/test_preshuffle_gemm.py:779-883).  Also raw-int and None streams."""
+    m, n, k = 1, 8192, 8192
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "fp8", seed=42)
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype="fp8")
+    a, b = as_i8(a_q.to(dev)).view(-1), as_i8(shuffle_weight(b_q.to(dev))).view(-1)
+    sa_d, sb_d = sa.to(dev), sb.to(dev)
+    bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    c = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+
+    def call(stream):
+        fn(c.view(-1), a, b, sa_d, sb_d, bias, m, n, stream)
+
+    call(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    ref = c.clone()
+    assert ref.abs().max().item() > 0
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        call(torch.cuda.current_stream())  # warm-up on the capture stream
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    c.zero_()
+    with torch.cuda.graph(g, stream=s):
+        call(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    c.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert c.abs().max().item() > 0, "graph replay produced zeros: the launch was not captured"
+    assert torch.allclose(ref, c, atol=1e-2)
+    assert torch.equal(ref, c)  # deterministic reduction order: bitwise equal
+    for stream in (None, 0, torch.cuda.current_stream().cuda_stream):
+        c.zero_()
+        call(stream)
+        torch.cuda.synchronize()
+        assert torch.equal(ref, c)
+    assert device_status() == 0
+
+
+def test_results_are_deterministic_and_row_independent(dev):
+    """Size-independent properties at a benchmark-sized decode shape: repeated
+    launches are bitwise equal, permuting tokens permutes output rows bitwise,
+    doubling a token scale doubles its row exactly."""
+    m, n, k = 32, 8192, 8192
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "fp8", seed=4)
+    c1 = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, "fp8")[:m].clone()
+    c2 = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, "fp8")[:m]
+    assert torch.equal(c1, c2)
+    perm = torch.randperm(m, generator=torch.Generator().manual_seed(0))
+    cp = run_gemm(dev, a_q[perm], b_q, sa[perm], sb, m, n, k, "fp8")[:m]
+    assert torch.equal(cp, c1[perm.to(dev)])
+    cd = run_gemm(dev, a_q, b_q, sa * 2, sb, m, n, k, "fp8")[:m]
+    assert torch.equal(cd.float(), c1.float() * 2)
+
+
+def test_m_zero_and_tensor_checks(dev):
+    fn = compile_preshuffle_gemm(N=64, K=256, tile_m=16, tile_n=64, tile_k=256, in_dtype="int8")
+    c = torch.full((16, 64), SENTINEL, dtype=torch.bfloat16, device=dev)
+    a = torch.zeros(16 * 256, dtype=torch.int8, device=dev)
+    b = torch.zeros(64 * 256, dtype=torch.int8, device=dev)
+    sa, sb = torch.ones(16, device=dev), torch.ones(64, device=dev)
+    bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    assert fn(c.view(-1), a, b, sa, sb, bias, 0, 64, None) is None  # M = 0: nothing to do
+    torch.cuda.synchronize()
+    assert bool((c == SENTINEL).all())
+    with pytest.raises(ValueError, match="buffer sizes"):
+        fn(c.view(-1), a[:100], b, sa, sb, bias, 16, 64, None)
+    with pytest.raises(ValueError, match="scale"):
+        fn(c.view(-1), a, b, sa[:4], sb, bias, 16, 64, None)
+    with pytest.raises(ValueError, match="c must be"):
+        fn(c.float().view(-1), a, b, sa, sb, bias, 16, 64, None)
+    fn(c.view(-1), a, b, torch.nn.Parameter(sa, requires_grad=False), sb, bias, 16, 64, None)  # Parameter accepted
+    torch.cuda.synchronize()
+    assert bool((c == 0).all())
