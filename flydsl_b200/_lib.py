@@ -38,7 +38,7 @@ SIGNATURES = {
     "flyb200_shuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_unshuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "flyb200_layout_kind": (_i, [_i, _i, _i]),
-    "flyb200_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "flyb200_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "flyb200_read_status": (_i, [ctypes.POINTER(_i)]),
     "flyb200_strerror": (ctypes.c_char_p, [_i]),
     "flyb200_last_cuda_error": (ctypes.c_char_p, []),

@@ -1,0 +1,386 @@
+// Small-M ("decode") kernel: weights on the UMMA M side (128 output channels
+// per CTA), the few tokens on the N side (BN = 16..256), K optionally split
+// over several CTAs.  The kernel is a weight stream: every byte of the
+// preshuffled weights is read once, in 16 KiB bursts, through a deep TMA ring;
+// the tensor core is nearly idle and HBM bandwidth is the bound.
+//
+// How the K splits of one channel tile are combined (GemmParams::reduce_mode):
+//   REDUCE_NONE       one CTA owns the whole K range.
+//   REDUCE_CLUSTER    the splits of a tile form a thread-block cluster; every
+//                     CTA parks its partial tile in its own shared memory, and
+//                     after a cluster barrier each CTA sums a slice of the
+//                     tokens over all peers through distributed shared memory
+//                     (fixed order s = 0..S-1) and writes that slice of C.  No
+//                     global scratch, no atomics.
+//   REDUCE_WORKSPACE  partial tiles go to a global workspace; a per-tile ticket
+//                     elects the last CTA, which sums the partials in fixed
+//                     order.  Used when the split exceeds the cluster limit.
+#pragma once
+#include "gemm_kernels.cuh"
+
+namespace flyb200 {
+
+enum : int { REDUCE_NONE = 0, REDUCE_WORKSPACE = 1, REDUCE_CLUSTER = 2 };
+constexpr int MAX_CLUSTER_SPLIT = 8;
+
+// Shared-memory carve-up for a given ring depth (computed identically on host and device).
+struct DecodeLayout {
+  int off_w, off_a, off_bar, off_misc, off_sa, total;
+};
+__host__ __device__ inline DecodeLayout decode_layout(int bn, int stages) {
+  DecodeLayout l;
+  l.off_w = 0;
+  l.off_a = stages * BLOCK_ROWS * KBLOCK_BYTES;
+  l.off_bar = l.off_a + stages * bn * KBLOCK_BYTES;
+  l.off_misc = l.off_bar + 8 * (2 * stages + 1);
+  l.off_misc = (l.off_misc + 15) & ~15;
+  l.off_sa = l.off_misc + 32;
+  l.total = l.off_sa + bn * 4;
+  return l;
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Executed by every thread of every CTA of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t ld_dsmem(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_smem(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+template <int KIND, int BN, int OUTMODE>
+__global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                  const GemmParams p) {
+  using KT = KindTraits<KIND>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const int stages = p.stages;
+  const DecodeLayout L = decode_layout(BN, stages);
+  constexpr int W_STAGE = BLOCK_ROWS * KBLOCK_BYTES;
+  constexpr int A_STAGE = BN * KBLOCK_BYTES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L.off_misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L.off_misc + 4);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(smem_raw + L.off_misc + 12);
+  float* sa_s = reinterpret_cast<float*>(smem_raw + L.off_sa);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t bar_full = smem_base + L.off_bar;
+  const uint32_t bar_empty = bar_full + 8 * stages;
+  const uint32_t bar_tfull = bar_empty + 8 * stages;
+
+  if ((smem_base & 1023u) != 0) {  // same answer in every CTA of the grid
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_SMEM_ALIGN);
+    return;
+  }
+  const int n0 = blockIdx.x * BLOCK_ROWS;
+  const int num_kb_total = p.K_bytes / KBLOCK_BYTES;
+  const int kb_begin = blockIdx.y * p.kb_per_split;
+  const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
+  const int num_kb = kb_end - kb_begin;  // >= 1 by construction of the grid
+  const bool scaled = (p.sa != nullptr) && (p.sb != nullptr);
+  const uint32_t w_rows = static_cast<uint32_t>(min(BLOCK_ROWS, p.N - n0));
+  const uint32_t w_bytes = w_rows * KBLOCK_BYTES;
+  const int pre = min(stages, num_kb);  // k-blocks whose loads are issued before the CTA-wide set-up finishes
+  bool ok = true;
+
+  // With programmatic dependent launch (pdl != 0) this kernel may start while
+  // the previous kernel on the stream is still running.  Nothing produced by
+  // that kernel may be read, and nothing written, before griddepcontrol.wait.
+  //   pdl == 1: no global access at all before the wait.
+  //   pdl == 2: the weights are model state that no kernel on the stream
+  //             writes, so their first loads are issued before the wait.
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_tfull, 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;  // stays zero: lets the drain below wait on time alone
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    // Start the weight stream at once: the ring is empty, so the first `pre`
+    // stages need no wait, and the TMEM allocation and the CTA-wide barrier
+    // below overlap with these loads.
+    const uint64_t pol_w = l2_policy_evict_first();
+    const uint64_t pol_a = l2_policy_evict_last();
+    if (p.pdl == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(bar_full + 8 * i, A_STAGE + w_bytes);
+      bulk_load_1d(smem_base + L.off_w + i * W_STAGE,
+                   p.w + (static_cast<size_t>(kb_begin + i) * p.N + n0) * KBLOCK_BYTES, w_bytes, bar_full + 8 * i, pol_w);
+    }
+    if (p.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d(smem_base + L.off_a + i * A_STAGE, &tmA, bar_full + 8 * i, (kb_begin + i) * KBLOCK_BYTES, 0, pol_a);
+  }
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (p.pdl && threadIdx.x != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      const uint64_t pol_a = l2_policy_evict_last();
+      const uint64_t pol_w = l2_policy_evict_first();
+      int stage = pre == stages ? 0 : pre;
+      uint32_t phase = pre == stages ? 1u : 0u;
+      int issued = pre;
+      for (int kb = kb_begin + pre; kb < kb_end; ++kb) {
+        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+          report_failure(p.status, ST_TIMEOUT, abort_flag);
+          ok = false;
+          break;
+        }
+        const uint32_t fb = bar_full + 8 * stage;
+        mbar_expect_tx(fb, A_STAGE + w_bytes);
+        bulk_load_1d(smem_base + L.off_w + stage * W_STAGE, p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES,
+                     w_bytes, fb, pol_w);
+        tma_load_2d(smem_base + L.off_a + stage * A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, 0, pol_a);
+        ++issued;
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!ok || *abort_flag) {
+        // wait (bounded) for copies still in flight so none lands after the CTA is gone
+        const int pending = min(issued, stages);
+        for (int i = 0; i < pending; ++i) {
+          int s = stage - 1 - i;
+          uint32_t ph = phase;
+          if (s < 0) {
+            s += stages;
+            ph ^= 1u;
+          }
+          mbar_wait(bar_full + 8 * s, ph, abort_flag + 1);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issue -----------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, BLOCK_ROWS, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+          report_failure(p.status, ST_TIMEOUT, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint64_t wdesc = umma_desc_sw128_kmajor(smem_base + L.off_w + stage * W_STAGE);
+        const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L.off_a + stage * A_STAGE);
+#pragma unroll
+        for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
+          umma_ss<KIND>(tmem_base, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                        adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(bar_empty + 8 * stage);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok) umma_commit(bar_tfull);
+    }
+    __syncwarp();
+  }
+
+  // ------------------------------ epilogue --------------------------------
+  // thread <-> output channel (TMEM lane), registers <-> tokens
+  const int q = warp & 3;
+  const int ch_local = q * 32 + lane;
+  const int n = n0 + ch_local;
+  const uint32_t red_base = smem_base;  // partial tile [BN][128] words, reuses the (by then idle) ring
+  float sb_v = 0.0f, bias_v = 0.0f;
+  constexpr int CH = 16;  // tokens per TMEM load
+
+  auto emit = [&](int m, uint32_t raw) {
+    if (m < p.M && n < p.N) {
+      if constexpr (OUTMODE == OUT_RAW32) {
+        reinterpret_cast<uint32_t*>(p.c)[static_cast<size_t>(m) * p.N + n] = raw;
+      } else {
+        const float v = epilogue_value<KT::is_int>(raw, sa_s[m], sb_v, bias_v, p.epilogue, scaled);
+        reinterpret_cast<uint16_t*>(p.c)[static_cast<size_t>(m) * p.N + n] = pack1<OUTMODE>(v);
+      }
+    }
+  };
+
+  if (warp >= 2) {
+    // epilogue operands, fetched while the weight stream runs
+    const int et = threadIdx.x - 64;
+    for (int i = et; i < BN; i += 128) sa_s[i] = (scaled && i < p.M) ? __ldg(p.sa + i) : 0.0f;
+    sb_v = (scaled && n < p.N) ? __ldg(p.sb + n) : 0.0f;
+    bias_v = (p.epilogue != EPI_NONE && n < p.N) ? load_bias<OUTMODE>(p.bias, n) : 0.0f;
+    named_bar_sync(1, 128);
+
+    ok = mbar_wait(bar_tfull, 0, abort_flag);
+    if (!ok && lane == 0) report_failure(p.status, ST_TIMEOUT, abort_flag);
+    // uniform verdict over the four epilogue warps: the paths below meet at barriers
+    ok = named_bar_and(1, 128, ok);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.reduce_mode == REDUCE_NONE) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          if (c0 >= p.M) break;
+          uint32_t r[CH];
+          tmem_ld_x16(t_row + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) emit(c0 + j, r[j]);
+        }
+      } else if (p.reduce_mode == REDUCE_CLUSTER) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          if (c0 >= p.M) break;
+          uint32_t r[CH];
+          tmem_ld_x16(t_row + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) st_smem(red_base + static_cast<uint32_t>(((c0 + j) * BLOCK_ROWS + ch_local) * 4), r[j]);
+        }
+      } else {
+        // partials: [split][channel tile][token][128 channels], 32-bit
+        uint32_t* part = reinterpret_cast<uint32_t*>(p.ws_partials);
+        const size_t tile_elems = static_cast<size_t>(BN) * BLOCK_ROWS;
+        const size_t split_stride = static_cast<size_t>(gridDim.x) * tile_elems;
+        uint32_t* mine = part + blockIdx.y * split_stride + blockIdx.x * tile_elems + ch_local;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          if (c0 >= p.M) break;
+          uint32_t r[CH];
+          tmem_ld_x16(t_row + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) __stcg(mine + static_cast<size_t>(c0 + j) * BLOCK_ROWS, r[j]);
+        }
+        __threadfence();
+        named_bar_sync(1, 128);
+        if (threadIdx.x == 64) {
+          const int old = atomicAdd(p.ws_tickets + blockIdx.x, 1);
+          const int last = (old == p.split_k - 1) ? 1 : 0;
+          if (last) p.ws_tickets[blockIdx.x] = 0;  // leave the ticket ready for the next launch
+          *last_flag = last;
+        }
+        named_bar_sync(1, 128);
+        if (*last_flag) {
+          __threadfence();
+          const uint32_t* src = part + blockIdx.x * tile_elems + ch_local;
+          const int m_lim = min(p.M, BN);
+          constexpr int U = 8;  // tokens in flight per thread
+#pragma unroll 1
+          for (int m0 = 0; m0 < m_lim; m0 += U) {
+            // fixed summation order over the splits: the result does not
+            // depend on which CTA happened to arrive last
+            uint32_t acc[U];
+#pragma unroll
+            for (int j = 0; j < U; ++j) acc[j] = 0u;
+            for (int k = 0; k < p.split_k; ++k) {
+              uint32_t v[U];
+#pragma unroll
+              for (int j = 0; j < U; ++j)
+                v[j] = (m0 + j < m_lim) ? __ldcg(src + k * split_stride + static_cast<size_t>(m0 + j) * BLOCK_ROWS) : 0u;
+#pragma unroll
+              for (int j = 0; j < U; ++j) {
+                if constexpr (KT::is_int) {
+                  acc[j] = static_cast<uint32_t>(static_cast<int32_t>(acc[j]) + static_cast<int32_t>(v[j]));
+                } else {
+                  acc[j] = __float_as_uint((k == 0 ? 0.0f : __uint_as_float(acc[j])) + __uint_as_float(v[j]));
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < U; ++j) emit(m0 + j, acc[j]);
+          }
+        }
+      }
+    }
+  }
+
+  if (p.reduce_mode == REDUCE_CLUSTER) {
+    // Every thread of every CTA of the cluster comes here, also after a failed
+    // wait (all waits above are bounded), so the cluster barriers always complete.
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp >= 2 && ok) {
+      const uint32_t rank = cluster_ctarank();
+      const int S = p.split_k;
+      const int m_lim = min(p.M, BN);
+      const int chunk = (m_lim + S - 1) / S;
+      const int m_begin = static_cast<int>(rank) * chunk;
+      const int m_end = min(m_lim, m_begin + chunk);
+      uint32_t peer[MAX_CLUSTER_SPLIT];
+#pragma unroll
+      for (int s = 0; s < MAX_CLUSTER_SPLIT; ++s)
+        peer[s] = map_to_cta(red_base + static_cast<uint32_t>(ch_local * 4), static_cast<uint32_t>(s < S ? s : 0));
+      constexpr int U = 4;
+#pragma unroll 1
+      for (int m0 = m_begin; m0 < m_end; m0 += U) {
+        uint32_t v[MAX_CLUSTER_SPLIT][U];
+#pragma unroll
+        for (int s = 0; s < MAX_CLUSTER_SPLIT; ++s) {
+          if (s < S) {
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+              v[s][j] = (m0 + j < m_end) ? ld_dsmem(peer[s] + static_cast<uint32_t>((m0 + j) * BLOCK_ROWS * 4)) : 0u;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+          uint32_t acc = v[0][j];
+#pragma unroll
+          for (int s = 1; s < MAX_CLUSTER_SPLIT; ++s) {
+            if (s < S) {
+              if constexpr (KT::is_int) {
+                acc = static_cast<uint32_t>(static_cast<int32_t>(acc) + static_cast<int32_t>(v[s][j]));
+              } else {
+                acc = __float_as_uint(__uint_as_float(acc) + __uint_as_float(v[s][j]));
+              }
+            }
+          }
+          if (m0 + j < m_end) emit(m0 + j, acc);
+        }
+      }
+    }
+    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace flyb200

@@ -2,10 +2,12 @@
 // checks, tensor-map encoding, kernel selection and launch.  No allocation, no
 // synchronisation and no memcpy on the launch path.
 #include "../../include/flyb200.h"
-#include "gemm_kernels.cuh"
+#include "decode_kernel.cuh"
+#include "rows2_kernel.cuh"
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -126,22 +128,103 @@ int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams
   return FLYB200_OK;
 }
 
-template <int BN>
-struct DecodeStages {
-  static constexpr int value = BN <= 32 ? 8 : (BN <= 128 ? 6 : 4);
-};
+// The preshuffled weights as a 3-D tensor {128 bytes, N rows, K/128 k-blocks}; boxes of
+// 128 rows x one k-block are copied verbatim (the image is already swizzled).
+int make_weight_map(CUtensorMap* m, const void* base, uint64_t n_rows, uint64_t k_blocks, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
+    return FLYB200_E_CUDA;
+  }
+  cuuint64_t dims[3] = {KBLOCK_BYTES, n_rows, k_blocks};
+  cuuint64_t strides[2] = {KBLOCK_BYTES, n_rows * KBLOCK_BYTES};
+  cuuint32_t box[3] = {KBLOCK_BYTES, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled (weights) failed with CUresult %d",
+             static_cast<int>(r));
+    return FLYB200_E_CUDA;
+  }
+  return FLYB200_OK;
+}
+
+constexpr int ROWS2_STAGES = 6;
+
+template <int KIND, int OUTMODE>
+int launch_rows2(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmC, const GemmParams& p, int sms,
+                 cudaStream_t s) {
+  using L = Rows2Smem<ROWS2_STAGES>;
+  static std::atomic<uint64_t> done{0};
+  static int max_clusters[MAX_DEVICES] = {0};
+  auto kernel = gemm_rows2_kernel<KIND, ROWS2_STAGES, OUTMODE>;
+  int rc = ensure_smem(kernel, L::TOTAL, done);
+  if (rc) return rc;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (max_clusters[dev] == 0) {
+    cfg.gridDim = dim3(sms & ~1, 1, 1);
+    int n = 0;
+    CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    if (n < 1) return FLYB200_E_UNSUPPORTED;
+    max_clusters[dev] = n;
+  }
+  const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  const int clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmA, tmW, tmC, p));
+  return FLYB200_OK;
+}
+
+constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
+
+inline int default_decode_stages(int bn) { return bn <= 32 ? 8 : (bn <= 128 ? 6 : 4); }
 
 template <int KIND, int BN, int OUTMODE>
 int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
-  constexpr int STAGES = DecodeStages<BN>::value;
-  using L = DecodeSmem<BN, STAGES>;
   static std::atomic<uint64_t> done{0};
-  auto kernel = gemm_decode_kernel<KIND, BN, STAGES, OUTMODE>;
-  int rc = ensure_smem(kernel, L::TOTAL, done);
+  auto kernel = gemm_decode_kernel<KIND, BN, OUTMODE>;
+  int rc = ensure_smem(kernel, SMEM_LIMIT, done);
   if (rc) return rc;
-  dim3 grid((p.N + BLOCK_ROWS - 1) / BLOCK_ROWS, p.split_k, 1);
-  kernel<<<grid, NUM_THREADS, L::TOTAL, s>>>(tmA, p);
-  CUDA_TRY(cudaGetLastError());
+  const DecodeLayout L = decode_layout(BN, p.stages);
+  if (L.total > SMEM_LIMIT || BN * BLOCK_ROWS * 4 > L.off_bar) return FLYB200_E_UNSUPPORTED;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((p.N + BLOCK_ROWS - 1) / BLOCK_ROWS, p.split_k, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = L.total;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (p.reduce_mode == REDUCE_CLUSTER) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = 1;
+    attrs[na].val.clusterDim.y = p.split_k;
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (p.pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmA, p));
   return FLYB200_OK;
 }
 
@@ -178,44 +261,93 @@ size_t partial_bytes(int split, int N, int bn) {
 
 struct Plan {
   bool decode;
+  bool two_sm;  // large-M kernel as CTA pairs (tcgen05 cta_group::2)
   int bn;
   int split_k;
   int kb_per_split;
   int group_m;
+  int reduce_mode;
+  int stages;
+  int pdl;
 };
 
+// 0 = off, 1 = on, 2 = on and the weights are known to be static
+int pdl_default() {
+  static const int mode = []() {
+    const char* e = getenv("FLYB200_PDL");
+    if (!e) return 1;
+    return e[0] == '1' ? 1 : e[0] == '2' ? 2 : 0;
+  }();
+  return mode;
+}
+
+bool rows_two_sm_default() {
+  static const bool on = []() {
+    const char* e = getenv("FLYB200_ROWS_2SM");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+
+// variant_hint fields (see include/flyb200.h)
+inline int hint_split(int h) { return h & 0xFF; }
+inline int hint_kernel(int h) { return (h >> 8) & 0xF; }
+inline int hint_reduce(int h) { return (h >> 12) & 0xF; }
+inline int hint_group(int h) { return (h >> 16) & 0xFF; }
+inline int hint_stages(int h) { return (h >> 24) & 0xF; }
+inline int hint_pdl(int h) { return (h >> 28) & 0x3; }
+
+bool workspace_fits(bool have_ws, size_t ws_bytes, int split, int N, int bn) {
+  return have_ws && ws_bytes >= TICKET_BYTES + partial_bytes(split, N, bn) &&
+         (N + BLOCK_ROWS - 1) / BLOCK_ROWS <= static_cast<int>(TICKET_BYTES / sizeof(int));
+}
+
 int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t workspace_bytes, bool have_ws, int sms) {
-  const int want_kernel = (variant_hint >> 8) & 0xF;
-  const int want_split = variant_hint & 0xFF;
-  const int want_group = (variant_hint >> 16) & 0xFF;
-  plan->decode = want_kernel == 1 ? true : want_kernel == 2 ? false : (M <= 256);
+  const int want_kernel = hint_kernel(variant_hint);
+  const int want_split = hint_split(variant_hint);
+  const int want_reduce = hint_reduce(variant_hint);
+  if (want_kernel > 3) return FLYB200_E_BAD_ARG;
+  plan->decode = want_kernel == 1 ? true : want_kernel >= 2 ? false : (M <= 256);
+  plan->two_sm = want_kernel == 3 ? true : want_kernel == 2 ? false : rows_two_sm_default();
   if (plan->decode && M > 256) return FLYB200_E_UNSUPPORTED;
+  if (want_reduce > REDUCE_CLUSTER) return FLYB200_E_BAD_ARG;
   plan->bn = plan->decode ? decode_bn_for(M) : ROWS_BN;
-  plan->group_m = want_group > 0 ? want_group : 16;
+  plan->group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : (plan->two_sm ? 8 : 16);
   plan->split_k = 1;
+  plan->reduce_mode = REDUCE_NONE;
+  plan->stages = hint_stages(variant_hint) >= 2 ? hint_stages(variant_hint) : default_decode_stages(plan->bn);
+  const int hp = hint_pdl(variant_hint);
+  plan->pdl = hp == 1 ? 1 : hp == 2 ? 0 : hp == 3 ? 2 : pdl_default();
   const int kb = K_bytes / KBLOCK_BYTES;
   plan->kb_per_split = kb;
   if (plan->decode) {
     int split = want_split > 0 ? want_split : auto_split_k(N, K_bytes, sms);
     if (split > kb) split = kb;
+    int mode = REDUCE_NONE;
     if (split > 1) {
-      const bool fits = have_ws && workspace_bytes >= TICKET_BYTES + partial_bytes(split, N, plan->bn) &&
-                        (N + BLOCK_ROWS - 1) / BLOCK_ROWS <= static_cast<int>(TICKET_BYTES / sizeof(int));
-      if (!fits) {
-        if (want_split > 0) return FLYB200_E_WORKSPACE;  // an explicit request is not silently changed
-        while (split > 1 && !(have_ws && workspace_bytes >= TICKET_BYTES + partial_bytes(split, N, plan->bn))) --split;
+      mode = want_reduce != 0 ? want_reduce : (split <= MAX_CLUSTER_SPLIT ? REDUCE_CLUSTER : REDUCE_WORKSPACE);
+      if (mode == REDUCE_CLUSTER && split > MAX_CLUSTER_SPLIT) {
+        if (want_split > 0) return FLYB200_E_UNSUPPORTED;
+        split = MAX_CLUSTER_SPLIT;
+      }
+      if (mode == REDUCE_WORKSPACE && !workspace_fits(have_ws, workspace_bytes, split, N, plan->bn)) {
+        if (want_split > 0 || want_reduce != 0) return FLYB200_E_WORKSPACE;  // explicit requests are not changed silently
+        split = split < MAX_CLUSTER_SPLIT ? split : MAX_CLUSTER_SPLIT;
+        mode = REDUCE_CLUSTER;
       }
     }
     plan->kb_per_split = (kb + split - 1) / split;
     plan->split_k = (kb + plan->kb_per_split - 1) / plan->kb_per_split;
+    plan->reduce_mode = plan->split_k > 1 ? mode : REDUCE_NONE;
   }
   return FLYB200_OK;
 }
 
 template <int KIND, int OUTMODE>
-int run_kind(const Plan& plan, const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams& p, int sms,
-             cudaStream_t s) {
+int run_kind(const Plan& plan, const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmC,
+             const GemmParams& p, int sms, cudaStream_t s) {
   if (plan.decode) return launch_decode_bn<KIND, OUTMODE>(plan.bn, tmA, p, s);
+  if (plan.two_sm) return launch_rows2<KIND, OUTMODE>(tmA, tmW, tmC, p, sms, s);
   return launch_rows<KIND, OUTMODE>(tmA, tmC, p, sms, s);
 }
 
@@ -258,12 +390,20 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
   p.group_m = plan.group_m;
   p.split_k = plan.split_k;
   p.kb_per_split = plan.kb_per_split;
+  p.reduce_mode = plan.reduce_mode;
+  p.stages = plan.stages;
+  p.pdl = plan.pdl;
   p.ws_tickets = static_cast<int*>(workspace);
   p.ws_partials = workspace ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + TICKET_BYTES) : nullptr;
   p.status = st->status;
 
-  CUtensorMap tmA, tmC;
+  CUtensorMap tmA, tmC, tmW;
   memset(&tmC, 0, sizeof(tmC));
+  memset(&tmW, 0, sizeof(tmW));
+  if (!plan.decode && plan.two_sm) {
+    rc = make_weight_map(&tmW, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K_bytes / KBLOCK_BYTES), BLOCK_ROWS);
+    if (rc) return rc;
+  }
   rc = make_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, static_cast<uint64_t>(K_bytes), static_cast<uint64_t>(M),
                 KBLOCK_BYTES, plan.decode ? plan.bn : BLOCK_ROWS);
   if (rc) return rc;
@@ -276,19 +416,19 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (in_dtype) {
     case FLYB200_DT_FP8:
-      if (outmode == OUT_BF16) return run_kind<KIND_F8, OUT_BF16>(plan, tmA, tmC, p, st->sms, s);
-      if (outmode == OUT_FP16) return run_kind<KIND_F8, OUT_FP16>(plan, tmA, tmC, p, st->sms, s);
-      return run_kind<KIND_F8, OUT_RAW32>(plan, tmA, tmC, p, st->sms, s);
+      if (outmode == OUT_BF16) return run_kind<KIND_F8, OUT_BF16>(plan, tmA, tmW, tmC, p, st->sms, s);
+      if (outmode == OUT_FP16) return run_kind<KIND_F8, OUT_FP16>(plan, tmA, tmW, tmC, p, st->sms, s);
+      return run_kind<KIND_F8, OUT_RAW32>(plan, tmA, tmW, tmC, p, st->sms, s);
     case FLYB200_DT_INT8:
-      if (outmode == OUT_BF16) return run_kind<KIND_I8, OUT_BF16>(plan, tmA, tmC, p, st->sms, s);
-      if (outmode == OUT_FP16) return run_kind<KIND_I8, OUT_FP16>(plan, tmA, tmC, p, st->sms, s);
-      return run_kind<KIND_I8, OUT_RAW32>(plan, tmA, tmC, p, st->sms, s);
+      if (outmode == OUT_BF16) return run_kind<KIND_I8, OUT_BF16>(plan, tmA, tmW, tmC, p, st->sms, s);
+      if (outmode == OUT_FP16) return run_kind<KIND_I8, OUT_FP16>(plan, tmA, tmW, tmC, p, st->sms, s);
+      return run_kind<KIND_I8, OUT_RAW32>(plan, tmA, tmW, tmC, p, st->sms, s);
     case FLYB200_DT_FP16:
-      if (outmode == OUT_BF16) return run_kind<KIND_F16, OUT_BF16>(plan, tmA, tmC, p, st->sms, s);
-      return run_kind<KIND_F16, OUT_FP16>(plan, tmA, tmC, p, st->sms, s);
+      if (outmode == OUT_BF16) return run_kind<KIND_F16, OUT_BF16>(plan, tmA, tmW, tmC, p, st->sms, s);
+      return run_kind<KIND_F16, OUT_FP16>(plan, tmA, tmW, tmC, p, st->sms, s);
     case FLYB200_DT_BF16:
-      if (outmode == OUT_BF16) return run_kind<KIND_BF16, OUT_BF16>(plan, tmA, tmC, p, st->sms, s);
-      return run_kind<KIND_BF16, OUT_FP16>(plan, tmA, tmC, p, st->sms, s);
+      if (outmode == OUT_BF16) return run_kind<KIND_BF16, OUT_BF16>(plan, tmA, tmW, tmC, p, st->sms, s);
+      return run_kind<KIND_BF16, OUT_FP16>(plan, tmA, tmW, tmC, p, st->sms, s);
   }
   return FLYB200_E_BAD_ARG;
 }
@@ -395,15 +535,17 @@ int flyb200_layout_kind(int N, int K, int elem_bytes) {
   return 1;
 }
 
-size_t flyb200_workspace_bytes(int M, int N, int K, int in_dtype) {
-  if (M <= 0 || M > 256 || N <= 0 || K <= 0) return 0;
+size_t flyb200_workspace_bytes(int M, int N, int K, int in_dtype, int variant_hint) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int eb = elem_bytes_of(in_dtype);
   if (!flyb200_layout_kind(N, K, eb)) return 0;
   DeviceState* st = nullptr;
   if (device_state(&st)) return 0;
-  const int split = auto_split_k(N, K * eb, st->sms);
-  if (split <= 1) return 0;
-  return TICKET_BYTES + partial_bytes(split, N, decode_bn_for(M));
+  // plan as the GEMM would with an unlimited workspace, then size for that plan
+  Plan plan;
+  if (make_plan(&plan, M, N, K * eb, variant_hint, static_cast<size_t>(-1) >> 1, true, st->sms)) return 0;
+  if (!plan.decode || plan.reduce_mode != REDUCE_WORKSPACE) return 0;
+  return TICKET_BYTES + partial_bytes(plan.split_k, N, plan.bn);
 }
 
 int flyb200_read_status(int* out_status) {

@@ -44,8 +44,11 @@ struct GemmParams {
   int group_m;           // rasterisation group (row tiles per group)
   int split_k;           // decode kernel: number of K splits
   int kb_per_split;      // decode kernel: k-blocks per split
-  float* ws_partials;    // decode kernel, split_k > 1
-  int* ws_tickets;       // decode kernel, split_k > 1 (zero before first use; self-resetting)
+  int reduce_mode;       // decode kernel: how the K splits are combined (REDUCE_*)
+  int stages;            // decode kernel: depth of the shared-memory ring
+  int pdl;               // decode kernel: launched with programmatic stream serialisation
+  float* ws_partials;    // decode kernel, REDUCE_WORKSPACE
+  int* ws_tickets;       // decode kernel, REDUCE_WORKSPACE (zero before first use; self-resetting)
   int* status;           // device status word (first failure wins)
 };
 
@@ -125,6 +128,92 @@ __device__ __forceinline__ float load_bias(const void* bias, int col) {
     return __half2float(reinterpret_cast<const __half*>(bias)[col]);
   } else {
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col]);
+  }
+}
+
+// One warp's share (32 rows x BN columns) of an accumulator tile: TMEM ->
+// registers -> scale / bias / activation -> bf16|fp16 -> 128-byte-swizzled
+// staging buffer -> TMA store (clipped at M and N), or raw 32-bit stores.
+// `release_tmem()` is called once, as soon as the accumulator has been read.
+template <int KIND, int BN, int OUTMODE, typename ReleaseFn>
+__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* tmC, uint32_t t_row, int m0,
+                                                   int n0, int lane, uint32_t stage_c, int& cbuf,
+                                                   ReleaseFn release_tmem) {
+  using KT = KindTraits<KIND>;
+  constexpr int C_BUF = 32 * 128;
+  const bool scaled = (p.sa != nullptr) && (p.sb != nullptr);
+  const int row = m0 + lane;
+  const float sa_v = (scaled && row < p.M) ? __ldg(p.sa + row) : 0.0f;
+  if constexpr (OUTMODE == OUT_RAW32) {
+    uint32_t* out = reinterpret_cast<uint32_t*>(p.c);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_x32(t_row + c0, r);
+      tmem_ld_wait();
+      if (row < p.M) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const int col = n0 + c0 + j;
+          if (col + 3 < p.N) {
+            *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * p.N + col) =
+                make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+          } else {
+            for (int e = 0; e < 4; ++e)
+              if (col + e < p.N) out[static_cast<size_t>(row) * p.N + col + e] = r[j + e];
+          }
+        }
+      }
+    }
+    release_tmem();
+  } else {
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 64) {
+      uint32_t r0[32], r1[32];
+      tmem_ld_x32(t_row + c0, r0);
+      tmem_ld_x32(t_row + c0 + 32, r1);
+      tmem_ld_wait();
+      if (c0 + 64 >= BN) release_tmem();  // accumulator fully read: hand the TMEM buffer back
+      // the store issued two chunks ago has to be done reading this buffer
+      if (lane == 0) bulk_wait_group_read<1>();
+      __syncwarp();
+      const uint32_t cdst = stage_c + cbuf * C_BUF + lane * 128;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t(&r)[32] = h == 0 ? r0 : r1;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          const int col = n0 + c0 + h * 32 + j;
+          float sbv[8], bv[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const bool in = (col + e) < p.N;
+            sbv[e] = (scaled && in) ? __ldg(p.sb + col + e) : 0.0f;
+            bv[e] = (p.epilogue != EPI_NONE && in) ? load_bias<OUTMODE>(p.bias, col + e) : 0.0f;
+          }
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float lo = epilogue_value<KT::is_int>(r[j + 2 * e], sa_v, sbv[2 * e], bv[2 * e], p.epilogue, scaled);
+            float hi =
+                epilogue_value<KT::is_int>(r[j + 2 * e + 1], sa_v, sbv[2 * e + 1], bv[2 * e + 1], p.epilogue, scaled);
+            pk[e] = pack2<OUTMODE>(lo, hi);
+          }
+          const int chunk = (h * 32 + j) >> 3;  // 16-byte chunk index inside the 128-byte row
+          const uint32_t addr = cdst + static_cast<uint32_t>(((chunk ^ (lane & 7)) << 4));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
+                       "r"(pk[3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (m0 < p.M && (n0 + c0) < p.N) tma_store_2d(tmC, stage_c + cbuf * C_BUF, n0 + c0, m0);
+        bulk_commit_group();
+      }
+      cbuf ^= 1;
+    }
   }
 }
 
@@ -307,7 +396,6 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int ew = warp - 2; // staging buffer owner
     const uint32_t stage_c = smem_base + L::OFF_C + ew * 2 * L::C_BUF;
-    const bool scaled = (p.sa != nullptr) && (p.sb != nullptr);
     int acc = 0;
     uint32_t acc_phase = 0;
     int cbuf = 0;
@@ -317,329 +405,22 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tile_coords(t, m_blk, n_blk);
       const int m0 = m_blk * BLOCK_ROWS + q * 32;
       const int n0 = n_blk * BN;
-      const int row = m0 + lane;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
         if (lane == 0) report_failure(p.status, ST_TIMEOUT, abort_flag);
         ok = false;
         break;
       }
       tc_fence_after();
-      const float sa_v = (scaled && row < p.M) ? __ldg(p.sa + row) : 0.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
-
-      if constexpr (OUTMODE == OUT_RAW32) {
-        uint32_t* out = reinterpret_cast<uint32_t*>(p.c);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_x32(t_row + c0, r);
-          tmem_ld_wait();
-          if (row < p.M) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const int col = n0 + c0 + j;
-              if (col + 3 < p.N) {
-                *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * p.N + col) =
-                    make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-              } else {
-                for (int e = 0; e < 4; ++e)
-                  if (col + e < p.N) out[static_cast<size_t>(row) * p.N + col + e] = r[j + e];
-              }
-            }
-          }
-        }
+      epilogue_warp_tile<KIND, BN, OUTMODE>(p, &tmC, t_row, m0, n0, lane, stage_c, cbuf, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
-      } else {
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 64) {
-          uint32_t r0[32], r1[32];
-          tmem_ld_x32(t_row + c0, r0);
-          tmem_ld_x32(t_row + c0 + 32, r1);
-          tmem_ld_wait();
-          if (c0 + 64 >= BN) {  // accumulator fully read: hand the TMEM buffer back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
-          }
-          // the store issued two chunks ago has to be done reading this buffer
-          if (lane == 0) bulk_wait_group_read<1>();
-          __syncwarp();
-          const uint32_t cdst = stage_c + cbuf * L::C_BUF + lane * 128;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t(&r)[32] = h == 0 ? r0 : r1;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              const int col = n0 + c0 + h * 32 + j;
-              float sbv[8], bv[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const bool in = (col + e) < p.N;
-                sbv[e] = (scaled && in) ? __ldg(p.sb + col + e) : 0.0f;
-                bv[e] = (p.epilogue != EPI_NONE && in) ? load_bias<OUTMODE>(p.bias, col + e) : 0.0f;
-              }
-              uint32_t pk[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float lo = epilogue_value<KT::is_int>(r[j + 2 * e], sa_v, sbv[2 * e], bv[2 * e], p.epilogue, scaled);
-                float hi = epilogue_value<KT::is_int>(r[j + 2 * e + 1], sa_v, sbv[2 * e + 1], bv[2 * e + 1],
-                                                      p.epilogue, scaled);
-                pk[e] = pack2<OUTMODE>(lo, hi);
-              }
-              const int chunk = (h * 32 + j) >> 3;  // 16-byte chunk index inside the 128-byte row
-              const uint32_t addr = cdst + static_cast<uint32_t>(((chunk ^ (lane & 7)) << 4));
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]), "r"(pk[1]),
-                           "r"(pk[2]), "r"(pk[3])
-                           : "memory");
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (m0 < p.M && (n0 + c0) < p.N) tma_store_2d(&tmC, stage_c + cbuf * L::C_BUF, n0 + c0, m0);
-            bulk_commit_group();
-          }
-          cbuf ^= 1;
-        }
-      }
+      });
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
     if (lane == 0) bulk_wait_group<0>();
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    __syncwarp();
-    tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
-  }
-}
-
-// ===========================================================================
-// Small-M (decode) kernel
-// ===========================================================================
-template <int BN, int STAGES>
-struct DecodeSmem {
-  static constexpr int W_STAGE = BLOCK_ROWS * KBLOCK_BYTES;
-  static constexpr int A_STAGE = BN * KBLOCK_BYTES;
-  static constexpr int OFF_W = 0;
-  static constexpr int OFF_A = OFF_W + STAGES * W_STAGE;
-  static constexpr int OFF_BAR = OFF_A + STAGES * A_STAGE;  // full[S], empty[S], tfull
-  static constexpr int OFF_MISC = OFF_BAR + 8 * (2 * STAGES + 1);
-  static constexpr int TOTAL = OFF_MISC + 16;
-};
-
-template <int KIND, int BN, int STAGES, int OUTMODE>
-__global__ void __launch_bounds__(NUM_THREADS)
-gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p) {
-  using L = DecodeSmem<BN, STAGES>;
-  using KT = KindTraits<KIND>;
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const uint32_t smem_base = smem_u32(smem_raw);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L::OFF_MISC);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L::OFF_MISC + 4);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(smem_raw + L::OFF_MISC + 12);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t bar_full = smem_base + L::OFF_BAR;
-  const uint32_t bar_empty = bar_full + 8 * STAGES;
-  const uint32_t bar_tfull = bar_empty + 8 * STAGES;
-
-  if ((smem_base & 1023u) != 0) {
-    if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_SMEM_ALIGN);
-    return;
-  }
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
-    }
-    mbar_init(bar_tfull, 1);
-    abort_flag[0] = 0;
-    abort_flag[1] = 0;  // stays zero: lets the drain below wait on time alone
-    fence_mbar_init();
-    prefetch_tensormap(&tmA);
-  }
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  const int n0 = blockIdx.x * BLOCK_ROWS;
-  const int num_kb_total = p.K_bytes / KBLOCK_BYTES;
-  const int kb_begin = blockIdx.y * p.kb_per_split;
-  const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
-  const int num_kb = kb_end - kb_begin;  // >= 1 by construction of the grid
-
-  if (warp == 0) {
-    if (lane == 0) {
-      const uint64_t pol_a = l2_policy_evict_last();
-      const uint64_t pol_w = l2_policy_evict_first();
-      const uint32_t w_rows = static_cast<uint32_t>(min(BLOCK_ROWS, p.N - n0));
-      const uint32_t w_bytes = w_rows * KBLOCK_BYTES;
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int issued = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
-        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
-          report_failure(p.status, ST_TIMEOUT, abort_flag);
-          ok = false;
-          break;
-        }
-        const uint32_t fb = bar_full + 8 * stage;
-        mbar_expect_tx(fb, L::A_STAGE + w_bytes);
-        bulk_load_1d(smem_base + L::OFF_W + stage * L::W_STAGE,
-                     p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES, w_bytes, fb, pol_w);
-        tma_load_2d(smem_base + L::OFF_A + stage * L::A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, 0, pol_a);
-        ++issued;
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-      if (!ok || *abort_flag) {
-        const int pending = min(issued, STAGES);
-        for (int i = 0; i < pending; ++i) {
-          int s = stage - 1 - i;
-          uint32_t ph = phase;
-          if (s < 0) {
-            s += STAGES;
-            ph ^= 1u;
-          }
-          mbar_wait(bar_full + 8 * s, ph, abort_flag + 1);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, BLOCK_ROWS, BN);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
-          report_failure(p.status, ST_TIMEOUT, abort_flag);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint64_t wdesc = umma_desc_sw128_kmajor(smem_base + L::OFF_W + stage * L::W_STAGE);
-        const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L::OFF_A + stage * L::A_STAGE);
-#pragma unroll
-        for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
-          umma_ss<KIND>(tmem_base, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
-                        adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb | k) != 0 ? 1u : 0u);
-        }
-        umma_commit(bar_empty + 8 * stage);
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-      if (ok) umma_commit(bar_tfull);
-    }
-  } else {
-    // epilogue: thread <-> output channel n (TMEM lane), registers <-> tokens
-    const int q = warp & 3;
-    const int ch_local = q * 32 + lane;
-    const int n = n0 + ch_local;
-    const bool scaled = (p.sa != nullptr) && (p.sb != nullptr);
-    bool ok = mbar_wait(bar_tfull, 0, abort_flag);
-    if (!ok && lane == 0) report_failure(p.status, ST_TIMEOUT, abort_flag);
-    // make the verdict uniform over the four epilogue warps: the split-K path
-    // below meets at a named barrier, which every one of them must reach
-    ok = named_bar_and(1, 128, ok);
-    if (ok) {
-      tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      const float sb_v = (scaled && n < p.N) ? __ldg(p.sb + n) : 0.0f;
-      const float bias_v = (p.epilogue != EPI_NONE && n < p.N) ? load_bias<OUTMODE>(p.bias, n) : 0.0f;
-      constexpr int CH = 16;  // columns (tokens) per TMEM load
-
-      auto emit = [&](int m, uint32_t raw) {
-        if (m < p.M && n < p.N) {
-          if constexpr (OUTMODE == OUT_RAW32) {
-            reinterpret_cast<uint32_t*>(p.c)[static_cast<size_t>(m) * p.N + n] = raw;
-          } else {
-            const float sa_v = scaled ? __ldg(p.sa + m) : 0.0f;
-            const float v = epilogue_value<KT::is_int>(raw, sa_v, sb_v, bias_v, p.epilogue, scaled);
-            reinterpret_cast<uint16_t*>(p.c)[static_cast<size_t>(m) * p.N + n] = pack1<OUTMODE>(v);
-          }
-        }
-      };
-
-      if (p.split_k == 1) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += CH) {
-          uint32_t r[CH];
-          tmem_ld_x16(t_row + c0, r);
-          tmem_ld_wait();
-          if (c0 < p.M) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j) emit(c0 + j, r[j]);
-          }
-        }
-      } else {
-        // partials: [split][channel tile][token][128 channels], 32-bit
-        uint32_t* part = reinterpret_cast<uint32_t*>(p.ws_partials);
-        const size_t tile_elems = static_cast<size_t>(BN) * BLOCK_ROWS;
-        const size_t split_stride = static_cast<size_t>(gridDim.x) * tile_elems;
-        uint32_t* mine = part + blockIdx.y * split_stride + blockIdx.x * tile_elems + ch_local;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += CH) {
-          uint32_t r[CH];
-          tmem_ld_x16(t_row + c0, r);
-          tmem_ld_wait();
-          if (c0 < p.M) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j) __stcg(mine + static_cast<size_t>(c0 + j) * BLOCK_ROWS, r[j]);
-          }
-        }
-        __threadfence();
-        named_bar_sync(1, 128);
-        if (threadIdx.x == 64) {
-          const int old = atomicAdd(p.ws_tickets + blockIdx.x, 1);
-          const int last = (old == p.split_k - 1) ? 1 : 0;
-          if (last) p.ws_tickets[blockIdx.x] = 0;  // leave the ticket ready for the next launch
-          *last_flag = last;
-        }
-        named_bar_sync(1, 128);
-        if (*last_flag) {
-          __threadfence();
-          const uint32_t* src = part + blockIdx.x * tile_elems + ch_local;
-          const int m_lim = min(p.M, BN);
-#pragma unroll 1
-          for (int m = 0; m < m_lim; ++m) {
-            // fixed summation order over the splits: the result does not
-            // depend on which CTA happened to arrive last
-            uint32_t raw;
-            if constexpr (KT::is_int) {
-              int32_t s = 0;
-              for (int k = 0; k < p.split_k; ++k)
-                s += static_cast<int32_t>(__ldcg(src + k * split_stride + static_cast<size_t>(m) * BLOCK_ROWS));
-              raw = static_cast<uint32_t>(s);
-            } else {
-              float s = 0.0f;
-              for (int k = 0; k < p.split_k; ++k)
-                s += __uint_as_float(__ldcg(src + k * split_stride + static_cast<size_t>(m) * BLOCK_ROWS));
-              raw = __float_as_uint(s);
-            }
-            emit(m, raw);
-          }
-        }
-      }
-    }
   }
 
   tc_fence_before();

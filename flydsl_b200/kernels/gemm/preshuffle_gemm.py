@@ -115,11 +115,7 @@ class PreshuffleGemm:
         def run():
             nbytes = self._ws_bytes.get((dev.index, M))
             if nbytes is None:
-                nbytes = int(lib.flyb200_workspace_bytes(M, self.N, self.K, self._dt))
-                forced_split = self.variant_hint & 0xFF
-                if forced_split > 1 and M <= 256:  # a tuning override may ask for more than the default
-                    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-                    nbytes = max(nbytes, 16384 + forced_split * ((self.N + 127) // 128) * bn * 128 * 4)
+                nbytes = int(lib.flyb200_workspace_bytes(M, self.N, self.K, self._dt, self.variant_hint))
                 self._ws_bytes[(dev.index, M)] = nbytes
             ws_ptr, ws_len = _workspace(dev, s, nbytes)
             rc = lib.flyb200_gemm_a8w8(
@@ -134,6 +130,53 @@ class PreshuffleGemm:
                 run()
         else:
             run()
+        return None
+
+
+class CompiledPreshuffleGemm:
+    """What ``flyc.compile(launch_fn, *args)`` returns: the same call signature
+    with the per-call argument checks hoisted out (they ran once, on the
+    arguments given to ``compile``), as the reference's compiled function does
+    no checking either (python/flydsl/compiler/jit_executor.py:185-214).
+    Passing buffers smaller than M, N, K imply is then the caller's error."""
+
+    __slots__ = ("op", "_fn", "_ws")
+
+    def __init__(self, op: "PreshuffleGemm"):
+        self.op = op
+        self._fn = _lib.load().flyb200_gemm_a8w8
+        self._ws = {}
+
+    def __call__(self, arg_c, arg_a, arg_b, arg_scale_a, arg_scale_b, arg_bias, i32_m, i32_n, stream=None):
+        op = self.op
+        M = int(i32_m)
+        if M <= 0:
+            if M < 0:
+                raise ValueError("M must be non-negative")
+            return None
+        if i32_n != op.N:
+            raise ValueError(f"N passed at call time ({i32_n}) differs from the N the launcher was built for ({op.N})")
+        s = 0 if stream is None else (stream if isinstance(stream, int) else stream.cuda_stream)
+        dev = arg_c.device
+        key = (dev.index, M)
+        nbytes = self._ws.get(key)
+        if nbytes is None:
+            with torch.cuda.device(dev):
+                nbytes = int(_lib.load().flyb200_workspace_bytes(M, op.N, op.K, op._dt, op.variant_hint))
+            self._ws[key] = nbytes
+        ws = _workspace(dev, s, nbytes) if nbytes else (0, 0)  # looked up per call: the buffer may have grown
+        eight = op._is_8bit
+        if torch.cuda.current_device() != dev.index:
+            with torch.cuda.device(dev):
+                return self.__call__(arg_c, arg_a, arg_b, arg_scale_a, arg_scale_b, arg_bias, i32_m, i32_n, stream)
+        rc = self._fn(
+            arg_c.data_ptr(), arg_a.data_ptr(), arg_b.data_ptr(),
+            arg_scale_a.data_ptr() if eight else None, arg_scale_b.data_ptr() if eight else None,
+            arg_bias.data_ptr() if op._epi else None,
+            M, op.N, op.K, op._dt, op._out, op._epi, op.variant_hint, ws[0] or None, ws[1], s or None,
+        )  # fmt: skip
+        if rc:
+            _lib.check(rc, "preshuffle_gemm")
         return None
 
 

@@ -52,9 +52,24 @@ extern "C" {
 #define FLYB200_SRC_MFMA_16x16 1 /* already permuted by the reference's shuffle_weight(layout=(16,16)) */
 
 /* variant_hint: 0 = choose automatically.  Otherwise a bit field used for
- * tuning sweeps: bits 0-7 split-K factor (decode kernel), bits 8-11 kernel
- * (1 = small-M weight-stationary kernel, 2 = large-M persistent kernel),
- * bits 16-23 rasterisation group (row tiles per group, large-M kernel). */
+ * tuning sweeps (each field: 0 = automatic):
+ *   bits 0-7   split-K factor of the small-M kernel
+ *   bits 8-11  kernel: 1 = small-M weight-stationary kernel (M <= 256),
+ *              2 = large-M persistent kernel, one CTA per 128x256 tile,
+ *              3 = large-M persistent kernel, CTA pairs on 256x256 tiles
+ *              (automatic: 1 for M <= 256, else 2; 3 when FLYB200_ROWS_2SM=1)
+ *   bits 12-15 how K splits are combined: 1 = global workspace + ticket,
+ *              2 = thread-block cluster + distributed shared memory (split <= 8)
+ *   bits 16-23 rasterisation group (row tiles per group, large-M kernel)
+ *   bits 24-27 depth of the shared-memory ring of the small-M kernel
+ *   bits 28-29 programmatic dependent launch of the small-M kernel: 1 = on (its
+ *              set-up overlaps the tail of the previous kernel on the stream; no
+ *              global memory is touched before that kernel has completed),
+ *              3 = on, and additionally the first weight loads are issued before
+ *              the previous kernel has completed (only valid when no kernel on
+ *              the stream writes the weights), 2 = off.  Automatic: the first
+ *              form, unless the environment variable FLYB200_PDL says 0 (off)
+ *              or 2 (the second form). */
 
 /* The GEMM: c[M,N] = epilogue((a[M,K] . w[N,K]^T) * scale_a[m] * scale_b[n]).
  * Replaces the launcher returned by compile_preshuffle_gemm and the kernel
@@ -67,11 +82,12 @@ extern "C" {
  *   scale_a  [M] fp32 per-token scale, scale_b [N] fp32 per-channel scale; both
  *            NULL for FP16/BF16 inputs (no scaling)
  *   bias     [N] in out_dtype; NULL when epilogue == FLYB200_EPI_NONE
- *   workspace/workspace_bytes  scratch for split-K partial sums, sized by
- *            flyb200_workspace_bytes(); its first 16 KiB must be zero before the
- *            first use and are left zero by every completed call; may be NULL
- *            (then no split-K is used).  Two calls that overlap on the GPU must
- *            not share a workspace.
+ *   workspace/workspace_bytes  scratch for the split-K variant that reduces
+ *            through global memory, sized by flyb200_workspace_bytes(); its
+ *            first 16 KiB must be zero before the first use and are left zero by
+ *            every completed call; may be NULL (the automatic choice then keeps
+ *            partial sums on chip).  Two calls that overlap on the GPU must not
+ *            share a workspace.
  * Requirements: N % 16 == 0, K * elem_bytes % 128 == 0, pointers 16-byte aligned. */
 int flyb200_gemm_a8w8(void* c, const void* a, const void* w_shuf, const float* scale_a, const float* scale_b,
                       const void* bias, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
@@ -100,9 +116,9 @@ int flyb200_unshuffle_weight(void* dst, const void* src, int N, int K, int elem_
  * the call convention uses (tests/kernels/test_preshuffle_gemm.py:234-245). */
 int flyb200_layout_kind(int N, int K, int elem_bytes);
 
-/* Bytes of workspace that flyb200_gemm_a8w8 can make use of for this shape on
- * the current device (0 when the shape never uses split-K). */
-size_t flyb200_workspace_bytes(int M, int N, int K, int in_dtype);
+/* Bytes of workspace flyb200_gemm_a8w8 needs for this shape and variant_hint on
+ * the current device (0 when the chosen variant keeps its partial sums on chip). */
+size_t flyb200_workspace_bytes(int M, int N, int K, int in_dtype, int variant_hint);
 
 /* Device-side status word of the current device (0 = no failure since the last
  * read).  Synchronises the device; not for the launch path.  The reference only

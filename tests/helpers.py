@@ -32,12 +32,9 @@ def gpu_acc(a_q, b_shuf, m, n, k, in_dtype, variant_hint=0, workspace=None):
     return out
 
 
-def make_workspace(m, n, k, in_dtype, device, split_k=0, bn=None):
+def make_workspace(m, n, k, in_dtype, device, variant_hint=0):
     lib = _lib.load()
-    nbytes = int(lib.flyb200_workspace_bytes(m, n, k, _lib.IN_DTYPES[in_dtype]))
-    if split_k > 1:
-        bn = bn or (16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128 if m <= 128 else 256)
-        nbytes = max(nbytes, 16384 + split_k * ((n + 127) // 128) * bn * 128 * 4)
+    nbytes = int(lib.flyb200_workspace_bytes(m, n, k, _lib.IN_DTYPES[in_dtype], variant_hint))
     return torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=device)
 
 

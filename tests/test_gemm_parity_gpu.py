@@ -20,7 +20,13 @@ pytestmark = pytest.mark.gpu
 
 RTOL = ATOL = 1e-2  # stated tolerance for fp8 / scaled outputs against the fp32 reference
 SENTINEL = -8192.0
-DEC, ROWS = 1 << 8, 2 << 8
+DEC, ROWS, ROWS2 = 1 << 8, 2 << 8, 3 << 8  # variant_hint: kernel field (small-M, large-M, large-M as CTA pairs)
+WS, CL = 1 << 12, 2 << 12  # variant_hint: split-K reduction through a global workspace / a cluster
+PDL = 1 << 28  # variant_hint: programmatic dependent launch
+
+
+def STAGES(n):
+    return n << 24
 
 
 @pytest.fixture(scope="module")
@@ -84,7 +90,12 @@ def test_scaled_output_matches_reference_check(dev, in_dtype, m, n, k, tile):
     check_scaled(c, a_q, b_q, sa, sb, m)
 
 
-@pytest.mark.parametrize("hint", [DEC | 1, DEC | 2, DEC | 5, ROWS])
+@pytest.mark.parametrize(
+    "hint",
+    [DEC | 1, DEC | CL | 2, DEC | CL | 5, DEC | CL | 8, DEC | WS | 3, DEC | WS | 16, DEC | 2 | STAGES(3), DEC | 2 | PDL,
+     DEC | 2 | (2 << 28), ROWS, ROWS2],
+    ids=["nosplit", "cluster2", "cluster5", "cluster8", "ws3", "ws16", "stages3", "pdl", "nopdl", "rows", "rows2"],
+)
 @pytest.mark.parametrize("m", [1, 16, 17, 64, 100, 256])
 def test_every_kernel_variant_small_m(dev, hint, m):
     n, k = 1040, 2048
@@ -93,30 +104,45 @@ def test_every_kernel_variant_small_m(dev, hint, m):
     check_scaled(c, a_q, b_q, sa, sb, m)
 
 
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+@pytest.mark.parametrize("m,n,k", [(257, 1024, 1152), (513, 2064, 2048), (2048, 4096, 4096)])
+def test_cta_pair_kernel_scaled_output(dev, in_dtype, m, n, k):
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=31 + m)
+    c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, in_dtype, hint=ROWS2)
+    check_scaled(c, a_q, b_q, sa, sb, m)
+
+
 # --- INT8: accumulators bit-exact before scaling
 
 
 @pytest.mark.parametrize(
-    "m,n,k,hint,split",
+    "m,n,k,hint",
     [
-        (32, 8192, 8192, 0, 0),  # benchmark config 2, automatic variant
-        (32, 8192, 8192, DEC, 1),
-        (32, 8192, 8192, DEC, 4),
-        (7, 144, 1024, DEC, 3),
-        (200, 512, 1024, DEC, 2),
-        (300, 784, 1024, ROWS, 0),
-        (1024, 2048, 8320, ROWS, 0),  # K = 65 * 128 as in the reference's large shapes
+        (32, 8192, 8192, 0),  # benchmark config 2, automatic variant
+        (32, 8192, 8192, DEC | 1),
+        (32, 8192, 8192, DEC | CL | 4),
+        (32, 8192, 8192, DEC | WS | 4),
+        (7, 144, 1024, DEC | WS | 3),
+        (7, 144, 1024, DEC | CL | 3),
+        (200, 512, 1024, DEC | CL | 2),
+        (200, 512, 1024, DEC | WS | 2),
+        (300, 784, 1024, ROWS),
+        (1024, 2048, 8320, ROWS),  # K = 65 * 128 as in the reference's large shapes
+        (300, 784, 1024, ROWS2),
+        (100, 272, 256, ROWS2),
+        (1024, 2048, 8320, ROWS2),
     ],
 )
-def test_int8_accumulators_bit_exact(dev, m, n, k, hint, split):
+def test_int8_accumulators_bit_exact(dev, m, n, k, hint):
     a_q, b_q, _, _ = oracle.make_inputs(m, n, k, "int8", seed=5 + m + n, rne_int8=True)
-    ws = make_workspace(m, n, k, "int8", dev, split_k=split)
-    acc = gpu_acc(a_q.to(dev), shuffle_weight(b_q.to(dev)), m, n, k, "int8", variant_hint=hint | split, workspace=ws)
+    ws = make_workspace(m, n, k, "int8", dev, variant_hint=hint)
+    acc = gpu_acc(a_q.to(dev), shuffle_weight(b_q.to(dev)), m, n, k, "int8", variant_hint=hint, workspace=ws)
     torch.cuda.synchronize()
     assert device_status() == 0
     want = oracle.int32_acc(a_q, b_q)
     assert torch.equal(acc.cpu(), want)
-    assert int(ws[:16384].any().item()) == 0, "split-K tickets must be left at zero"
+    if ws.numel() > 16384:
+        assert int(ws[:16384].any().item()) == 0, "split-K tickets must be left at zero"
 
 
 def test_int8_extreme_values_exact(dev):

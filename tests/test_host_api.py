@@ -64,6 +64,7 @@ def test_argument_checks_need_no_gpu():
     assert lib.flyb200_shuffle_weight(p16, p16 + 4096, 16, 128, 1, 5, None) == _lib.E_BAD_ARG
     assert lib.flyb200_shuffle_weight(p16, p16 + 4096, 20, 128, 1, 0, None) == _lib.E_UNSUPPORTED
     assert lib.flyb200_gemm_a8w8_acc(p16, p16, p16, 1, 16, 128, _lib.DT_BF16, 0, None, 0, None) == _lib.E_UNSUPPORTED
+    assert lib.flyb200_workspace_bytes(32, 24, 128, 0, 0) == 0  # unsupported shape: nothing to size
     with pytest.raises(_lib.FlyB200Error, match="16-byte"):
         _lib.check(_lib.E_BAD_ALIGN)
 
