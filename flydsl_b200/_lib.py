@@ -12,7 +12,7 @@ import threading
 from . import build as _build
 
 OK = 0
-E_BAD_ARG, E_BAD_ALIGN, E_CUDA, E_TIMEOUT, E_UNSUPPORTED, E_SMEM_ALIGN, E_WORKSPACE = range(1, 8)
+E_BAD_ARG, E_BAD_ALIGN, E_CUDA, E_TIMEOUT, E_UNSUPPORTED, E_SMEM_ALIGN, E_WORKSPACE, E_SCRATCH_LIMIT = range(1, 9)
 
 DT_FP8, DT_INT8, DT_FP16, DT_BF16 = range(4)
 OUT_BF16, OUT_FP16 = range(2)
@@ -35,6 +35,8 @@ _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 SIGNATURES = {
     "flyb200_gemm_a8w8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "flyb200_gemm_a8w8_acc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "flyb200_gemm_a8w8_static_scratch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "flyb200_static_scratch_bytes": (_sz, []),
     "flyb200_shuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_unshuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "flyb200_layout_kind": (_i, [_i, _i, _i]),

@@ -481,6 +481,44 @@ bool ranges_overlap(const void* a, const void* b, size_t bytes) {
   return x < y + bytes && y < x + bytes;
 }
 
+// ---------------------------------------------------------------------------
+// Built-in scratch for callers that must not allocate device memory.
+//
+// The array lives in the library's device image: every GPU that loads the
+// library carries these 8 MiB from load until the process exits, whether the
+// entry point below is ever used or not.  On the host the symbol
+// `g_static_scratch` is only a handle for the runtime, not an address a kernel
+// can use; the usable device address is looked up once per device with
+// cudaGetSymbolAddress and cached.
+// ---------------------------------------------------------------------------
+constexpr size_t STATIC_SCRATCH_BYTES = static_cast<size_t>(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+struct StaticScratchState {
+  std::once_flag once;
+  void* dev_ptr = nullptr;
+  cudaError_t err = cudaSuccess;
+};
+StaticScratchState g_scratch_state[MAX_DEVICES];
+
+// Device address of the scratch array on the current device (looked up on the
+// first call per device, with that device current).
+int static_scratch_address(void** out) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return FLYB200_E_UNSUPPORTED;
+  StaticScratchState& st = g_scratch_state[dev];
+  std::call_once(st.once, [&]() {
+    void* p = nullptr;
+    st.err = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (st.err == cudaSuccess) st.dev_ptr = p;
+  });
+  if (st.err != cudaSuccess) return cuda_fail(st.err, "cudaGetSymbolAddress(static scratch)");
+  if (st.dev_ptr == nullptr) return FLYB200_E_CUDA;
+  *out = st.dev_ptr;
+  return FLYB200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -503,6 +541,53 @@ int flyb200_gemm_a8w8_acc(void* acc, const void* a, const void* w_shuf, int M, i
   return gemm_common(acc, a, w_shuf, nullptr, nullptr, nullptr, M, N, K, in_dtype, OUT_RAW32, FLYB200_EPI_NONE,
                      variant_hint, workspace, workspace_bytes, stream);
 }
+
+int flyb200_gemm_a8w8_static_scratch(void* c, const void* a, const void* w_shuf, const float* scale_a,
+                                     const float* scale_b, const void* bias, int M, int N, int K, int in_dtype,
+                                     int out_dtype, int epilogue, int split_k, void* stream) {
+  if (out_dtype != FLYB200_OUT_BF16 && out_dtype != FLYB200_OUT_FP16) return FLYB200_E_BAD_ARG;
+  if (in_dtype < FLYB200_DT_FP8 || in_dtype > FLYB200_DT_BF16 || split_k < 0 || split_k > 255) return FLYB200_E_BAD_ARG;
+  const int eb = elem_bytes_of(in_dtype);
+  if (eb == 1 && (!scale_a || !scale_b)) return FLYB200_E_BAD_ARG;
+  if (eb == 2 && (scale_a || scale_b)) return FLYB200_E_BAD_ARG;
+  if (M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (M > 256) return FLYB200_E_UNSUPPORTED;  // only the small-M kernel has a split-K scratch
+  if (!flyb200_layout_kind(N, K, eb)) return FLYB200_E_UNSUPPORTED;
+  if (M == 0) return FLYB200_OK;
+
+  const int bn = decode_bn_for(M);
+  const int kb = (K * eb) / KBLOCK_BYTES;
+  int split = split_k;
+  if (split == 0) {
+    // automatic: the usual factor, lowered until its partial sums fit the array
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    split = auto_split_k(N, K * eb, st->sms);
+    while (split > 1 && TICKET_BYTES + partial_bytes(split, N, bn) > STATIC_SCRATCH_BYTES) --split;
+  }
+  if (split > kb) split = kb;
+  if (split < 1) split = 1;
+  if (split > 1 && TICKET_BYTES + partial_bytes(split, N, bn) > STATIC_SCRATCH_BYTES) return FLYB200_E_SCRATCH_LIMIT;
+  if ((N + BLOCK_ROWS - 1) / BLOCK_ROWS > static_cast<int>(TICKET_BYTES / sizeof(int))) return FLYB200_E_SCRATCH_LIMIT;
+
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array still holds whatever the previous call left behind.  Only the
+  // per-tile arrival counters have to start at zero (the partial sums are
+  // fully overwritten before they are read), so those are cleared on the same
+  // stream, ahead of the kernel.
+  CUDA_TRY(cudaMemsetAsync(scratch, 0, TICKET_BYTES, s));
+  // small-M kernel, reduction through the workspace, this split, no dependent launch
+  const int hint = (1 << 8) | (REDUCE_WORKSPACE << 12) | (2 << 28) | split;
+  return gemm_common(c, a, w_shuf, scale_a, scale_b, bias, M, N, K, in_dtype,
+                     out_dtype == FLYB200_OUT_FP16 ? OUT_FP16 : OUT_BF16, epilogue, hint, scratch, STATIC_SCRATCH_BYTES,
+                     stream);
+}
+
+size_t flyb200_static_scratch_bytes(void) { return STATIC_SCRATCH_BYTES; }
 
 int flyb200_shuffle_weight(void* dst, const void* src, int N, int K, int elem_bytes, int src_layout, void* stream) {
   if (!dst || !src || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
@@ -574,6 +659,7 @@ const char* flyb200_strerror(int code) {
     case FLYB200_E_UNSUPPORTED: return "unsupported shape or dtype (need N % 16 == 0 and K*elem_bytes % 128 == 0)";
     case FLYB200_E_SMEM_ALIGN: return "shared memory base not 1024-byte aligned";
     case FLYB200_E_WORKSPACE: return "workspace missing or too small for the requested split-K";
+    case FLYB200_E_SCRATCH_LIMIT: return "problem needs more scratch than the library's built-in 8 MiB array holds";
   }
   return "unknown error";
 }

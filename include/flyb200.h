@@ -28,6 +28,7 @@ extern "C" {
 #define FLYB200_E_UNSUPPORTED 5 /* shape or dtype outside what the kernels cover */
 #define FLYB200_E_SMEM_ALIGN 6  /* device reported misaligned shared memory (read via flyb200_read_status) */
 #define FLYB200_E_WORKSPACE 7   /* workspace missing or too small for the requested split */
+#define FLYB200_E_SCRATCH_LIMIT 8 /* flyb200_gemm_a8w8_static_scratch: needs more than the built-in array */
 
 /* in_dtype: element type of A and of the preshuffled weights
  * (compile_preshuffle_gemm(in_dtype=...), kernels/gemm/preshuffle_gemm.py:117,129-130) */
@@ -99,6 +100,36 @@ int flyb200_gemm_a8w8(void* c, const void* a, const void* w_shuf, const float* s
  * bit-exact.  Same kernels, same dispatch as flyb200_gemm_a8w8. */
 int flyb200_gemm_a8w8_acc(void* acc, const void* a, const void* w_shuf, int M, int N, int K, int in_dtype,
                           int variant_hint, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The small-M GEMM (M <= 256) for callers that cannot hand the library a
+ * workspace because they are not able to allocate device memory at the point
+ * of the call: a plug-in running inside a host application that has already
+ * claimed the device's memory for its own pool, code on a latency-critical
+ * path where cudaMalloc's implicit device-wide synchronisation is not
+ * acceptable, or a component whose allocator simply is not reachable from
+ * where the GEMM is issued.  It has no counterpart in the reference.
+ *
+ * Same arguments and result as flyb200_gemm_a8w8, except that the split-K
+ * partial sums go to an 8 MiB array that is part of the library's device image
+ * (flyb200_static_scratch_bytes(); every GPU that has loaded the library holds
+ * it until the process exits).  The call itself performs no cudaMalloc/cudaFree
+ * and uses no allocating library routine.
+ *   split_k  number of K splits, 0 = choose automatically (the largest useful
+ *            factor whose partial sums fit).  An explicit factor whose partial
+ *            sums (split_k * ceil(N/128) * BN * 512 bytes, BN = M rounded up
+ *            to 16/32/64/128/256, plus 16 KiB of counters) exceed the array is
+ *            rejected with FLYB200_E_SCRATCH_LIMIT; nothing is launched.
+ * The first call on each device looks up the array's device address; make that
+ * first call with the device current and before starting any stream capture.
+ * All calls on a device share the one array, which keeps the previous call's
+ * contents: the counters that must start at zero are cleared on `stream` before
+ * the kernel runs, and two calls that may overlap on the GPU (different
+ * streams, or different host threads on the same device) race on it and must
+ * be serialised by the caller. */
+int flyb200_gemm_a8w8_static_scratch(void* c, const void* a, const void* w_shuf, const float* scale_a,
+                                     const float* scale_b, const void* bias, int M, int N, int K, int in_dtype,
+                                     int out_dtype, int epilogue, int split_k, void* stream);
+size_t flyb200_static_scratch_bytes(void);
 
 /* Weight preshuffle: dst = B200 image of the [N, K] matrix src.  Replaces
  * shuffle_weight (tests/utils.py:76-96) and the layout it encodes
