@@ -261,3 +261,83 @@ def test_m_zero_and_tensor_checks(dev):
     fn(c.view(-1), a, b, torch.nn.Parameter(sa, requires_grad=False), sb, bias, 16, 64, None)  # Parameter accepted
     torch.cuda.synchronize()
     assert bool((c == 0).all())
+
+
+# --- fp16 / bf16 inputs (no scales) and the fused bias / activation epilogues
+#     (tests/kernels/test_preshuffle_gemm.py:116 dtype list, :889-980 epilogue test)
+
+TORCH_DT = {"fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+def run_gemm_generic(dev, a, b, sa, sb, bias, m, n, k, in_dtype, out_dtype="bf16", epilogue="none", hint=0):
+    fn = compile_preshuffle_gemm(
+        N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype=in_dtype, out_dtype=out_dtype, epilogue=epilogue,
+        variant_hint=hint,
+    )  # fmt: skip
+    odt = TORCH_DT[out_dtype]
+    c_alloc = torch.full((m + 8, n), SENTINEL, dtype=odt, device=dev)
+    empty_f32 = torch.empty(0, dtype=torch.float32, device=dev)
+    args = (
+        c_alloc.view(-1),
+        as_i8(a.to(dev)).contiguous().view(-1),
+        as_i8(shuffle_weight(b.to(dev))).contiguous().view(-1),
+        sa.to(dev) if sa is not None else empty_f32,
+        sb.to(dev) if sb is not None else empty_f32,
+        bias.to(dev) if bias is not None else torch.empty(0, dtype=odt, device=dev),
+        m,
+        n,
+        torch.cuda.current_stream(),
+    )
+    flyc.compile(fn, *args)(*args)
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert int((c_alloc[m:] != SENTINEL).sum().item()) == 0
+    return c_alloc[:m].float().cpu()
+
+
+@pytest.mark.parametrize("in_dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("m,n,k,hint", [(16, 5120, 8192, 0), (33, 1024, 2048, 0), (513, 1024, 2048, 0), (513, 1024, 2048, ROWS2), (200, 528, 1088, DEC | WS | 3)])
+def test_half_precision_inputs(dev, in_dtype, m, n, k, hint):
+    g = torch.Generator().manual_seed(m + n)
+    a = torch.randn(m, k, generator=g).to(TORCH_DT[in_dtype])
+    b = torch.randn(n, k, generator=g).to(TORCH_DT[in_dtype])
+    got = run_gemm_generic(dev, a, b, None, None, None, m, n, k, in_dtype, hint=hint)
+    ref = oracle.run_torch(a, b, None, None)
+    assert oracle.strict_mismatches(got, ref, RTOL, ATOL) == 0
+
+
+@pytest.mark.parametrize("epilogue", ["bias", "bias_relu", "bias_silu", "bias_gelu"])
+@pytest.mark.parametrize("in_dtype,m", [("bf16", 16), ("fp8", 16), ("fp8", 300), ("int8", 40)])
+def test_fused_epilogues(dev, epilogue, in_dtype, m):
+    n, k = 5120, 2048
+    g = torch.Generator().manual_seed(7)
+    bias = torch.randn(n, generator=g).to(torch.bfloat16)
+    if in_dtype == "bf16":
+        a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        b = torch.randn(n, k, generator=g).to(torch.bfloat16)
+        sa = sb = None
+        acc = a.float() @ b.float().T
+    else:
+        a, b, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=70 + m)
+        acc = a.float() @ b.float().T
+    got = run_gemm_generic(dev, a, b, sa, sb, bias, m, n, k, in_dtype, epilogue=epilogue)
+    ref = oracle.epilogue(acc, sa, sb, bias, epilogue, out_dtype=torch.float32)
+    assert not torch.isnan(got).any() and not torch.isinf(got).any()
+    assert oracle.strict_mismatches(got, ref, RTOL, ATOL) == 0
+    # the reference's own looser bar (tests/kernels/test_preshuffle_gemm.py:967-973)
+    assert torch.allclose(got, ref.to(torch.bfloat16).float(), atol=2.0, rtol=0.05)
+
+
+@pytest.mark.parametrize("in_dtype,m", [("fp8", 24), ("int8", 400), ("fp16", 24)])
+def test_fp16_output(dev, in_dtype, m):
+    n, k = 1024, 1024
+    if in_dtype == "fp16":
+        g = torch.Generator().manual_seed(3)
+        a = (torch.randn(m, k, generator=g) * 0.25).to(torch.float16)
+        b = (torch.randn(n, k, generator=g) * 0.25).to(torch.float16)
+        sa = sb = None
+    else:
+        a, b, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=m)
+    got = run_gemm_generic(dev, a, b, sa, sb, None, m, n, k, in_dtype, out_dtype="fp16")
+    ref = oracle.run_torch(a, b, sa, sb)
+    assert oracle.strict_mismatches(got, ref, RTOL, ATOL) == 0
