@@ -278,6 +278,7 @@ def main():
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the single-GPU decode/prefill side measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fused", action="store_true", help="skip the fused GEMM + all-gather measurement (N > 1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     m, n, k, in_dtype, wscale, seed = WORKLOADS[args.workload]
@@ -404,6 +405,31 @@ def main():
         gathered = {"ms_per_step": g_ms, "tflops": flops_step / (g_ms * 1e-3) / 1e12,
                     "what": "GEMM shard + NCCL all-gather of bf16 shards (shard-major result)"}
 
+    # ---- optional: the same full output from the GEMM fused with the exchange
+    #      (tiles TMA-stored straight into every rank's full-width buffer)
+    fused = None
+    if world > 1 and not args.no_fused:
+        try:
+            op.enable_fused_gather(m_max=m)
+            for _ in range(2):
+                op.forward_full_fused(a_q, sa)
+            barrier()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(stream)
+            reps = max(3, min(args.steps, 10))
+            for _ in range(reps):
+                op.forward_full_fused(a_q, sa)
+            f1.record(stream)
+            barrier()
+            t = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            f_ms = float(t.item()) / reps
+            fused = {"ms_per_step": f_ms, "tflops": flops_step / (f_ms * 1e-3) / 1e12,
+                     "what": "one GEMM kernel per rank whose epilogue TMA-stores every tile into all ranks' "
+                             "full-width buffers (peer memory), then a one-element NCCL all-reduce as barrier"}
+        except Exception as e:  # symmetric memory unavailable: report, keep the main numbers
+            fused = {"unavailable": repr(e)[:200]}
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -496,6 +522,8 @@ def main():
     }
     if gathered:
         line["with_allgather"] = gathered
+    if fused:
+        line["with_fused_allgather"] = fused
     if extras:
         line["extras"] = extras
     print(json.dumps(line), flush=True)

@@ -37,6 +37,10 @@ SIGNATURES = {
     "flyb200_gemm_a8w8_acc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "flyb200_gemm_a8w8_static_scratch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "flyb200_static_scratch_bytes": (_sz, []),
+    "flyb200_gemm_a8w8_scatter": (
+        _i,
+        [ctypes.POINTER(_vp), _i, _i, ctypes.c_longlong, ctypes.c_longlong, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    ),
     "flyb200_shuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_unshuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "flyb200_layout_kind": (_i, [_i, _i, _i]),

@@ -136,6 +136,60 @@ class ColumnParallelGemm:
                     self.spec.n_local, stream if stream is not None else torch.cuda.current_stream())
         return out
 
+    # ---- GEMM fused with the all-gather of its output shards -------------------
+    def enable_fused_gather(self, m_max: int) -> None:
+        """Allocate (once) two full-width [m_max, N] output buffers in symmetric
+        memory, i.e. mapped into every rank of the group, for
+        :meth:`forward_full_fused`.  Collective: every rank must call it."""
+        import ctypes
+        import os
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if self.world > 8:
+            raise ValueError("the fused gather writes to at most 8 output buffers")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only
+        dev = self.w_shuf.device
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._sym = []
+        for _ in range(2):
+            buf = symm_mem.empty((m_max, self.N), dtype=self._bias.dtype, device=dev)
+            hdl = symm_mem.rendezvous(buf, group)
+            ptrs = (ctypes.c_void_p * self.world)(*[int(hdl.buffer_ptrs[r]) for r in range(self.world)])
+            self._sym.append((buf, hdl, ptrs))
+        self._flip = 0
+        self._flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._m_max = m_max
+
+    def forward_full_fused(self, a_q: torch.Tensor, sa: torch.Tensor, stream=None) -> torch.Tensor:
+        """Full [M, N] output on every rank from ONE GEMM kernel per rank: each
+        output tile is TMA-stored into the full-width buffer of every rank
+        (columns [rank*N/w, (rank+1)*N/w)), so the exchange over NVLink overlaps
+        the math; a one-element NCCL all-reduce then orders the stores against
+        the readers.  The two output buffers alternate between calls, so the
+        result of call i stays valid until call i+2 is issued."""
+        from . import _lib
+
+        m = a_q.shape[0]
+        if m > self._m_max:
+            raise ValueError(f"M={m} exceeds the buffers allocated by enable_fused_gather({self._m_max})")
+        buf, _hdl, ptrs = self._sym[self._flip]
+        self._flip ^= 1
+        lib = _lib.load()
+        s = stream if stream is not None else torch.cuda.current_stream()
+        a = a_q.view(torch.int8) if a_q.element_size() == 1 else a_q
+        eight = self.in_dtype in ("fp8", "int8")
+        rc = lib.flyb200_gemm_a8w8_scatter(
+            ptrs, self.world, self.rank, self.N, self.spec.n0,
+            a.data_ptr(), self.w_shuf.data_ptr(), sa.data_ptr() if eight else None, self.sb.data_ptr() if eight else None,
+            None, m, self.spec.n_local, self.K, _lib.IN_DTYPES[self.in_dtype], _lib.OUT_DTYPES[self.out_dtype],
+            _lib.EPI_NONE, 0, s.cuda_stream,
+        )  # fmt: skip
+        _lib.check(rc, "gemm_a8w8_scatter")
+        if self.world > 1:
+            dist.all_reduce(self._flag, group=self.group)  # all ranks' stores have landed before anyone reads
+        return buf[:m]
+
     def forward_full(self, a_q, sa, row_major: bool = True):
         """Full [M, N] on every rank: local shard, then an NCCL all-gather."""
         local = self.forward(a_q, sa)

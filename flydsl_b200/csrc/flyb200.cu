@@ -190,6 +190,43 @@ int launch_rows2(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorM
   return FLYB200_OK;
 }
 
+// Output window [rows, cols] of a wider row-major matrix (row pitch given in
+// elements), 2-byte elements, 64 x 32 boxes with the 128-byte swizzle.
+int make_window_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t cols, uint64_t rows,
+                    uint64_t pitch_elems) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
+    return FLYB200_E_CUDA;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_elems * 2};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled (output window) failed with CUresult %d",
+             static_cast<int>(r));
+    return FLYB200_E_CUDA;
+  }
+  return FLYB200_OK;
+}
+
+template <int KIND, int OUTMODE>
+int launch_rows_scatter(const CUtensorMap& tmA, const OutputMaps& outs, const GemmParams& p, int sms, cudaStream_t s) {
+  using L = RowsSmem<ROWS_BN, ROWS_STAGES>;
+  static std::atomic<uint64_t> done{0};
+  auto kernel = gemm_rows_scatter_kernel<KIND, ROWS_BN, ROWS_STAGES, OUTMODE>;
+  int rc = ensure_smem(kernel, L::TOTAL, done);
+  if (rc) return rc;
+  const int tiles = ((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * ((p.N + ROWS_BN - 1) / ROWS_BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, NUM_THREADS, L::TOTAL, s>>>(tmA, outs, p);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
 constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 
 inline int default_decode_stages(int bn) { return bn <= 32 ? 8 : (bn <= 128 ? 6 : 4); }
@@ -588,6 +625,84 @@ int flyb200_gemm_a8w8_static_scratch(void* c, const void* a, const void* w_shuf,
 }
 
 size_t flyb200_static_scratch_bytes(void) { return STATIC_SCRATCH_BYTES; }
+
+int flyb200_gemm_a8w8_scatter(void* const* c_bufs, int n_bufs, int first_buf, long long c_pitch, long long c_col_offset,
+                              const void* a, const void* w_shuf, const float* scale_a, const float* scale_b,
+                              const void* bias, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
+                              int variant_hint, void* stream) {
+  if (!c_bufs || n_bufs < 1 || n_bufs > MAX_DESTINATIONS || first_buf < 0 || first_buf >= n_bufs) return FLYB200_E_BAD_ARG;
+  if (out_dtype != FLYB200_OUT_BF16 && out_dtype != FLYB200_OUT_FP16) return FLYB200_E_BAD_ARG;
+  if (in_dtype < FLYB200_DT_FP8 || in_dtype > FLYB200_DT_BF16) return FLYB200_E_BAD_ARG;
+  if (epilogue < FLYB200_EPI_NONE || epilogue > FLYB200_EPI_BIAS_GELU) return FLYB200_E_BAD_ARG;
+  if (epilogue != FLYB200_EPI_NONE && !bias) return FLYB200_E_BAD_ARG;
+  const int eb = elem_bytes_of(in_dtype);
+  if (eb == 1 && (!scale_a || !scale_b)) return FLYB200_E_BAD_ARG;
+  if (eb == 2 && (scale_a || scale_b)) return FLYB200_E_BAD_ARG;
+  if (!a || !w_shuf || M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (c_col_offset < 0 || c_pitch < c_col_offset + N || (c_pitch % 8) != 0 || (c_col_offset % 8) != 0)
+    return FLYB200_E_BAD_ARG;  // window inside the row, 16-byte aligned rows and window start
+  if (!flyb200_layout_kind(N, K, eb)) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(a) || !aligned16(w_shuf)) return FLYB200_E_BAD_ALIGN;
+  for (int d = 0; d < n_bufs; ++d) {
+    if (!c_bufs[d]) return FLYB200_E_BAD_ARG;
+    if (!aligned16(c_bufs[d])) return FLYB200_E_BAD_ALIGN;
+  }
+  if (M == 0) return FLYB200_OK;
+
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc) return rc;
+  const int K_bytes = K * eb;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.w = static_cast<const uint8_t*>(w_shuf);
+  p.sa = scale_a;
+  p.sb = scale_b;
+  p.bias = bias;
+  p.c = c_bufs[0];
+  p.M = M;
+  p.N = N;
+  p.K_bytes = K_bytes;
+  p.epilogue = epilogue;
+  p.group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : 16;
+  p.split_k = 1;
+  p.kb_per_split = K_bytes / KBLOCK_BYTES;
+  p.n_dst = n_bufs;
+  p.dst_first = first_buf;
+  p.status = st->status;
+
+  CUtensorMap tmA;
+  rc = make_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, static_cast<uint64_t>(K_bytes), static_cast<uint64_t>(M),
+                KBLOCK_BYTES, BLOCK_ROWS);
+  if (rc) return rc;
+  OutputMaps outs;
+  memset(&outs, 0, sizeof(outs));
+  const CUtensorMapDataType odt =
+      out_dtype == FLYB200_OUT_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  for (int d = 0; d < n_bufs; ++d) {
+    const uint8_t* base = static_cast<const uint8_t*>(c_bufs[d]) + static_cast<size_t>(c_col_offset) * 2;
+    rc = make_window_map(&outs.m[d], odt, base, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                         static_cast<uint64_t>(c_pitch));
+    if (rc) return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool f16out = out_dtype == FLYB200_OUT_FP16;
+  switch (in_dtype) {
+    case FLYB200_DT_FP8:
+      return f16out ? launch_rows_scatter<KIND_F8, OUT_FP16>(tmA, outs, p, st->sms, s)
+                    : launch_rows_scatter<KIND_F8, OUT_BF16>(tmA, outs, p, st->sms, s);
+    case FLYB200_DT_INT8:
+      return f16out ? launch_rows_scatter<KIND_I8, OUT_FP16>(tmA, outs, p, st->sms, s)
+                    : launch_rows_scatter<KIND_I8, OUT_BF16>(tmA, outs, p, st->sms, s);
+    case FLYB200_DT_FP16:
+      return f16out ? launch_rows_scatter<KIND_F16, OUT_FP16>(tmA, outs, p, st->sms, s)
+                    : launch_rows_scatter<KIND_F16, OUT_BF16>(tmA, outs, p, st->sms, s);
+    case FLYB200_DT_BF16:
+      return f16out ? launch_rows_scatter<KIND_BF16, OUT_FP16>(tmA, outs, p, st->sms, s)
+                    : launch_rows_scatter<KIND_BF16, OUT_BF16>(tmA, outs, p, st->sms, s);
+  }
+  return FLYB200_E_BAD_ARG;
+}
 
 int flyb200_shuffle_weight(void* dst, const void* src, int N, int K, int elem_bytes, int src_layout, void* stream) {
   if (!dst || !src || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;

@@ -49,6 +49,8 @@ struct GemmParams {
   int pdl;               // decode kernel: launched with programmatic stream serialisation
   float* ws_partials;    // decode kernel, REDUCE_WORKSPACE
   int* ws_tickets;       // decode kernel, REDUCE_WORKSPACE (zero before first use; self-resetting)
+  int n_dst;             // scatter kernel: number of output buffers
+  int dst_first;         // scatter kernel: buffer stored to first
   int* status;           // device status word (first failure wins)
 };
 
@@ -135,9 +137,13 @@ __device__ __forceinline__ float load_bias(const void* bias, int col) {
 // registers -> scale / bias / activation -> bf16|fp16 -> 128-byte-swizzled
 // staging buffer -> TMA store (clipped at M and N), or raw 32-bit stores.
 // `release_tmem()` is called once, as soon as the accumulator has been read.
+// `tmC` points to `n_dst` tensor maps: the staged chunk is stored through each
+// of them (the caller's own output, or the same window of the output buffers of
+// several GPUs), starting with map `dst_first` so that ranks do not all hit the
+// same peer at the same time.
 template <int KIND, int BN, int OUTMODE, typename ReleaseFn>
-__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* tmC, uint32_t t_row, int m0,
-                                                   int n0, int lane, uint32_t stage_c, int& cbuf,
+__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* tmC, int n_dst, int dst_first,
+                                                   uint32_t t_row, int m0, int n0, int lane, uint32_t stage_c, int& cbuf,
                                                    ReleaseFn release_tmem) {
   using KT = KindTraits<KIND>;
   constexpr int C_BUF = 32 * 128;
@@ -209,7 +215,13 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CU
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        if (m0 < p.M && (n0 + c0) < p.N) tma_store_2d(tmC, stage_c + cbuf * C_BUF, n0 + c0, m0);
+        if (m0 < p.M && (n0 + c0) < p.N) {
+          for (int d = 0; d < n_dst; ++d) {
+            int which = dst_first + d;
+            if (which >= n_dst) which -= n_dst;
+            tma_store_2d(tmC + which, stage_c + cbuf * C_BUF, n0 + c0, m0);
+          }
+        }
         bulk_commit_group();
       }
       cbuf ^= 1;
@@ -233,10 +245,17 @@ struct RowsSmem {
   static constexpr int TOTAL = OFF_MISC + 16;
 };
 
+constexpr int MAX_DESTINATIONS = 8;
+struct OutputMaps {
+  CUtensorMap m[MAX_DESTINATIONS];
+};
+
+// Body shared by the two entry kernels below: `tmC` points to `n_dst` output
+// tensor maps (kernel parameters of the caller).
 template <int KIND, int BN, int STAGES, int OUTMODE>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_rows_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC,
-                 const GemmParams p) {
+__device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUtensorMap* tmC_ptr, int n_dst,
+                                               int dst_first, const GemmParams& p) {
+  const CUtensorMap& tmC = *tmC_ptr;
   using L = RowsSmem<BN, STAGES>;
   using KT = KindTraits<KIND>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -412,7 +431,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      epilogue_warp_tile<KIND, BN, OUTMODE>(p, &tmC, t_row, m0, n0, lane, stage_c, cbuf, [&]() {
+      epilogue_warp_tile<KIND, BN, OUTMODE>(p, tmC_ptr, n_dst, dst_first, t_row, m0, n0, lane, stage_c, cbuf, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
@@ -430,6 +449,25 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// One output buffer (the regular GEMM).
+template <int KIND, int BN, int STAGES, int OUTMODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_rows_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC,
+                 const GemmParams p) {
+  gemm_rows_body<KIND, BN, STAGES, OUTMODE>(tmA, &tmC, 1, 0, p);
+}
+
+// Every output tile is stored into the same window of up to eight buffers, e.g.
+// the full-width output of each GPU of a column-parallel group (peer-mapped
+// memory; plain TMA stores, per CTA, no multicast): the all-gather of the
+// shards happens tile by tile inside the GEMM.
+template <int KIND, int BN, int STAGES, int OUTMODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_rows_scatter_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ OutputMaps outs,
+                         const GemmParams p) {
+  gemm_rows_body<KIND, BN, STAGES, OUTMODE>(tmA, outs.m, p.n_dst, p.dst_first, p);
 }
 
 }  // namespace flyb200

@@ -131,6 +131,28 @@ int flyb200_gemm_a8w8_static_scratch(void* c, const void* a, const void* w_shuf,
                                      int out_dtype, int epilogue, int split_k, void* stream);
 size_t flyb200_static_scratch_bytes(void);
 
+/* The large-M GEMM with its output tiles stored into the same window of several
+ * buffers at once: window = columns [c_col_offset, c_col_offset + N) of row-major
+ * matrices with c_pitch elements per row.  This is the column-parallel form of
+ * the operator fused with the all-gather of its output shards: rank r of a group
+ * of n_bufs GPUs passes the (peer-mapped) full-width output buffers of all ranks
+ * and c_col_offset = r * N, and every 128 x 256 tile leaves the kernel through
+ * one TMA store per buffer, so the transfer over NVLink overlaps the math tile
+ * by tile.  Plain per-CTA stores; no multicast, no loads from peer memory.  The
+ * reference has no multi-GPU form of this operator (its only matching
+ * collective is the all_gather_into_tensor fallback of
+ * kernels/comm/custom_all_reduce.py:929-938).
+ *   c_bufs     host array of n_bufs (1..8) device pointers, each 16-byte aligned
+ *              and writable from the current device
+ *   first_buf  index of the buffer stored to first (use the caller's rank)
+ *   c_pitch, c_col_offset  in elements; both multiples of 8
+ * The caller orders the kernel against readers on other GPUs (a barrier across
+ * the group after the call) and against the next overwrite of the buffers. */
+int flyb200_gemm_a8w8_scatter(void* const* c_bufs, int n_bufs, int first_buf, long long c_pitch, long long c_col_offset,
+                              const void* a, const void* w_shuf, const float* scale_a, const float* scale_b,
+                              const void* bias, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
+                              int variant_hint, void* stream);
+
 /* Weight preshuffle: dst = B200 image of the [N, K] matrix src.  Replaces
  * shuffle_weight (tests/utils.py:76-96) and the layout it encodes
  * (kernels/gemm/preshuffle_gemm.py:765-780).  dst and src must not overlap;
