@@ -58,6 +58,23 @@ __device__ __forceinline__ uint32_t ld_dsmem(uint32_t addr) {
   asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
   return v;
 }
+__device__ __forceinline__ uint4 ld_dsmem_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+// sum of two raw 32-bit accumulators (int32 or fp32 bit patterns)
+template <bool IS_INT>
+__device__ __forceinline__ uint32_t add_raw(uint32_t a, uint32_t b) {
+  if constexpr (IS_INT) {
+    return static_cast<uint32_t>(static_cast<int32_t>(a) + static_cast<int32_t>(b));
+  } else {
+    return __float_as_uint(__uint_as_float(a) + __uint_as_float(b));
+  }
+}
 __device__ __forceinline__ void st_smem(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
@@ -332,42 +349,72 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     tc_fence_before();
     cluster_sync_all();
     if (warp >= 2 && ok) {
+      // Reduce-scatter over the cluster: this CTA owns a slice of the tokens.
+      // A warp takes one token at a time and each lane four consecutive
+      // channels, so every peer read is one 16-byte load and every output row
+      // leaves as one 256-byte (bf16) run per warp.  Splits are summed in the
+      // fixed order 0..S-1.
       const uint32_t rank = cluster_ctarank();
       const int S = p.split_k;
       const int m_lim = min(p.M, BN);
       const int chunk = (m_lim + S - 1) / S;
       const int m_begin = static_cast<int>(rank) * chunk;
       const int m_end = min(m_lim, m_begin + chunk);
-      uint32_t peer[MAX_CLUSTER_SPLIT];
+      const int ew = warp - 2;
+      const int ch4 = lane * 4;
+      const int n4 = n0 + ch4;
+      const bool col_ok = n4 < p.N;  // N is a multiple of 4: the four channels are in or out together
+      float sb4[4] = {0.f, 0.f, 0.f, 0.f}, bias4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (col_ok) {
 #pragma unroll
-      for (int s = 0; s < MAX_CLUSTER_SPLIT; ++s)
-        peer[s] = map_to_cta(red_base + static_cast<uint32_t>(ch_local * 4), static_cast<uint32_t>(s < S ? s : 0));
-      constexpr int U = 4;
+        for (int e = 0; e < 4; ++e) {
+          if (scaled) sb4[e] = __ldg(p.sb + n4 + e);
+          if (p.epilogue != EPI_NONE) bias4[e] = load_bias<OUTMODE>(p.bias, n4 + e);
+        }
+      }
+      const uint32_t red_mine = red_base + static_cast<uint32_t>(ch4 * 4);
+      const uint32_t peer0 = map_to_cta(red_mine, 0);
+      constexpr int U = 8;  // tokens in flight per warp
 #pragma unroll 1
-      for (int m0 = m_begin; m0 < m_end; m0 += U) {
-        uint32_t v[MAX_CLUSTER_SPLIT][U];
+      for (int mb = m_begin + ew; mb < m_end; mb += 4 * U) {
+        uint4 acc[U];
 #pragma unroll
-        for (int s = 0; s < MAX_CLUSTER_SPLIT; ++s) {
-          if (s < S) {
+        for (int j = 0; j < U; ++j) {
+          const int m = mb + 4 * j;
+          acc[j] = (m < m_end) ? ld_dsmem_v4(peer0 + static_cast<uint32_t>(m * BLOCK_ROWS * 4)) : make_uint4(0, 0, 0, 0);
+        }
+        for (int s = 1; s < S; ++s) {
+          const uint32_t peer_s = map_to_cta(red_mine, static_cast<uint32_t>(s));
+          uint4 v[U];
 #pragma unroll
-            for (int j = 0; j < U; ++j)
-              v[s][j] = (m0 + j < m_end) ? ld_dsmem(peer[s] + static_cast<uint32_t>((m0 + j) * BLOCK_ROWS * 4)) : 0u;
+          for (int j = 0; j < U; ++j) {
+            const int m = mb + 4 * j;
+            v[j] = (m < m_end) ? ld_dsmem_v4(peer_s + static_cast<uint32_t>(m * BLOCK_ROWS * 4)) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int j = 0; j < U; ++j) {
+            acc[j].x = add_raw<KT::is_int>(acc[j].x, v[j].x);
+            acc[j].y = add_raw<KT::is_int>(acc[j].y, v[j].y);
+            acc[j].z = add_raw<KT::is_int>(acc[j].z, v[j].z);
+            acc[j].w = add_raw<KT::is_int>(acc[j].w, v[j].w);
           }
         }
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-          uint32_t acc = v[0][j];
-#pragma unroll
-          for (int s = 1; s < MAX_CLUSTER_SPLIT; ++s) {
-            if (s < S) {
-              if constexpr (KT::is_int) {
-                acc = static_cast<uint32_t>(static_cast<int32_t>(acc) + static_cast<int32_t>(v[s][j]));
-              } else {
-                acc = __float_as_uint(__uint_as_float(acc) + __uint_as_float(v[s][j]));
-              }
+          const int m = mb + 4 * j;
+          if (m < m_end && col_ok) {
+            if constexpr (OUTMODE == OUT_RAW32) {
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(p.c) + static_cast<size_t>(m) * p.N + n4) = acc[j];
+            } else {
+              const float sa_v = sa_s[m];
+              const float v0 = epilogue_value<KT::is_int>(acc[j].x, sa_v, sb4[0], bias4[0], p.epilogue, scaled);
+              const float v1 = epilogue_value<KT::is_int>(acc[j].y, sa_v, sb4[1], bias4[1], p.epilogue, scaled);
+              const float v2 = epilogue_value<KT::is_int>(acc[j].z, sa_v, sb4[2], bias4[2], p.epilogue, scaled);
+              const float v3 = epilogue_value<KT::is_int>(acc[j].w, sa_v, sb4[3], bias4[3], p.epilogue, scaled);
+              *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.c) + static_cast<size_t>(m) * p.N + n4) =
+                  make_uint2(pack2<OUTMODE>(v0, v1), pack2<OUTMODE>(v2, v3));
             }
           }
-          if (m0 + j < m_end) emit(m0 + j, acc);
         }
       }
     }

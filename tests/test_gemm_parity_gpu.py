@@ -296,7 +296,7 @@ def run_gemm_generic(dev, a, b, sa, sb, bias, m, n, k, in_dtype, out_dtype="bf16
 
 
 @pytest.mark.parametrize("in_dtype", ["fp16", "bf16"])
-@pytest.mark.parametrize("m,n,k,hint", [(16, 5120, 8192, 0), (33, 1024, 2048, 0), (513, 1024, 2048, 0), (513, 1024, 2048, ROWS2), (200, 528, 1088, DEC | WS | 3)])
+@pytest.mark.parametrize("m,n,k,hint", [(16, 5120, 8192, 0), (33, 1024, 2048, 0), (513, 1024, 2048, 0), (513, 1024, 2048, ROWS2), (200, 528, 1280, DEC | WS | 3)])
 def test_half_precision_inputs(dev, in_dtype, m, n, k, hint):
     g = torch.Generator().manual_seed(m + n)
     a = torch.randn(m, k, generator=g).to(TORCH_DT[in_dtype])
