@@ -41,6 +41,7 @@ SIGNATURES = {
         _i,
         [ctypes.POINTER(_vp), _i, _i, ctypes.c_longlong, ctypes.c_longlong, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     ),
+    "flyb200_pertoken_quant": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_shuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_unshuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "flyb200_layout_kind": (_i, [_i, _i, _i]),

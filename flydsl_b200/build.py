@@ -16,7 +16,7 @@ import sys
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libflyb200.so")
 SOURCES = ["flyb200.cu"]
-HEADERS = ["ptx.cuh", "gemm_kernels.cuh", "decode_kernel.cuh", "rows2_kernel.cuh", os.path.join("..", "..", "include", "flyb200.h")]
+HEADERS = ["ptx.cuh", "gemm_kernels.cuh", "decode_kernel.cuh", "rows2_kernel.cuh", "quant_kernel.cuh", os.path.join("..", "..", "include", "flyb200.h")]
 
 NVCC_FLAGS = [
     "-gencode",

@@ -3,6 +3,7 @@
 // synchronisation and no memcpy on the launch path.
 #include "../../include/flyb200.h"
 #include "decode_kernel.cuh"
+#include "quant_kernel.cuh"
 #include "rows2_kernel.cuh"
 
 #include <atomic>
@@ -723,6 +724,36 @@ int flyb200_unshuffle_weight(void* dst, const void* src, int N, int K, int elem_
   const size_t bytes = static_cast<size_t>(N) * K * elem_bytes;
   if (ranges_overlap(dst, src, bytes)) return FLYB200_E_BAD_ARG;
   return launch_shuffle<FLYB200_SRC_ROW_MAJOR, true>(dst, src, N, K * elem_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int flyb200_pertoken_quant(void* y, float* scale, const void* x, int rows, int K, int x_dtype, int quant_dtype,
+                           void* stream) {
+  if (!y || !scale || !x || rows < 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (x_dtype < QX_F32 || x_dtype > QX_BF16) return FLYB200_E_BAD_ARG;
+  if (quant_dtype != FLYB200_DT_FP8 && quant_dtype != FLYB200_DT_INT8) return FLYB200_E_BAD_ARG;
+  const int vec = x_dtype == QX_F32 ? 4 : 8;
+  if (K % vec != 0) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 7u) != 0) return FLYB200_E_BAD_ALIGN;
+  if (rows == 0) return FLYB200_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = rows < 148 * 16 ? rows : 148 * 16;
+  uint8_t* yo = static_cast<uint8_t*>(y);
+  const bool fp8 = quant_dtype == FLYB200_DT_FP8;
+  if (x_dtype == QX_F32) {
+    const float* xi = static_cast<const float*>(x);
+    if (fp8) pertoken_quant_kernel<float, true><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+    else pertoken_quant_kernel<float, false><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+  } else if (x_dtype == QX_F16) {
+    const __half* xi = static_cast<const __half*>(x);
+    if (fp8) pertoken_quant_kernel<__half, true><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+    else pertoken_quant_kernel<__half, false><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+  } else {
+    const __nv_bfloat16* xi = static_cast<const __nv_bfloat16*>(x);
+    if (fp8) pertoken_quant_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+    else pertoken_quant_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
 }
 
 int flyb200_layout_kind(int N, int K, int elem_bytes) {

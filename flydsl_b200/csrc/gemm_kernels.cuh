@@ -52,6 +52,9 @@ struct GemmParams {
   int n_dst;             // scatter kernel: number of output buffers
   int dst_first;         // scatter kernel: buffer stored to first
   int* status;           // device status word (first failure wins)
+#ifdef FLYB200_PROFILE
+  unsigned long long* prof;  // [8] cycle counters (profiling builds only)
+#endif
 };
 
 template <int KIND>
@@ -256,6 +259,10 @@ template <int KIND, int BN, int STAGES, int OUTMODE>
 __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUtensorMap* tmC_ptr, int n_dst,
                                                int dst_first, const GemmParams& p) {
   const CUtensorMap& tmC = *tmC_ptr;
+#ifdef FLYB200_PROFILE
+  long long prof_wait[4] = {0, 0, 0, 0};  // producer:empty, mma:tempty, mma:full, epilogue:tfull
+  const long long prof_begin = clock64();
+#endif
   using L = RowsSmem<BN, STAGES>;
   using KT = KindTraits<KIND>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -335,7 +342,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
         const uint32_t w_rows = static_cast<uint32_t>(min(BN, p.N - n0));
         const uint32_t w_bytes = w_rows * KBLOCK_BYTES;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag FLYB200_PROF_ARG(&prof_wait[0]))) {
             report_failure(p.status, ST_TIMEOUT, abort_flag);
             ok = false;
             break;
@@ -378,14 +385,14 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag FLYB200_PROF_ARG(&prof_wait[1]))) {
           report_failure(p.status, ST_TIMEOUT, abort_flag);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag FLYB200_PROF_ARG(&prof_wait[2]))) {
             report_failure(p.status, ST_TIMEOUT, abort_flag);
             ok = false;
             break;
@@ -424,7 +431,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
       tile_coords(t, m_blk, n_blk);
       const int m0 = m_blk * BLOCK_ROWS + q * 32;
       const int n0 = n_blk * BN;
-      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag FLYB200_PROF_ARG(&prof_wait[3]))) {
         if (lane == 0) report_failure(p.status, ST_TIMEOUT, abort_flag);
         ok = false;
         break;
@@ -442,6 +449,21 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
     if (lane == 0) bulk_wait_group<0>();
   }
 
+#ifdef FLYB200_PROFILE
+  if (lane == 0) {
+    const long long total = clock64() - prof_begin;
+    if (warp == 0) {
+      atomicAdd(p.prof + 0, static_cast<unsigned long long>(prof_wait[0]));
+      atomicAdd(p.prof + 4, static_cast<unsigned long long>(total));
+    } else if (warp == 1) {
+      atomicAdd(p.prof + 1, static_cast<unsigned long long>(prof_wait[1]));
+      atomicAdd(p.prof + 2, static_cast<unsigned long long>(prof_wait[2]));
+    } else if (warp == 2) {
+      atomicAdd(p.prof + 3, static_cast<unsigned long long>(prof_wait[3]));
+      atomicAdd(p.prof + 5, static_cast<unsigned long long>(total));
+    }
+  }
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {

@@ -76,8 +76,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false when the limit expires or when another role of
 // the CTA has already raised the abort flag; the caller then leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#ifdef FLYB200_PROFILE
+#define FLYB200_PROF_ARG(x) , x
+#else
+#define FLYB200_PROF_ARG(x)
+#endif
+// `waited`: optional cycle counter (profiling builds only) that receives the time spent in this wait.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long* waited = nullptr) {
   if (mbar_try_wait(bar, parity)) return true;
+  const long long t_begin = waited ? clock64() : 0;
+  struct Scope {
+    long long* w;
+    long long t0;
+    __device__ ~Scope() {
+      if (w) *w += clock64() - t0;
+    }
+  } scope{waited, t_begin};
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (!mbar_try_wait(bar, parity)) {

@@ -22,13 +22,58 @@ def get_dtype_max(dtype: torch.dtype) -> float:
     return torch.finfo(dtype).max if dtype.is_floating_point else torch.iinfo(dtype).max
 
 
-def pertoken_quant(x, scale=None, x_scale=None, scale_dtype=torch.float32, quant_dtype=torch.int8, dtypeMax=None):
+_X_DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def _kernel_can_quantise(x, scale, x_scale, scale_dtype, quant_dtype, dtypeMax) -> bool:
+    if not (isinstance(x, torch.Tensor) and x.is_cuda and x.is_contiguous() and x.dim() >= 1):
+        return False
+    if scale is not None or x_scale is not None or dtypeMax is not None or scale_dtype != torch.float32:
+        return False
+    if x.dtype not in _X_DTYPES or quant_dtype not in (torch.int8, getattr(torch, "float8_e4m3fn", None)):
+        return False
+    k = x.shape[-1]
+    return k > 0 and k % (4 if x.dtype == torch.float32 else 8) == 0 and x.data_ptr() % 16 == 0 and x.numel() < 2**31
+
+
+def pertoken_quant_kernel(x: torch.Tensor, quant_dtype=torch.int8):
+    """The quantiser as ONE CUDA kernel (row maximum, scale and conversion
+    fused; the torch statement below launches about ten element-wise kernels
+    and materialises fp32 temporaries).  Bit-identical to :func:`pertoken_quant`
+    evaluated by torch on the same GPU tensor."""
+    lib = _lib.load()
+    k = x.shape[-1]
+    rows = x.numel() // k
+    y = torch.empty(x.shape, dtype=quant_dtype, device=x.device)
+    s = torch.empty(*x.shape[:-1], 1, dtype=torch.float32, device=x.device)
+    qd = _lib.DT_INT8 if quant_dtype == torch.int8 else _lib.DT_FP8
+    with torch.cuda.device(x.device):
+        rc = lib.flyb200_pertoken_quant(
+            y.data_ptr(), s.data_ptr(), x.data_ptr(), rows, k, _X_DTYPES[x.dtype], qd, _stream_ptr(x.device)
+        )
+    _lib.check(rc, "pertoken_quant")
+    return y, s
+
+
+def pertoken_quant(
+    x, scale=None, x_scale=None, scale_dtype=torch.float32, quant_dtype=torch.int8, dtypeMax=None, use_kernel=None
+):
     """Symmetric per-row quantisation: returns ``(y, y_scale)`` with
     ``y = (x / s).to(quant_dtype)`` and ``s = rowmax(|x|) / dtypeMax`` (shape
     [..., 1]); all-zero rows get scale 1; NaN -> 0 and +-Inf -> +-dtypeMax before
     the reduction; ``x_scale`` is an optional smoothing factor multiplied in
     first; ``scale`` supplies the scales instead of computing them.  The cast is
-    torch's (int8 truncates toward zero, float8 rounds to nearest even)."""
+    torch's (int8 truncates toward zero, float8 rounds to nearest even).
+
+    CUDA tensors in the common form (no explicit scale, smoothing factor or
+    dtypeMax) go through the fused kernel (:func:`pertoken_quant_kernel`);
+    ``use_kernel=False`` forces the torch statement, ``use_kernel=True`` raises
+    if the kernel cannot take the arguments."""
+    can = _kernel_can_quantise(x, scale, x_scale, scale_dtype, quant_dtype, dtypeMax)
+    if use_kernel and not can:
+        raise ValueError("the fused quantiser needs a contiguous CUDA fp32/fp16/bf16 tensor and default options")
+    if can and use_kernel is not False:
+        return pertoken_quant_kernel(x, quant_dtype)
     h = x.to(torch.float32)
     if x_scale is not None:
         h = h * x_scale

@@ -163,6 +163,17 @@ int flyb200_shuffle_weight(void* dst, const void* src, int N, int K, int elem_by
 /* Inverse of flyb200_shuffle_weight: row-major [N, K] from the B200 image. */
 int flyb200_unshuffle_weight(void* dst, const void* src, int N, int K, int elem_bytes, void* stream);
 
+/* Per-token quantiser on the GPU: y[rows, K] (fp8 e4m3fn or int8) and
+ * scale[rows] (fp32) from x[rows, K] (x_dtype: 0 = fp32, 1 = fp16, 2 = bf16).
+ * Same arithmetic, bit for bit, as pertoken_quant (tests/utils.py:29-73)
+ * evaluated by torch on a GPU: scale = rowmax|x| * (1/qmax) with 0 -> 1 (qmax
+ * 448 / 127), y = x / scale converted with round-to-nearest-even (fp8) or
+ * truncation toward zero (int8), NaN -> 0 and +-Inf -> +-qmax beforehand.  The
+ * reference's own device kernel for this step is tests/kernels/test_quant.py:82-275.
+ * Requirements: K a multiple of 4 (fp32) or 8 (16-bit input), x 16-byte aligned. */
+int flyb200_pertoken_quant(void* y, float* scale, const void* x, int rows, int K, int x_dtype, int quant_dtype,
+                           void* stream);
+
 /* 1 when (N, K, elem_bytes) can be preshuffled into the B200 image, else 0.
  * A pure function of its arguments: the helper and the GEMM evaluate the same
  * predicate because the `is_shuffled` attribute does not survive the flat views
