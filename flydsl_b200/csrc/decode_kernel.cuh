@@ -66,6 +66,11 @@ __device__ __forceinline__ uint4 ld_dsmem_v4(uint32_t addr) {
                : "memory");
   return v;
 }
+__device__ __forceinline__ uint4 ld_smem_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 // sum of two raw 32-bit accumulators (int32 or fp32 bit patterns)
 template <bool IS_INT>
 __device__ __forceinline__ uint32_t add_raw(uint32_t a, uint32_t b) {
@@ -77,6 +82,64 @@ __device__ __forceinline__ uint32_t add_raw(uint32_t a, uint32_t b) {
 }
 __device__ __forceinline__ void st_smem(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// Sum, in the fixed order s = 0..S-1, the partial tiles of the S CTAs of the
+// cluster for the tokens m_first, m_first+4, ... < m_end and four consecutive
+// channels, apply the epilogue and store.  All S*U peer reads of an iteration
+// are issued before the first is used.
+template <int KIND, int OUTMODE, int SMAX, int U>
+__device__ __forceinline__ void cluster_reduce_slice(const GemmParams& p, uint32_t red_mine, uint32_t my_rank, int S,
+                                                     int m_first, int m_end, int m_base, int n4, bool col_ok,
+                                                     const float* sa_s, const float (&sb4)[4], const float (&bias4)[4],
+                                                     bool scaled) {
+  using KT = KindTraits<KIND>;
+  // Every load below is unconditional (addresses are clamped to a valid token
+  // and unused peers alias peer 0), so the compiler can keep all SMAX*U of them
+  // in flight; results outside the range are simply not used.
+  uint32_t peer[SMAX];
+#pragma unroll
+  for (int s = 0; s < SMAX; ++s) peer[s] = map_to_cta(red_mine, static_cast<uint32_t>(s < S ? s : 0));
+  (void)my_rank;
+#pragma unroll 1
+  for (int mb = m_first; mb < m_end; mb += 4 * U) {
+    uint4 v[SMAX][U];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) {
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int mc = min(mb + 4 * j, m_end - 1);
+        v[s][j] = ld_dsmem_v4(peer[s] + static_cast<uint32_t>(mc * BLOCK_ROWS * 4));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const int m = mb + 4 * j;
+      uint4 acc = v[0][j];
+#pragma unroll
+      for (int s = 1; s < SMAX; ++s) {
+        if (s < S) {
+          acc.x = add_raw<KT::is_int>(acc.x, v[s][j].x);
+          acc.y = add_raw<KT::is_int>(acc.y, v[s][j].y);
+          acc.z = add_raw<KT::is_int>(acc.z, v[s][j].z);
+          acc.w = add_raw<KT::is_int>(acc.w, v[s][j].w);
+        }
+      }
+      if (m < m_end && col_ok) {
+        if constexpr (OUTMODE == OUT_RAW32) {
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(p.c) + static_cast<size_t>(m_base + m) * p.N + n4) = acc;
+        } else {
+          const float sa_v = sa_s[m];
+          const float v0 = epilogue_value<KT::is_int>(acc.x, sa_v, sb4[0], bias4[0], p.epilogue, scaled);
+          const float v1 = epilogue_value<KT::is_int>(acc.y, sa_v, sb4[1], bias4[1], p.epilogue, scaled);
+          const float v2 = epilogue_value<KT::is_int>(acc.z, sa_v, sb4[2], bias4[2], p.epilogue, scaled);
+          const float v3 = epilogue_value<KT::is_int>(acc.w, sa_v, sb4[3], bias4[3], p.epilogue, scaled);
+          *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.c) + static_cast<size_t>(m_base + m) * p.N + n4) =
+              make_uint2(pack2<OUTMODE>(v0, v1), pack2<OUTMODE>(v2, v3));
+        }
+      }
+    }
+  }
 }
 
 template <int KIND, int BN, int OUTMODE>
@@ -105,6 +168,10 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     return;
   }
   const int n0 = blockIdx.x * BLOCK_ROWS;
+  // grid.z splits the tokens into blocks of BN: each CTA sees only its own block
+  const int m_base = blockIdx.z * BN;
+  const int M_loc = min(BN, p.M - m_base);  // >= 1 by construction of the grid
+  const int tile_id = blockIdx.z * gridDim.x + blockIdx.x;  // (token block, channel tile)
   const int num_kb_total = p.K_bytes / KBLOCK_BYTES;
   const int kb_begin = blockIdx.y * p.kb_per_split;
   const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
@@ -122,6 +189,13 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
   //   pdl == 2: the weights are model state that no kernel on the stream
   //             writes, so their first loads are issued before the wait.
   if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#ifdef FLYB200_PROFILE
+  const unsigned long long prof_t0 = globaltimer_ns();
+  if (threadIdx.x == 0) atomicMin(p.prof + 0, prof_t0);
+#define FLYB200_STAMP(idx) atomicAdd(p.prof + (idx), globaltimer_ns() - prof_t0)
+#else
+#define FLYB200_STAMP(idx)
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -146,7 +220,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     }
     if (p.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < pre; ++i)
-      tma_load_2d(smem_base + L.off_a + i * A_STAGE, &tmA, bar_full + 8 * i, (kb_begin + i) * KBLOCK_BYTES, 0, pol_a);
+      tma_load_2d(smem_base + L.off_a + i * A_STAGE, &tmA, bar_full + 8 * i, (kb_begin + i) * KBLOCK_BYTES, m_base, pol_a);
   }
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   if (warp == 1) {
@@ -177,7 +251,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
         mbar_expect_tx(fb, A_STAGE + w_bytes);
         bulk_load_1d(smem_base + L.off_w + stage * W_STAGE, p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES,
                      w_bytes, fb, pol_w);
-        tma_load_2d(smem_base + L.off_a + stage * A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, 0, pol_a);
+        tma_load_2d(smem_base + L.off_a + stage * A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, m_base, pol_a);
         ++issued;
         if (++stage == stages) {
           stage = 0;
@@ -212,6 +286,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
           break;
         }
         tc_fence_after();
+        if (kb == 0) FLYB200_STAMP(1);  // first stage landed
         const uint64_t wdesc = umma_desc_sw128_kmajor(smem_base + L.off_w + stage * W_STAGE);
         const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L.off_a + stage * A_STAGE);
 #pragma unroll
@@ -225,6 +300,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
           phase ^= 1u;
         }
       }
+      FLYB200_STAMP(2);  // last MMA issued (all stages landed)
       if (ok) umma_commit(bar_tfull);
     }
     __syncwarp();
@@ -240,12 +316,12 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
   constexpr int CH = 16;  // tokens per TMEM load
 
   auto emit = [&](int m, uint32_t raw) {
-    if (m < p.M && n < p.N) {
+    if (m < M_loc && n < p.N) {
       if constexpr (OUTMODE == OUT_RAW32) {
-        reinterpret_cast<uint32_t*>(p.c)[static_cast<size_t>(m) * p.N + n] = raw;
+        reinterpret_cast<uint32_t*>(p.c)[static_cast<size_t>(m_base + m) * p.N + n] = raw;
       } else {
         const float v = epilogue_value<KT::is_int>(raw, sa_s[m], sb_v, bias_v, p.epilogue, scaled);
-        reinterpret_cast<uint16_t*>(p.c)[static_cast<size_t>(m) * p.N + n] = pack1<OUTMODE>(v);
+        reinterpret_cast<uint16_t*>(p.c)[static_cast<size_t>(m_base + m) * p.N + n] = pack1<OUTMODE>(v);
       }
     }
   };
@@ -253,7 +329,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
   if (warp >= 2) {
     // epilogue operands, fetched while the weight stream runs
     const int et = threadIdx.x - 64;
-    for (int i = et; i < BN; i += 128) sa_s[i] = (scaled && i < p.M) ? __ldg(p.sa + i) : 0.0f;
+    for (int i = et; i < BN; i += 128) sa_s[i] = (scaled && i < M_loc) ? __ldg(p.sa + m_base + i) : 0.0f;
     sb_v = (scaled && n < p.N) ? __ldg(p.sb + n) : 0.0f;
     bias_v = (p.epilogue != EPI_NONE && n < p.N) ? load_bias<OUTMODE>(p.bias, n) : 0.0f;
     named_bar_sync(1, 128);
@@ -262,13 +338,14 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     if (!ok && lane == 0) report_failure(p.status, ST_TIMEOUT, abort_flag);
     // uniform verdict over the four epilogue warps: the paths below meet at barriers
     ok = named_bar_and(1, 128, ok);
+    if (threadIdx.x == 64) FLYB200_STAMP(3);  // accumulator complete
     if (ok) {
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       if (p.reduce_mode == REDUCE_NONE) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CH) {
-          if (c0 >= p.M) break;
+          if (c0 >= M_loc) break;
           uint32_t r[CH];
           tmem_ld_x16(t_row + c0, r);
           tmem_ld_wait();
@@ -278,7 +355,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
       } else if (p.reduce_mode == REDUCE_CLUSTER) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CH) {
-          if (c0 >= p.M) break;
+          if (c0 >= M_loc) break;
           uint32_t r[CH];
           tmem_ld_x16(t_row + c0, r);
           tmem_ld_wait();
@@ -289,11 +366,11 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
         // partials: [split][channel tile][token][128 channels], 32-bit
         uint32_t* part = reinterpret_cast<uint32_t*>(p.ws_partials);
         const size_t tile_elems = static_cast<size_t>(BN) * BLOCK_ROWS;
-        const size_t split_stride = static_cast<size_t>(gridDim.x) * tile_elems;
-        uint32_t* mine = part + blockIdx.y * split_stride + blockIdx.x * tile_elems + ch_local;
+        const size_t split_stride = static_cast<size_t>(gridDim.x) * gridDim.z * tile_elems;
+        uint32_t* mine = part + blockIdx.y * split_stride + tile_id * tile_elems + ch_local;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CH) {
-          if (c0 >= p.M) break;
+          if (c0 >= M_loc) break;
           uint32_t r[CH];
           tmem_ld_x16(t_row + c0, r);
           tmem_ld_wait();
@@ -303,16 +380,16 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
         __threadfence();
         named_bar_sync(1, 128);
         if (threadIdx.x == 64) {
-          const int old = atomicAdd(p.ws_tickets + blockIdx.x, 1);
+          const int old = atomicAdd(p.ws_tickets + tile_id, 1);
           const int last = (old == p.split_k - 1) ? 1 : 0;
-          if (last) p.ws_tickets[blockIdx.x] = 0;  // leave the ticket ready for the next launch
+          if (last) p.ws_tickets[tile_id] = 0;  // leave the ticket ready for the next launch
           *last_flag = last;
         }
         named_bar_sync(1, 128);
         if (*last_flag) {
           __threadfence();
-          const uint32_t* src = part + blockIdx.x * tile_elems + ch_local;
-          const int m_lim = min(p.M, BN);
+          const uint32_t* src = part + tile_id * tile_elems + ch_local;
+          const int m_lim = M_loc;
           constexpr int U = 8;  // tokens in flight per thread
 #pragma unroll 1
           for (int m0 = 0; m0 < m_lim; m0 += U) {
@@ -352,15 +429,13 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
       // Reduce-scatter over the cluster: this CTA owns a slice of the tokens.
       // A warp takes one token at a time and each lane four consecutive
       // channels, so every peer read is one 16-byte load and every output row
-      // leaves as one 256-byte (bf16) run per warp.  Splits are summed in the
-      // fixed order 0..S-1.
+      // leaves as one 256-byte (bf16) run per warp.
       const uint32_t rank = cluster_ctarank();
       const int S = p.split_k;
-      const int m_lim = min(p.M, BN);
+      const int m_lim = M_loc;
       const int chunk = (m_lim + S - 1) / S;
       const int m_begin = static_cast<int>(rank) * chunk;
       const int m_end = min(m_lim, m_begin + chunk);
-      const int ew = warp - 2;
       const int ch4 = lane * 4;
       const int n4 = n0 + ch4;
       const bool col_ok = n4 < p.N;  // N is a multiple of 4: the four channels are in or out together
@@ -373,51 +448,17 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
         }
       }
       const uint32_t red_mine = red_base + static_cast<uint32_t>(ch4 * 4);
-      const uint32_t peer0 = map_to_cta(red_mine, 0);
-      constexpr int U = 8;  // tokens in flight per warp
-#pragma unroll 1
-      for (int mb = m_begin + ew; mb < m_end; mb += 4 * U) {
-        uint4 acc[U];
-#pragma unroll
-        for (int j = 0; j < U; ++j) {
-          const int m = mb + 4 * j;
-          acc[j] = (m < m_end) ? ld_dsmem_v4(peer0 + static_cast<uint32_t>(m * BLOCK_ROWS * 4)) : make_uint4(0, 0, 0, 0);
-        }
-        for (int s = 1; s < S; ++s) {
-          const uint32_t peer_s = map_to_cta(red_mine, static_cast<uint32_t>(s));
-          uint4 v[U];
-#pragma unroll
-          for (int j = 0; j < U; ++j) {
-            const int m = mb + 4 * j;
-            v[j] = (m < m_end) ? ld_dsmem_v4(peer_s + static_cast<uint32_t>(m * BLOCK_ROWS * 4)) : make_uint4(0, 0, 0, 0);
-          }
-#pragma unroll
-          for (int j = 0; j < U; ++j) {
-            acc[j].x = add_raw<KT::is_int>(acc[j].x, v[j].x);
-            acc[j].y = add_raw<KT::is_int>(acc[j].y, v[j].y);
-            acc[j].z = add_raw<KT::is_int>(acc[j].z, v[j].z);
-            acc[j].w = add_raw<KT::is_int>(acc[j].w, v[j].w);
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < U; ++j) {
-          const int m = mb + 4 * j;
-          if (m < m_end && col_ok) {
-            if constexpr (OUTMODE == OUT_RAW32) {
-              *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(p.c) + static_cast<size_t>(m) * p.N + n4) = acc[j];
-            } else {
-              const float sa_v = sa_s[m];
-              const float v0 = epilogue_value<KT::is_int>(acc[j].x, sa_v, sb4[0], bias4[0], p.epilogue, scaled);
-              const float v1 = epilogue_value<KT::is_int>(acc[j].y, sa_v, sb4[1], bias4[1], p.epilogue, scaled);
-              const float v2 = epilogue_value<KT::is_int>(acc[j].z, sa_v, sb4[2], bias4[2], p.epilogue, scaled);
-              const float v3 = epilogue_value<KT::is_int>(acc[j].w, sa_v, sb4[3], bias4[3], p.epilogue, scaled);
-              *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.c) + static_cast<size_t>(m) * p.N + n4) =
-                  make_uint2(pack2<OUTMODE>(v0, v1), pack2<OUTMODE>(v2, v3));
-            }
-          }
-        }
+      const int m_first = m_begin + (warp - 2);
+      // sixteen 16-byte loads in flight per thread whatever the split
+      if (S <= 2) {
+        cluster_reduce_slice<KIND, OUTMODE, 2, 8>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
+      } else if (S <= 4) {
+        cluster_reduce_slice<KIND, OUTMODE, 4, 4>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
+      } else {
+        cluster_reduce_slice<KIND, OUTMODE, 8, 2>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
       }
     }
+    if (threadIdx.x == 64) FLYB200_STAMP(4);  // this CTA's slice of the output written
     cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
   }
 
@@ -428,6 +469,13 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+#ifdef FLYB200_PROFILE
+  if (threadIdx.x == 0) {
+    FLYB200_STAMP(5);
+    atomicMax(p.prof + 6, globaltimer_ns());
+  }
+#endif
+#undef FLYB200_STAMP
 }
 
 }  // namespace flyb200

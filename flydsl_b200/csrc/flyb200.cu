@@ -242,7 +242,7 @@ int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
   if (L.total > SMEM_LIMIT || BN * BLOCK_ROWS * 4 > L.off_bar) return FLYB200_E_UNSUPPORTED;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((p.N + BLOCK_ROWS - 1) / BLOCK_ROWS, p.split_k, 1);
+  cfg.gridDim = dim3((p.N + BLOCK_ROWS - 1) / BLOCK_ROWS, p.split_k, p.token_blocks < 1 ? 1 : p.token_blocks);
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = L.total;
   cfg.stream = s;
@@ -282,8 +282,9 @@ inline int decode_bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ?
 
 // Split-K factor of the small-M kernel when the caller does not force one:
 // enough CTAs to cover the SMs, at least four k-blocks per CTA.
-int auto_split_k(int N, int K_bytes, int sms) {
-  const int n_tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
+// `token_blocks`: CTAs per channel tile that the token split already provides.
+int auto_split_k(int N, int K_bytes, int sms, int token_blocks = 1) {
+  const int n_tiles = ((N + BLOCK_ROWS - 1) / BLOCK_ROWS) * token_blocks;
   const int kb = K_bytes / KBLOCK_BYTES;
   if (n_tiles >= sms || n_tiles > static_cast<int>(TICKET_BYTES / sizeof(int))) return 1;
   int split = sms / n_tiles;
@@ -292,14 +293,15 @@ int auto_split_k(int N, int K_bytes, int sms) {
   return split < 1 ? 1 : split;
 }
 
-size_t partial_bytes(int split, int N, int bn) {
-  const size_t n_tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
+size_t partial_bytes(int split, int N, int bn, int token_blocks = 1) {
+  const size_t n_tiles = static_cast<size_t>((N + BLOCK_ROWS - 1) / BLOCK_ROWS) * token_blocks;
   return static_cast<size_t>(split) * n_tiles * bn * BLOCK_ROWS * sizeof(uint32_t);
 }
 
 struct Plan {
   bool decode;
   bool two_sm;  // large-M kernel as CTA pairs (tcgen05 cta_group::2)
+  int token_blocks;  // small-M kernel: the tokens are split into this many blocks of bn (grid.z)
   int bn;
   int split_k;
   int kb_per_split;
@@ -334,11 +336,20 @@ inline int hint_reduce(int h) { return (h >> 12) & 0xF; }
 inline int hint_group(int h) { return (h >> 16) & 0xFF; }
 inline int hint_stages(int h) { return (h >> 24) & 0xF; }
 inline int hint_pdl(int h) { return (h >> 28) & 0x3; }
+inline int hint_tokens(int h) { return (h >> 30) & 0x3; }
 
-bool workspace_fits(bool have_ws, size_t ws_bytes, int split, int N, int bn) {
-  return have_ws && ws_bytes >= TICKET_BYTES + partial_bytes(split, N, bn) &&
-         (N + BLOCK_ROWS - 1) / BLOCK_ROWS <= static_cast<int>(TICKET_BYTES / sizeof(int));
+bool workspace_fits(bool have_ws, size_t ws_bytes, int split, int N, int bn, int token_blocks) {
+  return have_ws && ws_bytes >= TICKET_BYTES + partial_bytes(split, N, bn, token_blocks) &&
+         ((N + BLOCK_ROWS - 1) / BLOCK_ROWS) * token_blocks <= static_cast<int>(TICKET_BYTES / sizeof(int));
 }
+
+// How many blocks the tokens of the small-M kernel are split into when the
+// caller does not say.  Splitting the tokens gives more CTAs per channel tile
+// without a reduction step, but every weight block is then fetched once per
+// token block; measured on B200 (N = K = 8192, M = 32..256) that costs more
+// than the split-K reduction it saves (21 us vs 14.5 us at M = 32), so the
+// automatic choice is one block and the split stays a tuning option.
+int auto_token_blocks(int /*M*/, int /*N*/, int /*sms*/) { return 1; }
 
 int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t workspace_bytes, bool have_ws, int sms) {
   const int want_kernel = hint_kernel(variant_hint);
@@ -349,7 +360,14 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   plan->two_sm = want_kernel == 3 ? true : want_kernel == 2 ? false : rows_two_sm_default();
   if (plan->decode && M > 256) return FLYB200_E_UNSUPPORTED;
   if (want_reduce > REDUCE_CLUSTER) return FLYB200_E_BAD_ARG;
-  plan->bn = plan->decode ? decode_bn_for(M) : ROWS_BN;
+  plan->token_blocks = 1;
+  plan->bn = ROWS_BN;
+  if (plan->decode) {
+    const int ht = hint_tokens(variant_hint);
+    int t = ht == 0 ? auto_token_blocks(M, N, sms) : (ht == 1 ? 1 : ht == 2 ? 2 : 4);
+    plan->bn = decode_bn_for((M + t - 1) / t);
+    plan->token_blocks = (M + plan->bn - 1) / plan->bn;  // no empty block
+  }
   plan->group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : (plan->two_sm ? 8 : 16);
   plan->split_k = 1;
   plan->reduce_mode = REDUCE_NONE;
@@ -359,7 +377,7 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   const int kb = K_bytes / KBLOCK_BYTES;
   plan->kb_per_split = kb;
   if (plan->decode) {
-    int split = want_split > 0 ? want_split : auto_split_k(N, K_bytes, sms);
+    int split = want_split > 0 ? want_split : auto_split_k(N, K_bytes, sms, plan->token_blocks);
     if (split > kb) split = kb;
     int mode = REDUCE_NONE;
     if (split > 1) {
@@ -368,7 +386,8 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
         if (want_split > 0) return FLYB200_E_UNSUPPORTED;
         split = MAX_CLUSTER_SPLIT;
       }
-      if (mode == REDUCE_WORKSPACE && !workspace_fits(have_ws, workspace_bytes, split, N, plan->bn)) {
+      if (mode == REDUCE_WORKSPACE &&
+          !workspace_fits(have_ws, workspace_bytes, split, N, plan->bn, plan->token_blocks)) {
         if (want_split > 0 || want_reduce != 0) return FLYB200_E_WORKSPACE;  // explicit requests are not changed silently
         split = split < MAX_CLUSTER_SPLIT ? split : MAX_CLUSTER_SPLIT;
         mode = REDUCE_CLUSTER;
@@ -431,6 +450,7 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
   p.reduce_mode = plan.reduce_mode;
   p.stages = plan.stages;
   p.pdl = plan.pdl;
+  p.token_blocks = plan.token_blocks;
   p.ws_tickets = static_cast<int*>(workspace);
   p.ws_partials = workspace ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + TICKET_BYTES) : nullptr;
   p.status = st->status;
@@ -619,7 +639,8 @@ int flyb200_gemm_a8w8_static_scratch(void* c, const void* a, const void* w_shuf,
   // stream, ahead of the kernel.
   CUDA_TRY(cudaMemsetAsync(scratch, 0, TICKET_BYTES, s));
   // small-M kernel, reduction through the workspace, this split, no dependent launch
-  const int hint = (1 << 8) | (REDUCE_WORKSPACE << 12) | (2 << 28) | split;
+  // (and the tokens in one block, so that the size formula documented for this entry point holds)
+  const int hint = (1 << 8) | (REDUCE_WORKSPACE << 12) | (2 << 28) | (1 << 30) | split;
   return gemm_common(c, a, w_shuf, scale_a, scale_b, bias, M, N, K, in_dtype,
                      out_dtype == FLYB200_OUT_FP16 ? OUT_FP16 : OUT_BF16, epilogue, hint, scratch, STATIC_SCRATCH_BYTES,
                      stream);
@@ -776,7 +797,7 @@ size_t flyb200_workspace_bytes(int M, int N, int K, int in_dtype, int variant_hi
   Plan plan;
   if (make_plan(&plan, M, N, K * eb, variant_hint, static_cast<size_t>(-1) >> 1, true, st->sms)) return 0;
   if (!plan.decode || plan.reduce_mode != REDUCE_WORKSPACE) return 0;
-  return TICKET_BYTES + partial_bytes(plan.split_k, N, plan.bn);
+  return TICKET_BYTES + partial_bytes(plan.split_k, N, plan.bn, plan.token_blocks);
 }
 
 int flyb200_read_status(int* out_status) {

@@ -49,6 +49,7 @@ struct GemmParams {
   int pdl;               // decode kernel: launched with programmatic stream serialisation
   float* ws_partials;    // decode kernel, REDUCE_WORKSPACE
   int* ws_tickets;       // decode kernel, REDUCE_WORKSPACE (zero before first use; self-resetting)
+  int token_blocks;      // decode kernel: grid.z, blocks of BN tokens
   int n_dst;             // scatter kernel: number of output buffers
   int dst_first;         // scatter kernel: buffer stored to first
   int* status;           // device status word (first failure wins)

@@ -61,7 +61,8 @@ class PreshuffleGemm:
         self.N, self.K = int(N), int(K)
         self.in_dtype, self.out_dtype, self.epilogue = in_dtype, out_dtype, epilogue
         self.tile = tile
-        self.variant_hint = int(variant_hint)
+        h = int(variant_hint) & 0xFFFFFFFF
+        self.variant_hint = h - (1 << 32) if h >= (1 << 31) else h  # as a signed 32-bit C int
         self._dt = _lib.IN_DTYPES[in_dtype]
         self._out = _lib.OUT_DTYPES[out_dtype]
         self._epi = _lib.EPILOGUES[epilogue]

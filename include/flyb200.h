@@ -70,7 +70,11 @@ extern "C" {
  *              the previous kernel has completed (only valid when no kernel on
  *              the stream writes the weights), 2 = off.  Automatic: the first
  *              form, unless the environment variable FLYB200_PDL says 0 (off)
- *              or 2 (the second form). */
+ *              or 2 (the second form).
+ *   bits 30-31 token blocks of the small-M kernel (CTAs per channel tile that
+ *              each take a block of the tokens over the whole K range; no
+ *              reduction step, but every weight block is fetched once per token
+ *              block): 1 = one block, 2 = two, 3 = four.  Automatic: one. */
 
 /* The GEMM: c[M,N] = epilogue((a[M,K] . w[N,K]^T) * scale_a[m] * scale_b[n]).
  * Replaces the launcher returned by compile_preshuffle_gemm and the kernel

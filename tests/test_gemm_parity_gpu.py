@@ -23,6 +23,7 @@ SENTINEL = -8192.0
 DEC, ROWS, ROWS2 = 1 << 8, 2 << 8, 3 << 8  # variant_hint: kernel field (small-M, large-M, large-M as CTA pairs)
 WS, CL = 1 << 12, 2 << 12  # variant_hint: split-K reduction through a global workspace / a cluster
 PDL = 1 << 28  # variant_hint: programmatic dependent launch
+TOK1, TOK2, TOK4 = 1 << 30, 2 << 30, (3 << 30) - (1 << 32)  # variant_hint: token blocks (as signed 32-bit)
 
 
 def STAGES(n):
@@ -93,8 +94,9 @@ def test_scaled_output_matches_reference_check(dev, in_dtype, m, n, k, tile):
 @pytest.mark.parametrize(
     "hint",
     [DEC | 1, DEC | CL | 2, DEC | CL | 5, DEC | CL | 8, DEC | WS | 3, DEC | WS | 16, DEC | 2 | STAGES(3), DEC | 2 | PDL,
-     DEC | 2 | (2 << 28), ROWS, ROWS2],
-    ids=["nosplit", "cluster2", "cluster5", "cluster8", "ws3", "ws16", "stages3", "pdl", "nopdl", "rows", "rows2"],
+     DEC | 2 | (2 << 28), DEC | TOK1 | 2, DEC | TOK2, DEC | TOK4, DEC | TOK2 | CL | 2, DEC | TOK4 | WS | 3, ROWS, ROWS2],
+    ids=["nosplit", "cluster2", "cluster5", "cluster8", "ws3", "ws16", "stages3", "pdl", "nopdl", "tok1", "tok2", "tok4",
+         "tok2_cluster2", "tok4_ws3", "rows", "rows2"],
 )
 @pytest.mark.parametrize("m", [1, 16, 17, 64, 100, 256])
 def test_every_kernel_variant_small_m(dev, hint, m):
@@ -126,6 +128,9 @@ def test_cta_pair_kernel_scaled_output(dev, in_dtype, m, n, k):
         (7, 144, 1024, DEC | CL | 3),
         (200, 512, 1024, DEC | CL | 2),
         (200, 512, 1024, DEC | WS | 2),
+        (200, 512, 1024, DEC | TOK4 | WS | 2),
+        (33, 1040, 1024, DEC | TOK2 | CL | 4),
+        (8, 57344, 256, 0),  # very wide: more channel tiles than SMs
         (300, 784, 1024, ROWS),
         (1024, 2048, 8320, ROWS),  # K = 65 * 128 as in the reference's large shapes
         (300, 784, 1024, ROWS2),
