@@ -359,15 +359,11 @@ def main():
     a_host.copy_(a_q.view(torch.int8))
     sa_host = sa.cpu().pin_memory()
     c_host = torch.empty(m, nl, dtype=torch.bfloat16).pin_memory()
-    a_dev = torch.empty_like(a_q.view(torch.int8))
-    sa_dev = torch.empty_like(sa)
     e2e_steps = max(3, min(args.steps, 10))
 
     def e2e_step():
-        a_dev.copy_(a_host, non_blocking=True)
-        sa_dev.copy_(sa_host, non_blocking=True)
-        op.forward(a_dev, sa_dev, out=c)
-        c_host.copy_(c, non_blocking=True)
+        # upload, multiply and download pipelined over row blocks (ColumnParallelGemm.forward_host)
+        op.forward_host(a_host, sa_host, c_host, chunks=8)
 
     for _ in range(2):
         e2e_step()
@@ -452,7 +448,7 @@ def main():
         "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
         "traffic": None,
         "traffic_note": "DRAM counters captured on the 4096x8192x8192 case only: 214 MB per launch vs 168 MB "
-        "algorithmic (profiles/bench_launch_list.md); the full workload re-streams the weights once per group of "
+        "algorithmic (ncu launch-list summary under profiles/); the full workload re-streams the weights once per group of "
         "16 row tiles, so its traffic does not scale in proportion",
         "algorithmic_bytes": gemm_bytes(m, nl, k),
         "launch_ms_median": med_ms,

@@ -44,6 +44,7 @@ SIGNATURES = {
     "flyb200_pertoken_quant": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_shuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_unshuffle_weight": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "flyb200_describe_plan": (_i, [_i, _i, _i, _i, _i, _i, ctypes.POINTER(_i)]),
     "flyb200_layout_kind": (_i, [_i, _i, _i]),
     "flyb200_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "flyb200_read_status": (_i, [ctypes.POINTER(_i)]),
@@ -87,6 +88,16 @@ def check(code: int, what: str = "libflyb200") -> None:
     if code == E_CUDA:
         msg += ": " + lib.flyb200_last_cuda_error().decode()
     raise FlyB200Error(code, f"{what}: {msg} (code {code})")
+
+
+PLAN_FIELDS = ("kernel", "bn", "split_k", "kb_per_split", "reduce", "stages", "pdl", "token_blocks")
+
+
+def describe_plan(m: int, n: int, k: int, in_dtype: str = "fp8", variant_hint: int = 0, sm_count: int = 148) -> dict:
+    """The kernel variant the library would pick (no GPU needed)."""
+    out = (_i * 8)()
+    check(load().flyb200_describe_plan(m, n, k, IN_DTYPES[in_dtype], variant_hint, sm_count, out), "describe_plan")
+    return dict(zip(PLAN_FIELDS, list(out)))
 
 
 def read_status() -> int:

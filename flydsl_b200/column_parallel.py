@@ -136,6 +136,43 @@ class ColumnParallelGemm:
                     self.spec.n_local, stream if stream is not None else torch.cuda.current_stream())
         return out
 
+    # ---- host buffers in, host buffer out ---------------------------------------
+    def forward_host(self, a_host: torch.Tensor, sa_host: torch.Tensor, out_host: torch.Tensor, chunks: int = 8):
+        """This rank's shard computed from pinned HOST activations into a pinned
+        HOST output, with the three legs pipelined over row blocks: while block i
+        is multiplied, block i+1 is uploaded and block i-1 downloaded (separate
+        streams; PCIe is full duplex).  Returns after enqueueing; the caller
+        synchronises ``torch.cuda.current_stream()``."""
+        m = a_host.shape[0]
+        dev = self.w_shuf.device
+        if getattr(self, "_host_state", None) is None or self._host_state[0] < m:
+            a_dev = torch.empty((m, a_host.shape[1]), dtype=a_host.dtype, device=dev)
+            sa_dev = torch.empty(m, dtype=torch.float32, device=dev)
+            c_dev = torch.empty((m, self.spec.n_local), dtype=self._bias.dtype, device=dev)
+            self._host_state = (m, a_dev, sa_dev, c_dev, torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+        _, a_dev, sa_dev, c_dev, s_in, s_out = self._host_state
+        cur = torch.cuda.current_stream(dev)
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        rows = max(128, ((m + chunks - 1) // chunks + 127) // 128 * 128)
+        with torch.cuda.stream(s_in):
+            sa_dev[:m].copy_(sa_host.view(-1)[:m], non_blocking=True)
+        for r0 in range(0, m, rows):
+            r1 = min(m, r0 + rows)
+            with torch.cuda.stream(s_in):
+                a_dev[r0:r1].copy_(a_host[r0:r1], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            cur.wait_event(ready)
+            self.forward(a_dev[r0:r1], sa_dev[r0:r1], out=c_dev[r0:r1], stream=cur)
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                out_host[r0:r1].copy_(c_dev[r0:r1], non_blocking=True)
+        cur.wait_stream(s_out)
+        return out_host
+
     # ---- GEMM fused with the all-gather of its output shards -------------------
     def enable_fused_gather(self, m_max: int) -> None:
         """Allocate (once) two full-width [m_max, N] output buffers in symmetric

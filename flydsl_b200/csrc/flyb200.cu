@@ -534,6 +534,30 @@ int launch_shuffle(void* dst, const void* src, int N, int Kb, cudaStream_t s) {
   return FLYB200_OK;
 }
 
+// Row quantiser launch: rows that fit the register-cached single-pass kernel
+// use it (one block per row), longer rows take the two-pass kernel.
+template <typename TIn, bool FP8>
+void launch_quant_t(uint8_t* y, float* scale, const TIn* x, int rows, int K, cudaStream_t s) {
+  constexpr int per_vec = 256 * QuantIn<TIn>::VEC;
+  if (K <= per_vec) {
+    pertoken_quant_row_kernel<TIn, FP8, 1><<<rows, 256, 0, s>>>(y, scale, x, rows, K);
+  } else if (K <= 2 * per_vec) {
+    pertoken_quant_row_kernel<TIn, FP8, 2><<<rows, 256, 0, s>>>(y, scale, x, rows, K);
+  } else if (K <= 4 * per_vec) {
+    pertoken_quant_row_kernel<TIn, FP8, 4><<<rows, 256, 0, s>>>(y, scale, x, rows, K);
+  } else if (K <= 8 * per_vec) {
+    pertoken_quant_row_kernel<TIn, FP8, 8><<<rows, 256, 0, s>>>(y, scale, x, rows, K);
+  } else {
+    const int grid = rows < 148 * 16 ? rows : 148 * 16;
+    pertoken_quant_kernel<TIn, FP8><<<grid, 256, 0, s>>>(y, scale, x, rows, K);
+  }
+}
+template <typename TIn>
+void launch_quant(uint8_t* y, float* scale, const TIn* x, int rows, int K, bool fp8, cudaStream_t s) {
+  if (fp8) launch_quant_t<TIn, true>(y, scale, x, rows, K, s);
+  else launch_quant_t<TIn, false>(y, scale, x, rows, K, s);
+}
+
 bool ranges_overlap(const void* a, const void* b, size_t bytes) {
   const uintptr_t x = reinterpret_cast<uintptr_t>(a), y = reinterpret_cast<uintptr_t>(b);
   return x < y + bytes && y < x + bytes;
@@ -757,23 +781,36 @@ int flyb200_pertoken_quant(void* y, float* scale, const void* x, int rows, int K
   if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 7u) != 0) return FLYB200_E_BAD_ALIGN;
   if (rows == 0) return FLYB200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int grid = rows < 148 * 16 ? rows : 148 * 16;
   uint8_t* yo = static_cast<uint8_t*>(y);
   const bool fp8 = quant_dtype == FLYB200_DT_FP8;
   if (x_dtype == QX_F32) {
-    const float* xi = static_cast<const float*>(x);
-    if (fp8) pertoken_quant_kernel<float, true><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
-    else pertoken_quant_kernel<float, false><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+    launch_quant<float>(yo, scale, static_cast<const float*>(x), rows, K, fp8, s);
   } else if (x_dtype == QX_F16) {
-    const __half* xi = static_cast<const __half*>(x);
-    if (fp8) pertoken_quant_kernel<__half, true><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
-    else pertoken_quant_kernel<__half, false><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+    launch_quant<__half>(yo, scale, static_cast<const __half*>(x), rows, K, fp8, s);
   } else {
-    const __nv_bfloat16* xi = static_cast<const __nv_bfloat16*>(x);
-    if (fp8) pertoken_quant_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
-    else pertoken_quant_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(yo, scale, xi, rows, K);
+    launch_quant<__nv_bfloat16>(yo, scale, static_cast<const __nv_bfloat16*>(x), rows, K, fp8, s);
   }
   CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+int flyb200_describe_plan(int M, int N, int K, int in_dtype, int variant_hint, int sm_count, int* out8) {
+  if (!out8 || M <= 0 || N <= 0 || K <= 0 || sm_count <= 0) return FLYB200_E_BAD_ARG;
+  if (in_dtype < FLYB200_DT_FP8 || in_dtype > FLYB200_DT_BF16) return FLYB200_E_BAD_ARG;
+  const int eb = elem_bytes_of(in_dtype);
+  if (!flyb200_layout_kind(N, K, eb)) return FLYB200_E_UNSUPPORTED;
+  Plan plan;
+  // planned as with an unlimited workspace: the answer says what would be needed
+  int rc = make_plan(&plan, M, N, K * eb, variant_hint, static_cast<size_t>(-1) >> 1, true, sm_count);
+  if (rc) return rc;
+  out8[0] = plan.decode ? 1 : (plan.two_sm ? 3 : 2);
+  out8[1] = plan.bn;
+  out8[2] = plan.split_k;
+  out8[3] = plan.kb_per_split;
+  out8[4] = plan.reduce_mode;
+  out8[5] = plan.decode ? plan.stages : (plan.two_sm ? ROWS2_STAGES : ROWS_STAGES);
+  out8[6] = plan.decode ? plan.pdl : 0;
+  out8[7] = plan.token_blocks;
   return FLYB200_OK;
 }
 

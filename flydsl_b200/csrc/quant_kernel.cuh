@@ -79,6 +79,73 @@ __device__ __forceinline__ uint8_t quant_one(float v, float s) {
   }
 }
 
+// Single-pass form for rows of at most 256 * VEC * NV elements: every thread
+// keeps its NV vectors of the row in registers between the maximum and the
+// conversion, so the row is read from memory exactly once and all of a
+// thread's loads are in flight together.  One block per row.
+template <typename TIn, bool FP8, int NV>
+__global__ void __launch_bounds__(256) pertoken_quant_row_kernel(uint8_t* __restrict__ y, float* __restrict__ scale,
+                                                                 const TIn* __restrict__ x, int rows, int K) {
+  constexpr int VEC = QuantIn<TIn>::VEC;
+  constexpr float QMAX = FP8 ? 448.0f : 127.0f;
+  __shared__ float warp_max[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const TIn* xr = x + static_cast<size_t>(r) * K;
+  float v[NV][VEC];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (i * 256 + threadIdx.x) * VEC;
+    if (k < K) {
+      QuantIn<TIn>::load(xr + k, v[i]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) v[i][e] = 0.0f;
+    }
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      v[i][e] = scrub(v[i][e], QMAX);
+      amax = fmaxf(amax, fabsf(v[i][e]));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (lane == 0) warp_max[warp] = amax;
+  __syncthreads();
+  float m = warp_max[lane & 7];
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float s = __fmul_rn(m, __fdiv_rn(1.0f, QMAX));
+  if (s == 0.0f) s = 1.0f;
+  if (threadIdx.x == 0) scale[r] = s;
+  uint8_t* yr = y + static_cast<size_t>(r) * K;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (i * 256 + threadIdx.x) * VEC;
+    if (k < K) {
+      uint32_t packed[VEC / 4];
+#pragma unroll
+      for (int w = 0; w < VEC / 4; ++w) {
+        uint32_t b = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) b |= static_cast<uint32_t>(quant_one<FP8>(v[i][4 * w + e], s)) << (8 * e);
+        packed[w] = b;
+      }
+      if constexpr (VEC == 4) {
+        *reinterpret_cast<uint32_t*>(yr + k) = packed[0];
+      } else {
+        *reinterpret_cast<uint2*>(yr + k) = make_uint2(packed[0], packed[1]);
+      }
+    }
+  }
+}
+
+// General form (any row length): two passes over the row, the second one from L1/L2.
 template <typename TIn, bool FP8>
 __global__ void __launch_bounds__(256) pertoken_quant_kernel(uint8_t* __restrict__ y, float* __restrict__ scale,
                                                              const TIn* __restrict__ x, int rows, int K) {

@@ -24,8 +24,31 @@ def main():
     ap.add_argument("--dtype", default="fp8", choices=["fp8", "int8"])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--hint", type=lambda s: int(s, 0), default=0)
+    ap.add_argument("--op", default="gemm", choices=["gemm", "quant", "shuffle"],
+                    help="gemm (default), quant: per-token quantiser on [m, k] bf16, shuffle: weight preshuffle of [n, k]")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
+    if a.op != "gemm":
+        from .utils import pertoken_quant_kernel
+
+        if a.op == "quant":
+            x = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16)
+            qd = torch.float8_e4m3fn if a.dtype == "fp8" else torch.int8
+            fn, byts = (lambda: pertoken_quant_kernel(x, qd)), a.m * a.k * 3 + a.m * 4
+        else:
+            w8 = torch.randint(-127, 128, (a.n, a.k), device=dev, dtype=torch.int8)
+            fn, byts = (lambda: shuffle_weight(w8)), 2 * a.n * a.k
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / a.iters
+        print(json.dumps({"op": a.op, "M": a.m, "N": a.n, "K": a.k, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1)}))
+        return
     if a.dtype == "fp8":
         x = (torch.randn(a.m, a.k, device=dev) * 64).clamp_(-448, 448).to(torch.float8_e4m3fn).view(torch.int8)
         w = (torch.randn(a.n, a.k, device=dev) * 64).clamp_(-448, 448).to(torch.float8_e4m3fn)

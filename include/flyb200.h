@@ -188,6 +188,15 @@ int flyb200_layout_kind(int N, int K, int elem_bytes);
  * the current device (0 when the chosen variant keeps its partial sums on chip). */
 size_t flyb200_workspace_bytes(int M, int N, int K, int in_dtype, int variant_hint);
 
+/* Which kernel variant flyb200_gemm_a8w8 would run for this problem on a GPU with
+ * sm_count SMs (pure host function, no CUDA call): out8 = { kernel (1 small-M,
+ * 2 large-M, 3 large-M as CTA pairs), tile width on the UMMA N side, split-K
+ * factor, k-blocks per split, reduction (0 none, 1 workspace, 2 cluster), ring
+ * depth, dependent-launch mode, token blocks }.  The B200 counterpart of the
+ * per-tile table _TILE_PRELOAD_TABLE / tile arguments the reference's callers
+ * tune by hand (kernels/gemm/preshuffle_gemm.py:19-105). */
+int flyb200_describe_plan(int M, int N, int K, int in_dtype, int variant_hint, int sm_count, int* out8);
+
 /* Device-side status word of the current device (0 = no failure since the last
  * read).  Synchronises the device; not for the launch path.  The reference only
  * prints runtime errors (lib/Runtime/ROCm/FlyRocmRuntimeWrappers.cpp:23-31). */

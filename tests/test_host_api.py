@@ -148,3 +148,30 @@ def test_reference_import_paths():
     from flydsl_b200.kernels.gemm.preshuffle_gemm import compile_preshuffle_gemm as cpg  # noqa: F401
 
     assert callable(flyc.compile)
+
+
+def test_variant_selection_is_a_pure_host_function():
+    """The M-bucket dispatch (the counterpart of the reference's per-tile tuning
+    table) can be inspected without a GPU."""
+    d = _lib.describe_plan
+    # decode shapes at N = K = 8192 on 148 SMs: 64 channel tiles x split-K 2 as clusters
+    p = d(32, 8192, 8192, "int8")
+    assert (p["kernel"], p["bn"], p["split_k"], p["reduce"], p["token_blocks"]) == (1, 32, 2, 2, 1)
+    assert p["split_k"] * p["kb_per_split"] >= 64
+    assert d(1, 8192, 8192)["bn"] == 16 and d(17, 8192, 8192)["bn"] == 32 and d(256, 8192, 8192)["bn"] == 256
+    # more channel tiles than SMs: no split
+    assert d(8, 57344, 8192)["split_k"] == 1 and d(8, 57344, 8192)["reduce"] == 0
+    # benchmark config 1: 32 tiles -> split 4
+    assert d(128, 4096, 4096)["split_k"] == 4
+    # large M: persistent kernel, one CTA per tile unless asked otherwise
+    assert d(257, 8192, 8192)["kernel"] == 2 and d(8192, 28672, 8192, variant_hint=3 << 8)["kernel"] == 3
+    # explicit requests are honoured or refused, never changed silently
+    assert d(32, 8192, 8192, variant_hint=(1 << 8) | (1 << 12) | 16)["reduce"] == 1
+    with pytest.raises(_lib.FlyB200Error):
+        d(32, 8192, 8192, variant_hint=(1 << 8) | (2 << 12) | 16)  # a cluster cannot hold 16 splits
+    with pytest.raises(_lib.FlyB200Error):
+        d(300, 8192, 8192, variant_hint=1 << 8)  # small-M kernel beyond 256 tokens
+    # a single k-block cannot be split
+    assert d(16, 1024, 128)["split_k"] == 1
+    # fewer SMs -> smaller split
+    assert d(32, 8192, 8192, sm_count=64)["split_k"] == 1
