@@ -81,3 +81,34 @@ def test_quantised_activations_feed_the_gemm():
     exact = a @ w.T  # unquantised product: only the fp8 quantisation error separates the two
     rel = ((c.float().cpu() - exact).norm() / exact.norm()).item()
     assert rel < 0.05, rel
+
+
+@pytest.mark.parametrize("qd", [FP8, torch.int8], ids=["fp8", "int8"])
+def test_kernel_bit_identical_on_adversarial_values(qd):
+    """Rows built to sit on the rounding boundaries of the target type (exact
+    ties, values one fp32 ulp either side of them, e4m3 subnormals, integers
+    and near-integers): the kernel's shortcut around the IEEE division must not
+    change a single byte."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(99)
+    k = 4096
+    qmax = 448.0 if qd == FP8 else 127.0
+    rows = []
+    for scale in (1.0, 0.37, 3.0e-3, 17.25, 1.0 / 3.0):
+        if qd == FP8:
+            mant = torch.arange(16, 32, dtype=torch.float32)  # neighbouring e4m3 mantissas x2: every second value is a tie
+            exps = 2.0 ** torch.arange(-10, 9, dtype=torch.float32)
+            base = (mant[None, :] * exps[:, None] / 16.0).reshape(-1)
+        else:
+            base = torch.arange(0, 128, dtype=torch.float32)
+        base = base[base <= qmax]
+        cand = torch.cat([base, torch.nextafter(base, torch.tensor(1e9)), torch.nextafter(base, torch.tensor(-1e9)), -base])
+        cand = cand[torch.randint(0, cand.numel(), (k - 1,), generator=g)] * scale
+        row = torch.cat([torch.tensor([qmax * scale]), cand])  # first element pins amax so that the scale is `scale`-like
+        rows.append(row)
+    x = torch.stack(rows).to(dev)
+    y_k, s_k = pertoken_quant_kernel(x, qd)
+    y_t, s_t = pertoken_quant(x, quant_dtype=qd, use_kernel=False)
+    torch.cuda.synchronize()
+    assert torch.equal(s_k, s_t)
+    assert torch.equal(y_k.view(torch.uint8), y_t.view(torch.uint8))
