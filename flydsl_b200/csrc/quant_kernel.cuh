@@ -12,8 +12,10 @@
 // torch's CUDA backend as a multiplication by the fp32 reciprocal, the
 // element-wise division is a true IEEE division.
 //
-// HBM-bound: one 256-thread block per row, two passes over the row (the second
-// one hits L1/L2), 16-byte loads, 4..8-byte stores.
+// One 256-thread block per row, 16-byte loads, 4..8-byte stores.  Rows of up to
+// 8192 (fp32) / 16384 (16-bit) elements stay in registers between the maximum
+// and the conversion and are read from memory once; longer rows are read twice
+// (the second time from L1/L2).
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
@@ -79,6 +81,48 @@ __device__ __forceinline__ uint8_t quant_one(float v, float s) {
   }
 }
 
+// Four finite values -> four packed bytes, bit-identical to four quant_one calls
+// but normally without the IEEE divisions.  q' = v * rcp(s) differs from the
+// correctly rounded quotient q = v / s by at most 2.5 ulp, so converting q'
+// gives the same byte unless a rounding boundary of the target type lies
+// within 3 ulp of q': for e4m3 the midpoints between neighbouring values (low
+// 20 mantissa bits == 0x80000) and, conservatively, everything below 2^-5
+// (subnormal spacing); for int8 (truncation) the integers.  If any of the four
+// is that close to a boundary, all four take the exact route.
+template <bool FP8>
+__device__ __forceinline__ uint32_t quant_four(const float* v, float s, float inv_s) {
+  float q[4];
+  bool risky = false;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    q[e] = v[e] * inv_s;
+    if constexpr (FP8) {
+      const uint32_t b = __float_as_uint(q[e]);
+      const uint32_t mag = b & 0x7FFFFFFFu;
+      risky |= ((b & 0xFFFFFu) - (0x80000u - 3u)) <= 6u;
+      risky |= (mag < 0x3D000000u) && (mag != 0u);
+    } else {
+      risky |= (fabsf(q[e] - rintf(q[e])) < 6.2e-5f) && (q[e] != 0.0f);
+    }
+  }
+  if (risky) {
+    uint32_t b = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) b |= static_cast<uint32_t>(quant_one<FP8>(v[e], s)) << (8 * e);
+    return b;
+  }
+  if constexpr (FP8) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+  } else {
+    uint32_t b = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) b |= (static_cast<uint32_t>(__float2int_rz(q[e])) & 0xFFu) << (8 * e);
+    return b;
+  }
+}
+
 // Single-pass form for rows of at most 256 * VEC * NV elements: every thread
 // keeps its NV vectors of the row in registers between the maximum and the
 // conversion, so the row is read from memory exactly once and all of a
@@ -104,38 +148,71 @@ __global__ void __launch_bounds__(256) pertoken_quant_row_kernel(uint8_t* __rest
       for (int e = 0; e < VEC; ++e) v[i][e] = 0.0f;
     }
   }
-  float amax = 0.0f;
+  // Row maximum on the bit patterns: for finite floats the order of |x| is the
+  // order of (bits & 0x7fffffff) as unsigned integers, and any Inf / NaN in the
+  // row shows up as a maximum >= 0x7f800000, which sends the whole row down the
+  // careful path below.  (The kernel is instruction-bound, not memory-bound, for
+  // 16-bit inputs: every instruction per element counts.)
+  uint32_t bmax = 0u;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      v[i][e] = scrub(v[i][e], QMAX);
-      amax = fmaxf(amax, fabsf(v[i][e]));
-    }
+    for (int e = 0; e < VEC; ++e) bmax = max(bmax, __float_as_uint(v[i][e]) & 0x7FFFFFFFu);
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  if (lane == 0) warp_max[warp] = amax;
+  for (int o = 16; o > 0; o >>= 1) bmax = max(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+  if (lane == 0) warp_max[warp] = __uint_as_float(bmax);
   __syncthreads();
-  float m = warp_max[lane & 7];
+  uint32_t mb = __float_as_uint(warp_max[lane & 7]);
 #pragma unroll
-  for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  float s = __fmul_rn(m, __fdiv_rn(1.0f, QMAX));
+  for (int o = 4; o > 0; o >>= 1) mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+  uint8_t* yr = y + static_cast<size_t>(r) * K;
+
+  if (mb >= 0x7F800000u) {
+    // ---- careful path: the row holds Inf or NaN (block-uniform branch) ----
+    __syncthreads();  // warp_max is reused
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        v[i][e] = scrub(v[i][e], QMAX);
+        amax = fmaxf(amax, fabsf(v[i][e]));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) warp_max[warp] = amax;
+    __syncthreads();
+    float m = warp_max[lane & 7];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = __fmul_rn(m, __fdiv_rn(1.0f, QMAX));
+    if (s == 0.0f) s = 1.0f;
+    if (threadIdx.x == 0) scale[r] = s;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int k = (i * 256 + threadIdx.x) * VEC;
+      if (k < K) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) yr[k + e] = quant_one<FP8>(v[i][e], s);
+      }
+    }
+    return;
+  }
+
+  // ---- fast path: all finite ----
+  float s = __fmul_rn(__uint_as_float(mb), __fdiv_rn(1.0f, QMAX));
   if (s == 0.0f) s = 1.0f;
   if (threadIdx.x == 0) scale[r] = s;
-  uint8_t* yr = y + static_cast<size_t>(r) * K;
+  const float inv_s = __frcp_rn(s);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int k = (i * 256 + threadIdx.x) * VEC;
     if (k < K) {
       uint32_t packed[VEC / 4];
 #pragma unroll
-      for (int w = 0; w < VEC / 4; ++w) {
-        uint32_t b = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) b |= static_cast<uint32_t>(quant_one<FP8>(v[i][4 * w + e], s)) << (8 * e);
-        packed[w] = b;
-      }
+      for (int w = 0; w < VEC / 4; ++w) packed[w] = quant_four<FP8>(&v[i][4 * w], s, inv_s);
       if constexpr (VEC == 4) {
         *reinterpret_cast<uint32_t*>(yr + k) = packed[0];
       } else {
