@@ -48,6 +48,7 @@ SIGNATURES = {
     "flyb200_layout_kind": (_i, [_i, _i, _i]),
     "flyb200_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "flyb200_read_status": (_i, [ctypes.POINTER(_i)]),
+    "flyb200_selftest_bounded_wait": (_i, [ctypes.c_uint, _vp]),
     "flyb200_strerror": (ctypes.c_char_p, [_i]),
     "flyb200_last_cuda_error": (ctypes.c_char_p, []),
     "flyb200_version": (_i, []),

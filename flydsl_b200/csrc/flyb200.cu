@@ -563,6 +563,23 @@ bool ranges_overlap(const void* a, const void* b, size_t bytes) {
   return x < y + bytes && y < x + bytes;
 }
 
+// A wait on a barrier that nothing will ever complete, with a short limit: the
+// same bounded wait the GEMM kernels use must give up, record ST_TIMEOUT in the
+// status word and let the kernel return normally (no trap, no endless loop).
+__global__ void selftest_wait_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!mbar_wait(smem_u32(&bar), 0, &abort_flag, nullptr, limit_ns)) atomicCAS(status, 0, ST_TIMEOUT);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Built-in scratch for callers that must not allocate device memory.
 //
@@ -790,6 +807,17 @@ int flyb200_pertoken_quant(void* y, float* scale, const void* x, int rows, int K
   } else {
     launch_quant<__nv_bfloat16>(yo, scale, static_cast<const __nv_bfloat16*>(x), rows, K, fp8, s);
   }
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+int flyb200_selftest_bounded_wait(unsigned int limit_us, void* stream) {
+  if (limit_us == 0 || limit_us > 100000u) return FLYB200_E_BAD_ARG;  // at most 0.1 s
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc) return rc;
+  selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st->status,
+                                                                      static_cast<unsigned long long>(limit_us) * 1000ull);
   CUDA_TRY(cudaGetLastError());
   return FLYB200_OK;
 }

@@ -82,8 +82,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 #define FLYB200_PROF_ARG(x)
 #endif
 // `waited`: optional cycle counter (profiling builds only) that receives the time spent in this wait.
+// `limit_ns`: wall-clock limit of this wait (default: FLYB200_WAIT_LIMIT_NS).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          long long* waited = nullptr) {
+                                          long long* waited = nullptr,
+                                          unsigned long long limit_ns = FLYB200_WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t_begin = waited ? clock64() : 0;
   struct Scope {
@@ -101,7 +103,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > FLYB200_WAIT_LIMIT_NS) {
+      } else if (now - t0 > limit_ns) {
         return false;
       }
     }

@@ -202,6 +202,14 @@ int flyb200_describe_plan(int M, int N, int K, int in_dtype, int variant_hint, i
  * prints runtime errors (lib/Runtime/ROCm/FlyRocmRuntimeWrappers.cpp:23-31). */
 int flyb200_read_status(int* out_status);
 
+/* Failure-path self test: launches one tiny kernel whose bounded wait (the one
+ * every GEMM kernel uses) can never be satisfied and must give up after
+ * limit_us microseconds (1..100000), set the status word to FLYB200_E_TIMEOUT
+ * and return; the device stays usable.  Read the result with
+ * flyb200_read_status.  The reference has no device-side failure reporting
+ * (lib/Runtime/ROCm/FlyRocmRuntimeWrappers.cpp:23-31 prints host errors only). */
+int flyb200_selftest_bounded_wait(unsigned int limit_us, void* stream);
+
 const char* flyb200_strerror(int code);
 const char* flyb200_last_cuda_error(void);
 int flyb200_version(void);

@@ -346,3 +346,68 @@ def test_fp16_output(dev, in_dtype, m):
     got = run_gemm_generic(dev, a, b, sa, sb, None, m, n, k, in_dtype, out_dtype="fp16")
     ref = oracle.run_torch(a, b, sa, sb)
     assert oracle.strict_mismatches(got, ref, RTOL, ATOL) == 0
+
+
+# --- failure path: a bounded device-side wait that cannot succeed
+
+
+def test_bounded_wait_expires_and_reports(dev):
+    """A wait on a barrier that nothing completes gives up after its limit, the
+    kernel returns normally with FLYB200_E_TIMEOUT in the status word, and the
+    device keeps working (no trap, no hang)."""
+    import time
+
+    lib = _lib.load()
+    assert device_status() == 0
+    t0 = time.perf_counter()
+    _lib.check(lib.flyb200_selftest_bounded_wait(20000, torch.cuda.current_stream().cuda_stream), "selftest")  # 20 ms
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    assert 0.015 < elapsed < 2.0, elapsed
+    assert device_status() == _lib.E_TIMEOUT
+    assert device_status() == 0  # reading clears the word
+    assert lib.flyb200_selftest_bounded_wait(0, None) == _lib.E_BAD_ARG
+    assert lib.flyb200_selftest_bounded_wait(10**6, None) == _lib.E_BAD_ARG
+    # the context is still good: a GEMM right after gives exact results
+    a_q, b_q, _, _ = oracle.make_inputs(16, 256, 512, "int8", seed=1)
+    acc = gpu_acc(a_q.to(dev), shuffle_weight(b_q.to(dev)), 16, 256, 512, "int8")
+    assert torch.equal(acc.cpu(), oracle.int32_acc(a_q, b_q))
+    assert device_status() == 0
+
+
+@pytest.mark.parametrize("in_dtype", ["bf16", "int8"])
+def test_cudagraph_capture_other_dtypes(dev, in_dtype):
+    """Graph capture for the 16-bit path (the reference captures bf16 and fp8) and for INT8."""
+    m, n, k = 1, 8192, 8192
+    g = torch.Generator().manual_seed(5)
+    if in_dtype == "bf16":
+        a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev)
+        b = shuffle_weight(torch.randn(n, k, generator=g).to(torch.bfloat16).to(dev))
+        sa = sb = torch.empty(0, dtype=torch.float32, device=dev)
+    else:
+        a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "int8", seed=6)
+        a, b, sa, sb = a_q.to(dev), shuffle_weight(b_q.to(dev)), sa.to(dev), sb.to(dev)
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype=in_dtype)
+    bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    c = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+    args = lambda: (c.view(-1), a.view(-1), b.view(-1), sa, sb, bias, m, n, torch.cuda.current_stream())  # noqa: E731
+    cf = flyc.compile(fn, *args())
+    cf(*args())
+    torch.cuda.synchronize()
+    ref = c.clone()
+    assert ref.abs().max().item() > 0
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        cf(*args())
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=s):
+        cf(*args())
+        cf(*args())  # back to back inside one graph: the dependent-launch edge is captured too
+    c.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(ref, c)
+    assert device_status() == 0
