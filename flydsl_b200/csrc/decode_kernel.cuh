@@ -27,10 +27,10 @@ constexpr int MAX_CLUSTER_SPLIT = 8;
 struct DecodeLayout {
   int off_w, off_a, off_bar, off_misc, off_sa, total;
 };
-__host__ __device__ inline DecodeLayout decode_layout(int bn, int stages) {
+__host__ __device__ inline DecodeLayout decode_layout(int bn, int stages, int w_rows = BLOCK_ROWS) {
   DecodeLayout l;
   l.off_w = 0;
-  l.off_a = stages * BLOCK_ROWS * KBLOCK_BYTES;
+  l.off_a = stages * w_rows * KBLOCK_BYTES;
   l.off_bar = l.off_a + stages * bn * KBLOCK_BYTES;
   l.off_misc = l.off_bar + 8 * (2 * stages + 1);
   l.off_misc = (l.off_misc + 15) & ~15;
@@ -142,15 +142,21 @@ __device__ __forceinline__ void cluster_reduce_slice(const GemmParams& p, uint32
   }
 }
 
-template <int KIND, int BN, int OUTMODE>
+// WROWS: output channels per CTA = UMMA M.  128 is the general form.  64 halves
+// the weight tile so that twice as many CTAs stream without any K split (and so
+// without a reduction step); its accumulator uses TMEM lanes 0-15 of each
+// 32-lane quadrant (row r of the tile sits in lane (r % 16) + 32 * (r / 16)),
+// and it supports REDUCE_NONE only.
+template <int KIND, int BN, int OUTMODE, int WROWS = BLOCK_ROWS>
 __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const GemmParams p) {
+  static_assert(WROWS == 128 || WROWS == 64, "weight tile of 128 or 64 channels");
   using KT = KindTraits<KIND>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = smem_u32(smem_raw);
   const int stages = p.stages;
-  const DecodeLayout L = decode_layout(BN, stages);
-  constexpr int W_STAGE = BLOCK_ROWS * KBLOCK_BYTES;
+  const DecodeLayout L = decode_layout(BN, stages, WROWS);
+  constexpr int W_STAGE = WROWS * KBLOCK_BYTES;
   constexpr int A_STAGE = BN * KBLOCK_BYTES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L.off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L.off_misc + 4);
@@ -167,7 +173,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_SMEM_ALIGN);
     return;
   }
-  const int n0 = blockIdx.x * BLOCK_ROWS;
+  const int n0 = blockIdx.x * WROWS;
   // grid.z splits the tokens into blocks of BN: each CTA sees only its own block
   const int m_base = blockIdx.z * BN;
   const int M_loc = min(BN, p.M - m_base);  // >= 1 by construction of the grid
@@ -177,7 +183,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
   const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
   const int num_kb = kb_end - kb_begin;  // >= 1 by construction of the grid
   const bool scaled = (p.sa != nullptr) && (p.sb != nullptr);
-  const uint32_t w_rows = static_cast<uint32_t>(min(BLOCK_ROWS, p.N - n0));
+  const uint32_t w_rows = static_cast<uint32_t>(min(WROWS, p.N - n0));
   const uint32_t w_bytes = w_rows * KBLOCK_BYTES;
   const int pre = min(stages, num_kb);  // k-blocks whose loads are issued before the CTA-wide set-up finishes
   bool ok = true;
@@ -276,7 +282,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
   } else if (warp == 1) {
     // ------------------------------ MMA issue -----------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, BLOCK_ROWS, BN);
+      constexpr uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, WROWS, BN);
       int stage = 0;
       uint32_t phase = 0;
       for (int kb = 0; kb < num_kb; ++kb) {
@@ -309,8 +315,10 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
   // ------------------------------ epilogue --------------------------------
   // thread <-> output channel (TMEM lane), registers <-> tokens
   const int q = warp & 3;
-  const int ch_local = q * 32 + lane;
-  const int n = n0 + ch_local;
+  // channel of this thread; with 64-channel tiles only lanes 0-15 of a quadrant hold rows
+  const int ch_local = WROWS == 128 ? q * 32 + lane : q * 16 + (lane & 15);
+  const bool lane_has_row = WROWS == 128 || lane < 16;
+  const int n = lane_has_row ? n0 + ch_local : p.N;  // p.N: out of range, never stored
   const uint32_t red_base = smem_base;  // partial tile [BN][128] words, reuses the (by then idle) ring
   float sb_v = 0.0f, bias_v = 0.0f;
   constexpr int CH = 16;  // tokens per TMEM load

@@ -230,19 +230,26 @@ int launch_rows_scatter(const CUtensorMap& tmA, const OutputMaps& outs, const Ge
 
 constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 
-inline int default_decode_stages(int bn) { return bn <= 32 ? 8 : (bn <= 128 ? 6 : 4); }
+// Ring depth of the small-M kernel: as deep as ~200 KB of shared memory allow, at most 12.
+inline int default_decode_stages(int bn, int w_rows = BLOCK_ROWS) {
+  if (w_rows == BLOCK_ROWS) return bn <= 32 ? 8 : (bn <= 128 ? 6 : 4);
+  const int stage = (w_rows + bn) * KBLOCK_BYTES;
+  int n = 200 * 1024 / stage;
+  return n > 12 ? 12 : (n < 2 ? 2 : n);
+}
 
-template <int KIND, int BN, int OUTMODE>
+template <int KIND, int BN, int OUTMODE, int WROWS = BLOCK_ROWS>
 int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
   static std::atomic<uint64_t> done{0};
-  auto kernel = gemm_decode_kernel<KIND, BN, OUTMODE>;
+  auto kernel = gemm_decode_kernel<KIND, BN, OUTMODE, WROWS>;
   int rc = ensure_smem(kernel, SMEM_LIMIT, done);
   if (rc) return rc;
-  const DecodeLayout L = decode_layout(BN, p.stages);
+  const DecodeLayout L = decode_layout(BN, p.stages, WROWS);
   if (L.total > SMEM_LIMIT || BN * BLOCK_ROWS * 4 > L.off_bar) return FLYB200_E_UNSUPPORTED;
+  if (WROWS != BLOCK_ROWS && p.reduce_mode != REDUCE_NONE) return FLYB200_E_UNSUPPORTED;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((p.N + BLOCK_ROWS - 1) / BLOCK_ROWS, p.split_k, p.token_blocks < 1 ? 1 : p.token_blocks);
+  cfg.gridDim = dim3((p.N + WROWS - 1) / WROWS, p.split_k, p.token_blocks < 1 ? 1 : p.token_blocks);
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = L.total;
   cfg.stream = s;
@@ -267,7 +274,15 @@ int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
 }
 
 template <int KIND, int OUTMODE>
-int launch_decode_bn(int bn, const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
+int launch_decode_bn(int bn, int w_rows, const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
+  if (w_rows == 64) {  // half-height weight tiles: built for the token counts where they pay off
+    switch (bn) {
+      case 16: return launch_decode<KIND, 16, OUTMODE, 64>(tmA, p, s);
+      case 32: return launch_decode<KIND, 32, OUTMODE, 64>(tmA, p, s);
+      case 64: return launch_decode<KIND, 64, OUTMODE, 64>(tmA, p, s);
+    }
+    return FLYB200_E_UNSUPPORTED;
+  }
   switch (bn) {
     case 16: return launch_decode<KIND, 16, OUTMODE>(tmA, p, s);
     case 32: return launch_decode<KIND, 32, OUTMODE>(tmA, p, s);
@@ -302,6 +317,7 @@ struct Plan {
   bool decode;
   bool two_sm;  // large-M kernel as CTA pairs (tcgen05 cta_group::2)
   int token_blocks;  // small-M kernel: the tokens are split into this many blocks of bn (grid.z)
+  int w_rows;        // small-M kernel: output channels per CTA (128, or 64 without any K split)
   int bn;
   int split_k;
   int kb_per_split;
@@ -319,6 +335,18 @@ int pdl_default() {
     return e[0] == '1' ? 1 : e[0] == '2' ? 2 : 0;
   }();
   return mode;
+}
+
+bool w64_default() {
+  static const bool on = []() {
+    // Off unless asked for: with one CTA streaming a tile's whole K range the
+    // single MMA-issuing thread (about 290 cycles per k-block) becomes the limit;
+    // measured 21 us against 14.5 us for 128-channel tiles with split-K 2
+    // (M = 32, N = K = 8192).
+    const char* e = getenv("FLYB200_DECODE_W64");
+    return e && e[0] == '1';
+  }();
+  return on;
 }
 
 bool rows_two_sm_default() {
@@ -355,13 +383,14 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   const int want_kernel = hint_kernel(variant_hint);
   const int want_split = hint_split(variant_hint);
   const int want_reduce = hint_reduce(variant_hint);
-  if (want_kernel > 3) return FLYB200_E_BAD_ARG;
-  plan->decode = want_kernel == 1 ? true : want_kernel >= 2 ? false : (M <= 256);
+  if (want_kernel > 4) return FLYB200_E_BAD_ARG;
+  plan->decode = (want_kernel == 1 || want_kernel == 4) ? true : want_kernel >= 2 ? false : (M <= 256);
   plan->two_sm = want_kernel == 3 ? true : want_kernel == 2 ? false : rows_two_sm_default();
   if (plan->decode && M > 256) return FLYB200_E_UNSUPPORTED;
   if (want_reduce > REDUCE_CLUSTER) return FLYB200_E_BAD_ARG;
   plan->token_blocks = 1;
   plan->bn = ROWS_BN;
+  plan->w_rows = BLOCK_ROWS;
   if (plan->decode) {
     const int ht = hint_tokens(variant_hint);
     int t = ht == 0 ? auto_token_blocks(M, N, sms) : (ht == 1 ? 1 : ht == 2 ? 2 : 4);
@@ -371,13 +400,25 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   plan->group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : (plan->two_sm ? 8 : 16);
   plan->split_k = 1;
   plan->reduce_mode = REDUCE_NONE;
-  plan->stages = hint_stages(variant_hint) >= 2 ? hint_stages(variant_hint) : default_decode_stages(plan->bn);
+  if (plan->decode) {
+    // 64-channel tiles: when they alone put one CTA on (nearly) every SM, no K
+    // split and therefore no reduction step is needed.
+    const int tiles64 = (N + 63) / 64;
+    const bool fits = plan->bn <= 64 && plan->token_blocks == 1;
+    const bool wanted = want_kernel == 4;
+    const bool automatic = want_kernel == 0 && want_split == 0 && want_reduce == 0 && tiles64 <= sms &&
+                           4 * tiles64 >= 3 * sms && w64_default();
+    if (wanted && (!fits || want_split > 1 || want_reduce != 0)) return FLYB200_E_UNSUPPORTED;
+    if (fits && (wanted || automatic)) plan->w_rows = 64;
+  }
+  plan->stages = hint_stages(variant_hint) >= 2 ? hint_stages(variant_hint) : default_decode_stages(plan->bn, plan->w_rows);
   const int hp = hint_pdl(variant_hint);
   plan->pdl = hp == 1 ? 1 : hp == 2 ? 0 : hp == 3 ? 2 : pdl_default();
   const int kb = K_bytes / KBLOCK_BYTES;
   plan->kb_per_split = kb;
   if (plan->decode) {
     int split = want_split > 0 ? want_split : auto_split_k(N, K_bytes, sms, plan->token_blocks);
+    if (plan->w_rows == 64) split = 1;
     if (split > kb) split = kb;
     int mode = REDUCE_NONE;
     if (split > 1) {
@@ -403,7 +444,7 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
 template <int KIND, int OUTMODE>
 int run_kind(const Plan& plan, const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmC,
              const GemmParams& p, int sms, cudaStream_t s) {
-  if (plan.decode) return launch_decode_bn<KIND, OUTMODE>(plan.bn, tmA, p, s);
+  if (plan.decode) return launch_decode_bn<KIND, OUTMODE>(plan.bn, plan.w_rows, tmA, p, s);
   if (plan.two_sm) return launch_rows2<KIND, OUTMODE>(tmA, tmW, tmC, p, sms, s);
   return launch_rows<KIND, OUTMODE>(tmA, tmC, p, sms, s);
 }
@@ -831,7 +872,7 @@ int flyb200_describe_plan(int M, int N, int K, int in_dtype, int variant_hint, i
   // planned as with an unlimited workspace: the answer says what would be needed
   int rc = make_plan(&plan, M, N, K * eb, variant_hint, static_cast<size_t>(-1) >> 1, true, sm_count);
   if (rc) return rc;
-  out8[0] = plan.decode ? 1 : (plan.two_sm ? 3 : 2);
+  out8[0] = plan.decode ? (plan.w_rows == 64 ? 4 : 1) : (plan.two_sm ? 3 : 2);
   out8[1] = plan.bn;
   out8[2] = plan.split_k;
   out8[3] = plan.kb_per_split;

@@ -58,7 +58,11 @@ extern "C" {
  *   bits 8-11  kernel: 1 = small-M weight-stationary kernel (M <= 256),
  *              2 = large-M persistent kernel, one CTA per 128x256 tile,
  *              3 = large-M persistent kernel, CTA pairs on 256x256 tiles
- *              (automatic: 1 for M <= 256, else 2; 3 when FLYB200_ROWS_2SM=1)
+ *              4 = small-M kernel with 64-channel weight tiles and no K split
+ *              (M <= 64 per token block; twice the CTAs, no reduction step)
+ *              (automatic: M <= 256 -> 1, or 4 when FLYB200_DECODE_W64=1 and the
+ *              N/64 tiles fill 75-100 % of the SMs; else 2, or 3 when
+ *              FLYB200_ROWS_2SM=1)
  *   bits 12-15 how K splits are combined: 1 = global workspace + ticket,
  *              2 = thread-block cluster + distributed shared memory (split <= 8)
  *   bits 16-23 rasterisation group (row tiles per group, large-M kernel)

@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 
 RTOL = ATOL = 1e-2  # stated tolerance for fp8 / scaled outputs against the fp32 reference
 SENTINEL = -8192.0
-DEC, ROWS, ROWS2 = 1 << 8, 2 << 8, 3 << 8  # variant_hint: kernel field (small-M, large-M, large-M as CTA pairs)
+DEC, ROWS, ROWS2, W64 = 1 << 8, 2 << 8, 3 << 8, 4 << 8  # variant_hint: kernel field (small-M, large-M, large-M as CTA pairs, small-M with 64-channel tiles)
 WS, CL = 1 << 12, 2 << 12  # variant_hint: split-K reduction through a global workspace / a cluster
 PDL = 1 << 28  # variant_hint: programmatic dependent launch
 TOK1, TOK2, TOK4 = 1 << 30, 2 << 30, (3 << 30) - (1 << 32)  # variant_hint: token blocks (as signed 32-bit)
@@ -94,12 +94,14 @@ def test_scaled_output_matches_reference_check(dev, in_dtype, m, n, k, tile):
 @pytest.mark.parametrize(
     "hint",
     [DEC | 1, DEC | CL | 2, DEC | CL | 5, DEC | CL | 8, DEC | WS | 3, DEC | WS | 16, DEC | 2 | STAGES(3), DEC | 2 | PDL,
-     DEC | 2 | (2 << 28), DEC | TOK1 | 2, DEC | TOK2, DEC | TOK4, DEC | TOK2 | CL | 2, DEC | TOK4 | WS | 3, ROWS, ROWS2],
-    ids=["nosplit", "cluster2", "cluster5", "cluster8", "ws3", "ws16", "stages3", "pdl", "nopdl", "tok1", "tok2", "tok4",
+     DEC | 2 | (2 << 28), W64, W64 | STAGES(3), DEC | TOK1 | 2, DEC | TOK2, DEC | TOK4, DEC | TOK2 | CL | 2, DEC | TOK4 | WS | 3, ROWS, ROWS2],
+    ids=["nosplit", "cluster2", "cluster5", "cluster8", "ws3", "ws16", "stages3", "pdl", "nopdl", "w64", "w64_stages3", "tok1", "tok2", "tok4",
          "tok2_cluster2", "tok4_ws3", "rows", "rows2"],
 )
 @pytest.mark.parametrize("m", [1, 16, 17, 64, 100, 256])
 def test_every_kernel_variant_small_m(dev, hint, m):
+    if (hint & 0xF00) == W64 and m > 64:
+        pytest.skip("64-channel tiles are built for up to 64 tokens")
     n, k = 1040, 2048
     a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "fp8", seed=77 + m)
     c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, "fp8", hint=hint)
@@ -122,6 +124,9 @@ def test_cta_pair_kernel_scaled_output(dev, in_dtype, m, n, k):
     [
         (32, 8192, 8192, 0),  # benchmark config 2, automatic variant
         (32, 8192, 8192, DEC | 1),
+        (32, 8192, 8192, W64),
+        (7, 144, 1024, W64),
+        (64, 1040, 2048, W64),
         (32, 8192, 8192, DEC | CL | 4),
         (32, 8192, 8192, DEC | WS | 4),
         (7, 144, 1024, DEC | WS | 3),

@@ -155,9 +155,15 @@ def test_variant_selection_is_a_pure_host_function():
     table) can be inspected without a GPU."""
     d = _lib.describe_plan
     # decode shapes at N = K = 8192 on 148 SMs: 64 channel tiles x split-K 2 as clusters
-    p = d(32, 8192, 8192, "int8")
+    p = d(32, 8192, 8192, "int8", variant_hint=1 << 8)
     assert (p["kernel"], p["bn"], p["split_k"], p["reduce"], p["token_blocks"]) == (1, 32, 2, 2, 1)
     assert p["split_k"] * p["kb_per_split"] >= 64
+    assert d(32, 8192, 8192, "int8")["kernel"] == 1  # also the automatic choice
+    # ... or, on request, 128 tiles of 64 channels with no split at all
+    p = d(32, 8192, 8192, "int8", variant_hint=4 << 8)
+    assert (p["kernel"], p["bn"], p["split_k"], p["reduce"]) == (4, 32, 1, 0)
+    with pytest.raises(_lib.FlyB200Error):
+        d(128, 8192, 8192, variant_hint=4 << 8)  # too many tokens for the half-height tiles
     assert d(1, 8192, 8192)["bn"] == 16 and d(17, 8192, 8192)["bn"] == 32 and d(256, 8192, 8192)["bn"] == 256
     # more channel tiles than SMs: no split
     assert d(8, 57344, 8192)["split_k"] == 1 and d(8, 57344, 8192)["reduce"] == 0
@@ -174,4 +180,4 @@ def test_variant_selection_is_a_pure_host_function():
     # a single k-block cannot be split
     assert d(16, 1024, 128)["split_k"] == 1
     # fewer SMs -> smaller split
-    assert d(32, 8192, 8192, sm_count=64)["split_k"] == 1
+    assert d(32, 8192, 8192, sm_count=64, variant_hint=1 << 8)["split_k"] == 1
