@@ -21,6 +21,8 @@
 namespace flyb200 {
 
 enum : int { REDUCE_NONE = 0, REDUCE_WORKSPACE = 1, REDUCE_CLUSTER = 2 };
+// warp 0 producer, warp 1 MMA issuer (even k-blocks), warps 2..5 epilogue, warp 6 MMA issuer (odd k-blocks)
+constexpr int DECODE_THREADS = 224;
 constexpr int MAX_CLUSTER_SPLIT = 8;
 
 // Shared-memory carve-up for a given ring depth (computed identically on host and device).
@@ -148,7 +150,7 @@ __device__ __forceinline__ void cluster_reduce_slice(const GemmParams& p, uint32
 // 32-lane quadrant (row r of the tile sits in lane (r % 16) + 32 * (r / 16)),
 // and it supports REDUCE_NONE only.
 template <int KIND, int BN, int OUTMODE, int WROWS = BLOCK_ROWS>
-__global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA,
+__global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const GemmParams p) {
   static_assert(WROWS == 128 || WROWS == 64, "weight tile of 128 or 64 channels");
   using KT = KindTraits<KIND>;
@@ -208,7 +210,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_tfull, 1);
+    mbar_init(bar_tfull, num_kb >= 2 ? 2 : 1);  // one commit per MMA issuer that has k-blocks
     abort_flag[0] = 0;
     abort_flag[1] = 0;  // stays zero: lets the drain below wait on time alone
     fence_mbar_init();
@@ -228,7 +230,11 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     for (int i = 0; i < pre; ++i)
       tma_load_2d(smem_base + L.off_a + i * A_STAGE, &tmA, bar_full + 8 * i, (kb_begin + i) * KBLOCK_BYTES, m_base, pol_a);
   }
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  // Two accumulators (columns [0, BN) and [BN, 2 BN)): even k-blocks are issued by
+  // warp 1 into the first, odd k-blocks by warp 6 into the second, so that the
+  // ~290 cycles one thread needs to issue a k-block's MMAs are spent by two
+  // threads in parallel; the epilogue adds the two.
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
@@ -279,13 +285,15 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 6) {
     // ------------------------------ MMA issue -----------------------------
-    if (lane == 0) {
+    const int which = warp == 1 ? 0 : 1;  // issuer 0: k-blocks 0, 2, 4, ...; issuer 1: 1, 3, 5, ...
+    if (lane == 0 && which < num_kb) {
       constexpr uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, WROWS, BN);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(which * BN);
+      for (int kb = which; kb < num_kb; kb += 2) {
+        const int stage = kb % stages;
+        const uint32_t phase = static_cast<uint32_t>(kb / stages) & 1u;
         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
           report_failure(p.status, ST_TIMEOUT, abort_flag);
           ok = false;
@@ -297,16 +305,12 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
         const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L.off_a + stage * A_STAGE);
 #pragma unroll
         for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
-          umma_ss<KIND>(tmem_base, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
-                        adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_ss<KIND>(d_tmem, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                        adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb >= 2 || k != 0) ? 1u : 0u);
         }
         umma_commit(bar_empty + 8 * stage);
-        if (++stage == stages) {
-          stage = 0;
-          phase ^= 1u;
-        }
       }
-      FLYB200_STAMP(2);  // last MMA issued (all stages landed)
+      if (which == 0) FLYB200_STAMP(2);  // last MMA of this issuer issued
       if (ok) umma_commit(bar_tfull);
     }
     __syncwarp();
@@ -322,6 +326,20 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
   const uint32_t red_base = smem_base;  // partial tile [BN][128] words, reuses the (by then idle) ring
   float sb_v = 0.0f, bias_v = 0.0f;
   constexpr int CH = 16;  // tokens per TMEM load
+  const bool two_acc = num_kb >= 2;
+  // accumulator columns [c0, c0 + 16) of this thread's lane: first plus (if used) second accumulator
+  auto load_acc = [&](uint32_t t_row, int c0, uint32_t (&r)[CH]) {
+    tmem_ld_x16(t_row + c0, r);
+    if (two_acc) {
+      uint32_t r2[CH];
+      tmem_ld_x16(t_row + BN + c0, r2);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < CH; ++j) r[j] = add_raw<KT::is_int>(r[j], r2[j]);
+    } else {
+      tmem_ld_wait();
+    }
+  };
 
   auto emit = [&](int m, uint32_t raw) {
     if (m < M_loc && n < p.N) {
@@ -334,7 +352,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     }
   };
 
-  if (warp >= 2) {
+  if (warp >= 2 && warp <= 5) {
     // epilogue operands, fetched while the weight stream runs
     const int et = threadIdx.x - 64;
     for (int i = et; i < BN; i += 128) sa_s[i] = (scaled && i < M_loc) ? __ldg(p.sa + m_base + i) : 0.0f;
@@ -355,8 +373,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
         for (int c0 = 0; c0 < BN; c0 += CH) {
           if (c0 >= M_loc) break;
           uint32_t r[CH];
-          tmem_ld_x16(t_row + c0, r);
-          tmem_ld_wait();
+          load_acc(t_row, c0, r);
 #pragma unroll
           for (int j = 0; j < CH; ++j) emit(c0 + j, r[j]);
         }
@@ -365,8 +382,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
         for (int c0 = 0; c0 < BN; c0 += CH) {
           if (c0 >= M_loc) break;
           uint32_t r[CH];
-          tmem_ld_x16(t_row + c0, r);
-          tmem_ld_wait();
+          load_acc(t_row, c0, r);
 #pragma unroll
           for (int j = 0; j < CH; ++j) st_smem(red_base + static_cast<uint32_t>(((c0 + j) * BLOCK_ROWS + ch_local) * 4), r[j]);
         }
@@ -380,8 +396,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
         for (int c0 = 0; c0 < BN; c0 += CH) {
           if (c0 >= M_loc) break;
           uint32_t r[CH];
-          tmem_ld_x16(t_row + c0, r);
-          tmem_ld_wait();
+          load_acc(t_row, c0, r);
 #pragma unroll
           for (int j = 0; j < CH; ++j) __stcg(mine + static_cast<size_t>(c0 + j) * BLOCK_ROWS, r[j]);
         }
@@ -433,7 +448,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_decode_kernel(const __grid_c
     // wait (all waits above are bounded), so the cluster barriers always complete.
     tc_fence_before();
     cluster_sync_all();
-    if (warp >= 2 && ok) {
+    if (warp >= 2 && warp <= 5 && ok) {
       // Reduce-scatter over the cluster: this CTA owns a slice of the tokens.
       // A warp takes one token at a time and each lane four consecutive
       // channels, so every peer read is one 16-byte load and every output row

@@ -250,7 +250,7 @@ int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((p.N + WROWS - 1) / WROWS, p.split_k, p.token_blocks < 1 ? 1 : p.token_blocks);
-  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.blockDim = dim3(DECODE_THREADS, 1, 1);
   cfg.dynamicSmemBytes = L.total;
   cfg.stream = s;
   cudaLaunchAttribute attrs[2];

@@ -27,6 +27,8 @@ def gpu_inputs(m, n, k, dev, seed, weight_scale=1.0):
     [
         (8192, 28672, 8192, 0.02),  # benchmark config 3 (prefill, MLP up-projection)
         (5133, 5120, 8320, 1.0),  # the reference's ragged large shape
+        (5120, 2048, 8320, 1.0),  # reference large shape, narrow N
+        (9728, 8192, 8320, 1.0),  # reference large shape (its int8 benchmark shape, here fp8)
         (16384, 8192, 8192, 1.0),  # top of the M sweep
     ],
 )
@@ -84,3 +86,21 @@ def test_int8_large_accumulators_exact_on_sample():
     col_sum = acc.to(torch.int64).sum(dim=0).cpu()
     want_sum = (a_q.to(torch.float64).sum(dim=0, keepdim=True).cpu() @ b_q.to(torch.float64).cpu().T).to(torch.int64).view(-1)
     assert torch.equal(col_sum, want_sum)
+
+
+def test_cta_pair_kernel_matches_single_cta_kernel_at_full_size():
+    """Both large-M kernels accumulate each output in the same k order, so their bf16 outputs are bitwise equal."""
+    dev = torch.device("cuda:0")
+    m, n, k = 4096, 8192, 8192
+    a_q, b_q, sa, sb = gpu_inputs(m, n, k, dev, seed=77)
+    b_shuf = shuffle_weight(b_q)
+    bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    outs = []
+    for hint in (2 << 8, 3 << 8):
+        fn = compile_preshuffle_gemm(N=n, K=k, tile_m=128, tile_n=256, tile_k=128, in_dtype="fp8", variant_hint=hint)
+        c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        fn(c.view(-1), as_i8(a_q).view(-1), as_i8(b_shuf).view(-1), sa, sb, bias, m, n, torch.cuda.current_stream())
+        outs.append(c)
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert torch.equal(outs[0], outs[1])
