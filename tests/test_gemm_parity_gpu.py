@@ -126,6 +126,10 @@ def test_cta_pair_kernel_scaled_output(dev, in_dtype, m, n, k):
         (32, 8192, 8192, DEC | 1),
         (32, 8192, 8192, W64),
         (7, 144, 1024, W64),
+        (16, 256, 128, DEC | 1),  # a single k-block: only one of the two MMA issuers has work
+        (16, 256, 384, DEC | 1),  # three k-blocks: uneven share between the issuers
+        (16, 256, 384, DEC | CL | 3),  # one k-block per split
+        (40, 272, 640, W64),
         (64, 1040, 2048, W64),
         (32, 8192, 8192, DEC | CL | 4),
         (32, 8192, 8192, DEC | WS | 4),
