@@ -86,6 +86,25 @@ __device__ __forceinline__ void st_smem(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
+// Epilogue and store of four consecutive channels of token m (raw sums in `acc`).
+template <int KIND, int OUTMODE>
+__device__ __forceinline__ void store_reduced(const GemmParams& p, const uint4& acc, int m, int m_base, int n4,
+                                              const float* sa_s, const float (&sb4)[4], const float (&bias4)[4],
+                                              bool scaled) {
+  using KT = KindTraits<KIND>;
+  if constexpr (OUTMODE == OUT_RAW32) {
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(p.c) + static_cast<size_t>(m_base + m) * p.N + n4) = acc;
+  } else {
+    const float sa_v = sa_s[m];
+    const float v0 = epilogue_value<KT::is_int>(acc.x, sa_v, sb4[0], bias4[0], p.epilogue, scaled);
+    const float v1 = epilogue_value<KT::is_int>(acc.y, sa_v, sb4[1], bias4[1], p.epilogue, scaled);
+    const float v2 = epilogue_value<KT::is_int>(acc.z, sa_v, sb4[2], bias4[2], p.epilogue, scaled);
+    const float v3 = epilogue_value<KT::is_int>(acc.w, sa_v, sb4[3], bias4[3], p.epilogue, scaled);
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.c) + static_cast<size_t>(m_base + m) * p.N + n4) =
+        make_uint2(pack2<OUTMODE>(v0, v1), pack2<OUTMODE>(v2, v3));
+  }
+}
+
 // Sum, in the fixed order s = 0..S-1, the partial tiles of the S CTAs of the
 // cluster for the tokens m_first, m_first+4, ... < m_end and four consecutive
 // channels, apply the epilogue and store.  All S*U peer reads of an iteration
@@ -127,19 +146,7 @@ __device__ __forceinline__ void cluster_reduce_slice(const GemmParams& p, uint32
           acc.w = add_raw<KT::is_int>(acc.w, v[s][j].w);
         }
       }
-      if (m < m_end && col_ok) {
-        if constexpr (OUTMODE == OUT_RAW32) {
-          *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(p.c) + static_cast<size_t>(m_base + m) * p.N + n4) = acc;
-        } else {
-          const float sa_v = sa_s[m];
-          const float v0 = epilogue_value<KT::is_int>(acc.x, sa_v, sb4[0], bias4[0], p.epilogue, scaled);
-          const float v1 = epilogue_value<KT::is_int>(acc.y, sa_v, sb4[1], bias4[1], p.epilogue, scaled);
-          const float v2 = epilogue_value<KT::is_int>(acc.z, sa_v, sb4[2], bias4[2], p.epilogue, scaled);
-          const float v3 = epilogue_value<KT::is_int>(acc.w, sa_v, sb4[3], bias4[3], p.epilogue, scaled);
-          *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.c) + static_cast<size_t>(m_base + m) * p.N + n4) =
-              make_uint2(pack2<OUTMODE>(v0, v1), pack2<OUTMODE>(v2, v3));
-        }
-      }
+      if (m < m_end && col_ok) store_reduced<KIND, OUTMODE>(p, acc, m, m_base, n4, sa_s, sb4, bias4, scaled);
     }
   }
 }
@@ -200,7 +207,13 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
 #ifdef FLYB200_PROFILE
   const unsigned long long prof_t0 = globaltimer_ns();
   if (threadIdx.x == 0) atomicMin(p.prof + 0, prof_t0);
-#define FLYB200_STAMP(idx) atomicAdd(p.prof + (idx), globaltimer_ns() - prof_t0)
+  // prof[idx]: sum over CTAs of the time since the CTA's own start; prof[8 + idx]: latest absolute time
+#define FLYB200_STAMP(idx)                            \
+  do {                                                \
+    const unsigned long long now_ = globaltimer_ns(); \
+    atomicAdd(p.prof + (idx), now_ - prof_t0);        \
+    atomicMax(p.prof + 8 + (idx), now_);              \
+  } while (0)
 #else
 #define FLYB200_STAMP(idx)
 #endif
@@ -325,6 +338,8 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
   const int n = lane_has_row ? n0 + ch_local : p.N;  // p.N: out of range, never stored
   const uint32_t red_base = smem_base;  // partial tile [BN][128] words, reuses the (by then idle) ring
   float sb_v = 0.0f, bias_v = 0.0f;
+  // the same operands for the four consecutive channels a thread owns in the cluster reduce
+  float sb4[4] = {0.f, 0.f, 0.f, 0.f}, bias4[4] = {0.f, 0.f, 0.f, 0.f};
   constexpr int CH = 16;  // tokens per TMEM load
   const bool two_acc = num_kb >= 2;
   // accumulator columns [c0, c0 + 16) of this thread's lane: first plus (if used) second accumulator
@@ -358,6 +373,13 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
     for (int i = et; i < BN; i += 128) sa_s[i] = (scaled && i < M_loc) ? __ldg(p.sa + m_base + i) : 0.0f;
     sb_v = (scaled && n < p.N) ? __ldg(p.sb + n) : 0.0f;
     bias_v = (p.epilogue != EPI_NONE && n < p.N) ? load_bias<OUTMODE>(p.bias, n) : 0.0f;
+    if (p.reduce_mode == REDUCE_CLUSTER && n0 + lane * 4 < p.N) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (scaled) sb4[e] = __ldg(p.sb + n0 + lane * 4 + e);
+        if (p.epilogue != EPI_NONE) bias4[e] = load_bias<OUTMODE>(p.bias, n0 + lane * 4 + e);
+      }
+    }
     named_bar_sync(1, 128);
 
     ok = mbar_wait(bar_tfull, 0, abort_flag);
@@ -462,14 +484,6 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
       const int ch4 = lane * 4;
       const int n4 = n0 + ch4;
       const bool col_ok = n4 < p.N;  // N is a multiple of 4: the four channels are in or out together
-      float sb4[4] = {0.f, 0.f, 0.f, 0.f}, bias4[4] = {0.f, 0.f, 0.f, 0.f};
-      if (col_ok) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (scaled) sb4[e] = __ldg(p.sb + n4 + e);
-          if (p.epilogue != EPI_NONE) bias4[e] = load_bias<OUTMODE>(p.bias, n4 + e);
-        }
-      }
       const uint32_t red_mine = red_base + static_cast<uint32_t>(ch4 * 4);
       const int m_first = m_begin + (warp - 2);
       // sixteen 16-byte loads in flight per thread whatever the split

@@ -412,6 +412,14 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     if (fits && (wanted || automatic)) plan->w_rows = 64;
   }
   plan->stages = hint_stages(variant_hint) >= 2 ? hint_stages(variant_hint) : default_decode_stages(plan->bn, plan->w_rows);
+  // The two MMA issuers take alternate k-blocks.  With an even ring depth a stage
+  // always belongs to the same issuer, so its full-barrier is never more than
+  // one phase ahead of the thread waiting on it (a parity wait cannot tell
+  // phase n from phase n + 2).  An odd depth becomes the next even one, or the
+  // one below when that does not fit into shared memory.
+  if (plan->stages & 1) {
+    plan->stages += decode_layout(plan->bn, plan->stages + 1, plan->w_rows).total <= SMEM_LIMIT ? 1 : -1;
+  }
   const int hp = hint_pdl(variant_hint);
   plan->pdl = hp == 1 ? 1 : hp == 2 ? 0 : hp == 3 ? 2 : pdl_default();
   const int kb = K_bytes / KBLOCK_BYTES;

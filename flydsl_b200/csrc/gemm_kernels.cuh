@@ -54,7 +54,7 @@ struct GemmParams {
   int dst_first;         // scatter kernel: buffer stored to first
   int* status;           // device status word (first failure wins)
 #ifdef FLYB200_PROFILE
-  unsigned long long* prof;  // [8] cycle counters (profiling builds only)
+  unsigned long long* prof;  // [16] time stamps (profiling builds only)
 #endif
 };
 

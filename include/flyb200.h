@@ -66,7 +66,9 @@ extern "C" {
  *   bits 12-15 how K splits are combined: 1 = global workspace + ticket,
  *              2 = thread-block cluster + distributed shared memory (split <= 8)
  *   bits 16-23 rasterisation group (row tiles per group, large-M kernel)
- *   bits 24-27 depth of the shared-memory ring of the small-M kernel
+ *   bits 24-27 depth of the shared-memory ring of the small-M kernel (an odd
+ *              depth becomes the next even one, or the one below when that
+ *              does not fit into shared memory)
  *   bits 28-29 programmatic dependent launch of the small-M kernel: 1 = on (its
  *              set-up overlaps the tail of the previous kernel on the stream; no
  *              global memory is touched before that kernel has completed),
