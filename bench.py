@@ -269,6 +269,65 @@ def time_config(m, n, k, in_dtype, dev, iters=40, hint=0):
     return us, copies
 
 
+def time_moe(tokens, model_dim, inter_dim, experts, topk, tile_m, dev, iters=20):
+    """Device time of the two mixture-of-experts GEMM stages (activation gather
+    included) on seeded synthetic routing, with the algorithmic bytes of the
+    reference's own model: routed activation rows + every expert's weights once +
+    output rows (tests/kernels/test_moe_gemm_2stage.py:2001-2025)."""
+    from flydsl_b200 import shuffle_weight
+    from flydsl_b200.kernels.moe.moe_gemm_2stage import compile_moe_gemm1, compile_moe_gemm2, moe_sorting
+
+    g = torch.Generator(device=dev).manual_seed(77)
+    score = torch.rand(tokens, experts, generator=g, device=dev)
+    vals, ids = torch.topk(score, k=topk, dim=1)
+    srt, wts, e_ids, post = moe_sorting(ids.to(torch.int32), torch.softmax(vals, dim=1), num_experts=experts, block_size=tile_m)
+    n_valid, blocks = post[:1].contiguous(), int(e_ids.numel())
+
+    def q8(*shape):
+        return (torch.randn(*shape, generator=g, device=dev) * 64).clamp_(-448, 448).to(FP8)
+
+    x, a2 = q8(tokens, model_dim), q8(tokens * topk, inter_dim)
+    w1 = shuffle_weight(q8(experts, 2 * inter_dim, model_dim))
+    w2 = shuffle_weight(q8(experts, model_dim, inter_dim))
+    sx, sa2 = torch.rand(tokens, device=dev) + 0.5, torch.rand(tokens * topk, device=dev) + 0.5
+    sw1, sw2 = torch.rand(experts * 2 * inter_dim, device=dev) * 1e-3, torch.rand(experts * model_dim, device=dev) * 1e-3
+    out1 = torch.empty(tokens * topk, inter_dim, dtype=torch.bfloat16, device=dev)
+    out2 = torch.empty(tokens * topk, model_dim, dtype=torch.bfloat16, device=dev)
+    kw = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, tile_n=128, tile_k=128,
+              out_dtype="bf16", in_dtype="fp8")
+    g1 = compile_moe_gemm1(**kw, doweight_stage1=False)
+    g2 = compile_moe_gemm2(**kw, doweight_stage2=True, accumulate=False)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2
+    st = torch.cuda.Stream()
+    res = {}
+    for name, fn, args, flops, byts in (
+        ("stage1", g1, (out1, x.view(-1), w1.view(-1), sx, sw1, srt, e_ids, wts, n_valid, tokens, inter_dim, model_dim, blocks),
+         2.0 * tokens * topk * 2 * inter_dim * model_dim,
+         tokens * topk * model_dim + experts * 2 * inter_dim * model_dim + tokens * topk * inter_dim * 2),
+        ("stage2", g2, (out2, a2.view(-1), w2.view(-1), sa2, sw2, srt, e_ids, wts, n_valid, tokens, model_dim, inter_dim, blocks),
+         2.0 * tokens * topk * model_dim * inter_dim,
+         tokens * topk * inter_dim + experts * model_dim * inter_dim + tokens * topk * model_dim * 2),
+    ):
+        with torch.cuda.stream(st):
+            for _ in range(3):
+                fn(*args, st)
+            times = []
+            for _ in range(iters):
+                flush.zero_()  # evict the weights between timed launches
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(st)
+                fn(*args, st)
+                e1.record(st)
+                st.synchronize()
+                times.append(e0.elapsed_time(e1) * 1e3)
+        us = float(statistics.median(times))
+        res[name] = {"us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "hbm_gbs": round(byts / us / 1e3, 1),
+                     "algorithmic_bytes": int(byts)}
+    res["config"] = {"tokens": tokens, "model_dim": model_dim, "inter_dim": inter_dim, "experts": experts, "topk": topk,
+                     "tile_m": tile_m, "blocks": blocks, "l2": "256 MiB written between timed launches"}
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -482,6 +541,13 @@ def main():
                 "frac_of_nominal_fp8": round(2.0 * em * en * ek / us / 1e6 / NOMINAL_FP8_TFLOPS, 3),
                 "rotating_copies": copies,
             }
+        # the grouped (mixture-of-experts) stages: a decode-sized and a prefill-sized batch
+        for name, mt, mtile in (("moe_fp8_decode_32tok", 32, 16), ("moe_fp8_prefill_4096tok", 4096, 128)):
+            r = time_moe(mt, 4096, 2048, 8, 2, mtile, dev)
+            for stage in ("stage1", "stage2"):
+                r[stage]["hbm_frac_of_measured"] = round(r[stage]["hbm_gbs"] / peaks["hbm_gbs"], 3)
+                r[stage]["frac_of_nominal_fp8"] = round(r[stage]["tflops"] / NOMINAL_FP8_TFLOPS, 3)
+            extras[name] = r
     cpu = None
     if not args.no_cpu_baseline and world == 1:
         tf, sample, dt, threads = cpu_reference_rate(m, n, k, in_dtype, seconds_budget=15.0, steps=1, warmup=0)

@@ -15,7 +15,7 @@ OK = 0
 E_BAD_ARG, E_BAD_ALIGN, E_CUDA, E_TIMEOUT, E_UNSUPPORTED, E_SMEM_ALIGN, E_WORKSPACE, E_SCRATCH_LIMIT = range(1, 9)
 
 DT_FP8, DT_INT8, DT_FP16, DT_BF16 = range(4)
-OUT_BF16, OUT_FP16 = range(2)
+OUT_BF16, OUT_FP16, OUT_F32 = range(3)
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_SILU, EPI_BIAS_GELU = range(5)
 SRC_ROW_MAJOR, SRC_MFMA_16x16 = range(2)
 
@@ -49,6 +49,9 @@ SIGNATURES = {
     "flyb200_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "flyb200_read_status": (_i, [ctypes.POINTER(_i)]),
     "flyb200_selftest_bounded_wait": (_i, [ctypes.c_uint, _vp]),
+    "flyb200_moe_gather_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "flyb200_moe_gemm": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 11 + [_vp]),
+    "flyb200_moe_reduce": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_strerror": (ctypes.c_char_p, [_i]),
     "flyb200_last_cuda_error": (ctypes.c_char_p, []),
     "flyb200_version": (_i, []),

@@ -3,6 +3,7 @@
 // synchronisation and no memcpy on the launch path.
 #include "../../include/flyb200.h"
 #include "decode_kernel.cuh"
+#include "host_common.h"
 #include "quant_kernel.cuh"
 #include "rows2_kernel.cuh"
 
@@ -668,6 +669,22 @@ int static_scratch_address(void** out) {
 }
 
 }  // namespace
+
+namespace flyb200 {
+namespace host {
+int byte_matrix_map(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+  return make_map(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, row_bytes, rows, KBLOCK_BYTES, box_rows);
+}
+int status_word(int** out) {
+  DeviceState* st = nullptr;
+  const int rc = device_state(&st);
+  if (rc) return rc;
+  *out = st->status;
+  return FLYB200_OK;
+}
+int record_cuda_error(cudaError_t e, const char* what) { return cuda_fail(e, what); }
+}  // namespace host
+}  // namespace flyb200
 
 extern "C" {
 

@@ -1,0 +1,179 @@
+// libflyb200: host side of the grouped (mixture-of-experts) entry points of
+// include/flyb200.h — argument checks, tensor map, kernel selection, launch.
+#include "../../include/flyb200.h"
+#include "host_common.h"
+#include "moe_kernel.cuh"
+
+#include <atomic>
+#include <cstring>
+#include <type_traits>
+
+using namespace flyb200;
+
+namespace {
+
+#define CUDA_TRY(expr)                                                  \
+  do {                                                                  \
+    cudaError_t _e = (expr);                                            \
+    if (_e != cudaSuccess) return host::record_cuda_error(_e, #expr);   \
+  } while (0)
+
+constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Ring depth: as many stages of two weight tiles and one token tile as fit, at most 8.
+inline int moe_stages(int bn) {
+  const int stage = 2 * BLOCK_ROWS * KBLOCK_BYTES + bn * KBLOCK_BYTES;
+  int n = (SMEM_LIMIT - 1024 - 12 * bn) / stage;
+  return n > 8 ? 8 : n;
+}
+
+template <int KIND, int BN, int STAGE, int OUTMODE, bool ACCUM>
+int launch_moe(const CUtensorMap& tmA, MoeParams p, int blocks, cudaStream_t s) {
+  static std::atomic<uint64_t> done{0};
+  auto kernel = moe_gemm_kernel<KIND, BN, STAGE, OUTMODE, ACCUM>;
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  const uint64_t bit = 1ull << dev;
+  if (!(done.load(std::memory_order_acquire) & bit)) {
+    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
+    done.fetch_or(bit, std::memory_order_release);
+  }
+  p.stages = moe_stages(BN);
+  const MoeLayout L = moe_layout(BN, p.stages);
+  if (p.stages < 2 || L.total > SMEM_LIMIT) return FLYB200_E_UNSUPPORTED;
+  const int tiles = STAGE == 1 ? (p.n_out + BLOCK_ROWS - 1) / BLOCK_ROWS : (p.n_out + 2 * BLOCK_ROWS - 1) / (2 * BLOCK_ROWS);
+  kernel<<<dim3(blocks, tiles, 1), MOE_THREADS, L.total, s>>>(tmA, p);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+template <int KIND, int BN>
+int launch_moe_variant(int stage, int out_dtype, bool accumulate, const CUtensorMap& tmA, const MoeParams& p, int blocks,
+                       cudaStream_t s) {
+  if (stage == 1) {
+    if (out_dtype == FLYB200_OUT_BF16) return launch_moe<KIND, BN, 1, MOE_OUT_BF16, false>(tmA, p, blocks, s);
+    if (out_dtype == FLYB200_OUT_FP16) return launch_moe<KIND, BN, 1, MOE_OUT_FP16, false>(tmA, p, blocks, s);
+    return FLYB200_E_UNSUPPORTED;
+  }
+  if (accumulate) {
+    if (out_dtype == FLYB200_OUT_BF16) return launch_moe<KIND, BN, 2, MOE_OUT_BF16, true>(tmA, p, blocks, s);
+    if (out_dtype == FLYB200_OUT_FP16) return launch_moe<KIND, BN, 2, MOE_OUT_FP16, true>(tmA, p, blocks, s);
+    if (out_dtype == FLYB200_OUT_F32) return launch_moe<KIND, BN, 2, MOE_OUT_F32, true>(tmA, p, blocks, s);
+    return FLYB200_E_UNSUPPORTED;
+  }
+  if (out_dtype == FLYB200_OUT_BF16) return launch_moe<KIND, BN, 2, MOE_OUT_BF16, false>(tmA, p, blocks, s);
+  if (out_dtype == FLYB200_OUT_FP16) return launch_moe<KIND, BN, 2, MOE_OUT_FP16, false>(tmA, p, blocks, s);
+  return FLYB200_E_UNSUPPORTED;  // per-slot partials are 16-bit only, as in the reference
+}
+
+template <int KIND>
+int launch_moe_bn(int bn, int stage, int out_dtype, bool accumulate, const CUtensorMap& tmA, const MoeParams& p,
+                  int blocks, cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch_moe_variant<KIND, 16>(stage, out_dtype, accumulate, tmA, p, blocks, s);
+    case 32: return launch_moe_variant<KIND, 32>(stage, out_dtype, accumulate, tmA, p, blocks, s);
+    case 64: return launch_moe_variant<KIND, 64>(stage, out_dtype, accumulate, tmA, p, blocks, s);
+    case 128: return launch_moe_variant<KIND, 128>(stage, out_dtype, accumulate, tmA, p, blocks, s);
+    case 256: return launch_moe_variant<KIND, 256>(stage, out_dtype, accumulate, tmA, p, blocks, s);
+  }
+  return FLYB200_E_UNSUPPORTED;
+}
+
+}  // namespace
+
+extern "C" {
+
+int flyb200_moe_gather_rows(void* dst, float* dst_scale, const void* src, const float* src_scale, const int* sorted_ids,
+                            const int* num_valid_ids, int tokens, int topk, int by_slot, int row_bytes, int rows,
+                            void* stream) {
+  if (!dst || !dst_scale || !src || !src_scale || !sorted_ids || !num_valid_ids) return FLYB200_E_BAD_ARG;
+  if (tokens < 0 || topk <= 0 || topk > 255 || row_bytes <= 0 || rows < 0) return FLYB200_E_BAD_ARG;
+  if (row_bytes % 16 != 0) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(dst) || !aligned16(src)) return FLYB200_E_BAD_ALIGN;
+  if (rows == 0) return FLYB200_OK;
+  const int warps = 8;
+  int grid = (rows + warps - 1) / warps;
+  if (grid > 148 * 8) grid = 148 * 8;
+  moe_gather_rows_kernel<<<grid, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint8_t*>(dst), dst_scale, static_cast<const uint8_t*>(src), src_scale, sorted_ids, num_valid_ids,
+      tokens, topk, by_slot ? 1 : 0, row_bytes, rows);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_shuf, const float* scale_a_sorted,
+                     const float* scale_w, const int* sorted_ids, const int* expert_ids, const float* sorted_weights,
+                     const int* num_valid_ids, int tokens, int topk, int experts, int model_dim, int inter_dim,
+                     int tile_m, int blocks, int in_dtype, int out_dtype, int doweight, int accumulate, void* stream) {
+  if (stage != 1 && stage != 2) return FLYB200_E_BAD_ARG;
+  if (!out || !a_sorted || !w_shuf || !scale_a_sorted || !scale_w || !sorted_ids || !expert_ids || !num_valid_ids)
+    return FLYB200_E_BAD_ARG;
+  if (doweight && !sorted_weights) return FLYB200_E_BAD_ARG;
+  if (tokens < 0 || topk <= 0 || topk > 255 || experts <= 0 || model_dim <= 0 || inter_dim <= 0 || blocks < 0)
+    return FLYB200_E_BAD_ARG;
+  if (tokens >= (1 << 24)) return FLYB200_E_UNSUPPORTED;  // a sorted id keeps the token in 24 bits
+  if (in_dtype != FLYB200_DT_FP8 && in_dtype != FLYB200_DT_INT8) return FLYB200_E_UNSUPPORTED;
+  if (tile_m < 16 || tile_m > 256 || tile_m % 16 != 0) return FLYB200_E_BAD_ARG;
+  if (stage == 1 && accumulate) return FLYB200_E_BAD_ARG;
+  const int K = stage == 1 ? model_dim : inter_dim;
+  const int n_out = stage == 1 ? inter_dim : model_dim;
+  if (K % KBLOCK_BYTES != 0 || n_out % 16 != 0) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(out) || !aligned16(a_sorted) || !aligned16(w_shuf)) return FLYB200_E_BAD_ALIGN;
+  if (blocks == 0 || tokens == 0) return FLYB200_OK;
+
+  MoeParams p;
+  memset(&p, 0, sizeof(p));
+  p.w = static_cast<const uint8_t*>(w_shuf);
+  p.sa = scale_a_sorted;
+  p.sw = scale_w;
+  p.sorted_ids = sorted_ids;
+  p.expert_ids = expert_ids;
+  p.sorted_w = sorted_weights;
+  p.num_valid = num_valid_ids;
+  p.out = out;
+  p.tokens = tokens;
+  p.topk = topk;
+  p.experts = experts;
+  p.n_expert = stage == 1 ? 2 * inter_dim : model_dim;
+  p.n_out = n_out;
+  p.K_bytes = K;
+  p.tile_m = tile_m;
+  p.doweight = doweight ? 1 : 0;
+  int rc = host::status_word(&p.status);
+  if (rc) return rc;
+
+  int bn = 16;
+  while (bn < tile_m) bn *= 2;
+  CUtensorMap tmA;
+  rc = host::byte_matrix_map(&tmA, a_sorted, static_cast<uint64_t>(K), static_cast<uint64_t>(blocks) * tile_m, bn);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (in_dtype == FLYB200_DT_FP8) return launch_moe_bn<KIND_F8>(bn, stage, out_dtype, accumulate != 0, tmA, p, blocks, s);
+  return launch_moe_bn<KIND_I8>(bn, stage, out_dtype, accumulate != 0, tmA, p, blocks, s);
+}
+
+int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, void* stream) {
+  if (!y || !x || tokens < 0 || topk <= 0 || dim <= 0) return FLYB200_E_BAD_ARG;
+  if (dim % 2 != 0) return FLYB200_E_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(y) & 3u) || (reinterpret_cast<uintptr_t>(x) & 3u)) return FLYB200_E_BAD_ALIGN;
+  if (tokens == 0) return FLYB200_OK;
+  const long long total = static_cast<long long>(tokens) * dim / 2;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == FLYB200_OUT_BF16) {
+    moe_reduce_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, s>>>(
+        static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x), tokens, topk, dim);
+  } else if (dtype == FLYB200_OUT_FP16) {
+    moe_reduce_kernel<__half><<<static_cast<int>(blocks), 256, 0, s>>>(static_cast<__half*>(y),
+                                                                       static_cast<const __half*>(x), tokens, topk, dim);
+  } else {
+    return FLYB200_E_UNSUPPORTED;
+  }
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+}  // extern "C"

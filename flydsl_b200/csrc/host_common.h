@@ -1,0 +1,19 @@
+// Host helpers shared by the translation units of libflyb200 (not part of the C ABI).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace flyb200 {
+namespace host {
+
+// Tensor map over a row-major byte matrix [rows, row_bytes]: boxes of
+// 128 bytes x box_rows rows, 128-byte swizzle, out-of-bounds rows read as zero.
+int byte_matrix_map(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows);
+// Pointer to the current device's status word (first failed bounded wait wins).
+int status_word(int** out);
+// Remember a CUDA error for flyb200_last_cuda_error(); returns FLYB200_E_CUDA.
+int record_cuda_error(cudaError_t e, const char* what);
+
+}  // namespace host
+}  // namespace flyb200

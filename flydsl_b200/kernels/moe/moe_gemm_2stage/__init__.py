@@ -1,0 +1,248 @@
+"""Two-stage mixture-of-experts GEMM: the operator surface of the reference's
+``kernels/moe/moe_gemm_2stage`` (gemm1.py:541-580 ``compile_moe_gemm1``,
+gemm2.py:595-643 ``compile_moe_gemm2``, moe_reduce.py:164-205
+``compile_moe_reduction``) bound to the grouped kernels of libflyb200.
+
+    exe = compile_moe_gemm1(model_dim=.., inter_dim=.., experts=.., topk=.., tile_m=.., tile_n=.., tile_k=..,
+                            doweight_stage1=False, out_dtype="bf16", in_dtype="fp8")
+    exe(out, x, w1_shuffled, scale_x, scale_w1, sorted_token_ids, sorted_expert_ids, sorted_weights,
+        num_valid_ids, tokens, inter_dim, model_dim, blocks, stream)          # -> None, writes out
+
+The positional arguments are the reference's
+(tests/kernels/test_moe_gemm_2stage.py:161-193).  ``w`` is
+``shuffle_weight(w_q)`` of the ``[experts, rows, K]`` weights: one B200 image
+per expert.  ``tile_m`` is the routing block size the sorted ids were padded
+to; ``tile_n`` / ``tile_k`` are validated as the reference does and are
+otherwise hints (a CTA always takes two 128-channel weight tiles and 128-byte
+k-blocks).  ``in_dtype`` "fp8" and "int8" are built; "int8smooth" and "int4"
+raise ``ValueError``.
+
+``moe_sorting`` restates the routing-table layout the kernels consume
+(tests/kernels/test_moe_gemm_2stage.py:99-137) with torch ops on the tensors'
+own device.
+"""
+
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from .... import _lib
+from ...gemm.preshuffle_gemm import _stream_handle
+
+_OUT = {
+    "f16": (_lib.OUT_FP16, torch.float16),
+    "fp16": (_lib.OUT_FP16, torch.float16),
+    "half": (_lib.OUT_FP16, torch.float16),
+    "bf16": (_lib.OUT_BF16, torch.bfloat16),
+    "bfloat16": (_lib.OUT_BF16, torch.bfloat16),
+    "f32": (_lib.OUT_F32, torch.float32),
+    "fp32": (_lib.OUT_F32, torch.float32),
+    "float": (_lib.OUT_F32, torch.float32),
+}
+_IN = {"fp8": (_lib.DT_FP8, torch.float8_e4m3fn), "int8": (_lib.DT_INT8, torch.int8)}
+_REFERENCE_IN_DTYPES = ("fp8", "int8", "int8smooth", "int4")
+
+
+def moe_sorting(
+    topk_ids: torch.Tensor, topk_weights: torch.Tensor, *, num_experts: int, block_size: int
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Routing table for the two GEMM stages: ``(sorted_ids, sorted_weights,
+    sorted_expert_ids, num_tokens_post_pad)``.
+
+    The (token, slot) pairs are grouped by expert in ascending (token, slot)
+    order, every group padded to a multiple of ``block_size``; a sorted id is
+    ``(slot << 24) | token``, padding is ``(topk << 24) | tokens``;
+    ``sorted_expert_ids[b]`` is the expert of block ``b`` (-1 past the end);
+    ``num_tokens_post_pad = [rows in use, tokens]``.
+    """
+    tokens, topk = topk_ids.shape
+    dev = topk_ids.device
+    e, bs = int(num_experts), int(block_size)
+    max_padded = int(topk_ids.numel() + e * bs - topk)
+    max_blocks = (max_padded + bs - 1) // bs
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    order = torch.sort(flat, stable=True).indices  # by expert, then (token, slot)
+    counts = torch.bincount(flat, minlength=e)[:e]
+    padded = (counts + bs - 1) // bs * bs
+    starts = torch.cumsum(padded, 0) - padded
+    first = torch.cumsum(counts, 0) - counts
+    expert_of = flat[order]
+    dest = starts[expert_of] + (torch.arange(flat.numel(), device=dev) - first[expert_of])
+    sorted_ids = torch.full((max_padded,), (topk << 24) | tokens, dtype=torch.int32, device=dev)
+    sorted_weights = torch.zeros((max_padded,), dtype=torch.float32, device=dev)
+    tok = (order // topk).to(torch.int32)
+    slot = (order % topk).to(torch.int32)
+    sorted_ids[dest] = (slot << 24) | tok
+    sorted_weights[dest] = topk_weights.reshape(-1).to(torch.float32)[order]
+    blocks_per = padded // bs
+    sorted_expert_ids = torch.full((max_blocks,), -1, dtype=torch.int32, device=dev)
+    total_blocks = int(blocks_per.sum())
+    sorted_expert_ids[:total_blocks] = torch.repeat_interleave(
+        torch.arange(e, device=dev, dtype=torch.int32), blocks_per
+    )
+    num_tokens_post_pad = torch.tensor([int(padded.sum()), tokens], dtype=torch.int32, device=dev)
+    return sorted_ids, sorted_weights, sorted_expert_ids, num_tokens_post_pad
+
+
+class _MoeStage:
+    """Shared launcher: gathers the activation rows into sorted order, then runs the grouped GEMM."""
+
+    def __init__(self, stage, model_dim, inter_dim, experts, topk, tile_m, in_dtype, out_dtype, doweight, accumulate):
+        self.stage = stage
+        self.model_dim, self.inter_dim = int(model_dim), int(inter_dim)
+        self.experts, self.topk, self.tile_m = int(experts), int(topk), int(tile_m)
+        self.in_dtype, self.out_dtype = in_dtype, out_dtype
+        self.doweight, self.accumulate = bool(doweight), bool(accumulate)
+        self._dt, self._torch_in = _IN[in_dtype]
+        self._out, self._torch_out = _OUT[out_dtype]
+        self._k = self.model_dim if stage == 1 else self.inter_dim
+        self._scratch: dict = {}
+
+    def _sorted_buffers(self, device, rows):
+        buf = self._scratch.get(device.index)
+        if buf is None or buf[0].shape[0] < rows:
+            buf = (
+                torch.empty((rows, self._k), dtype=torch.uint8, device=device),
+                torch.empty((rows,), dtype=torch.float32, device=device),
+            )
+            self._scratch[device.index] = buf
+        return buf
+
+    def __call__(
+        self, out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights, num_valid_ids,
+        tokens, dim0, dim1, blocks, stream=None,
+    ):
+        n_out, k = (self.inter_dim, self.model_dim) if self.stage == 1 else (self.model_dim, self.inter_dim)
+        if (int(dim0), int(dim1)) != (n_out, k):
+            raise ValueError(f"launch dims ({dim0}, {dim1}) do not match the compiled ({n_out}, {k})")
+        tokens, blocks = int(tokens), int(blocks)
+        for name, t in (("out", out), ("x", x), ("w", w), ("scale_x", scale_x), ("scale_w", scale_w)):
+            if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous CUDA tensor")
+        if out.dtype != self._torch_out:
+            raise ValueError(f"out must be {self._torch_out}, got {out.dtype}")
+        x_rows = tokens if self.stage == 1 else tokens * self.topk
+        out_rows = tokens if (self.stage == 2 and self.accumulate) else tokens * self.topk
+        w_rows = self.experts * (2 * self.inter_dim if self.stage == 1 else self.model_dim)
+        need = (
+            ("out", out, out_rows * n_out), ("x", x, x_rows * k), ("w", w, w_rows * k),
+            ("scale_x", scale_x, x_rows), ("scale_w", scale_w, w_rows),
+            # the sorted ids are read up to num_valid_ids[0] only, which may end inside the last block
+            ("sorted_token_ids", sorted_token_ids, (blocks - 1) * self.tile_m + 1), ("sorted_expert_ids", sorted_expert_ids, blocks),
+            ("num_valid_ids", num_valid_ids, 1),
+        )
+        for name, t, n in need:
+            if t.numel() < n:
+                raise ValueError(f"{name} holds {t.numel()} elements, the launch needs {n}")
+        if x.element_size() != 1 or w.element_size() != 1:
+            raise ValueError("x and w must be 8-bit tensors")
+        if scale_x.dtype != torch.float32 or scale_w.dtype != torch.float32:
+            raise ValueError("scales must be float32")
+        if sorted_token_ids.dtype != torch.int32 or sorted_expert_ids.dtype != torch.int32 or num_valid_ids.dtype != torch.int32:
+            raise ValueError("routing tensors must be int32")
+        if self.doweight and (sorted_weights is None or sorted_weights.numel() < sorted_token_ids.numel()):
+            raise ValueError("sorted_weights is required when the routed weight is applied in this stage")
+        if tokens == 0 or blocks == 0:
+            return None
+        lib = _lib.load()
+        s = _stream_handle(stream)
+        rows = blocks * self.tile_m
+        with torch.cuda.device(out.device):
+            a_sorted, sa_sorted = self._sorted_buffers(out.device, rows)
+            _lib.check(
+                lib.flyb200_moe_gather_rows(
+                    a_sorted.data_ptr(), sa_sorted.data_ptr(), x.data_ptr(), scale_x.data_ptr(),
+                    sorted_token_ids.data_ptr(), num_valid_ids.data_ptr(), tokens, self.topk,
+                    0 if self.stage == 1 else 1, k, rows, s,
+                ),
+                "moe_gather_rows",
+            )
+            _lib.check(
+                lib.flyb200_moe_gemm(
+                    self.stage, out.data_ptr(), a_sorted.data_ptr(), w.data_ptr(), sa_sorted.data_ptr(),
+                    scale_w.data_ptr(), sorted_token_ids.data_ptr(), sorted_expert_ids.data_ptr(),
+                    sorted_weights.data_ptr() if sorted_weights is not None and sorted_weights.numel() else None,
+                    num_valid_ids.data_ptr(), tokens, self.topk, self.experts, self.model_dim, self.inter_dim,
+                    self.tile_m, blocks, self._dt, self._out, int(self.doweight), int(self.accumulate), s,
+                ),
+                "moe_gemm",
+            )
+        return None
+
+
+def _check_common(model_dim, inter_dim, experts, topk, tile_m, tile_n, tile_k, in_dtype, k):
+    if in_dtype not in _REFERENCE_IN_DTYPES:
+        raise ValueError(f"in_dtype must be 'fp8', 'int8', 'int8smooth', or 'int4', got {in_dtype!r}")
+    if in_dtype not in _IN:
+        raise ValueError(f"in_dtype={in_dtype!r} is not built for B200 (fp8 and int8 are)")
+    if min(int(model_dim), int(inter_dim), int(experts), int(topk)) <= 0:
+        raise ValueError("model_dim, inter_dim, experts and topk must be positive")
+    if not (16 <= int(tile_m) <= 256 and int(tile_m) % 16 == 0):
+        raise ValueError(f"tile_m must be a 16-multiple in [16,256], got {tile_m}")
+    if not (64 <= int(tile_n) <= 256 and int(tile_n) % 64 == 0):
+        raise ValueError(f"tile_n must be in [64,256] multiple of 64, got {tile_n}")
+    if int(tile_k) not in (128, 256):
+        raise ValueError(f"tile_k must be 128 or 256, got {tile_k}")
+    if k % int(tile_k) != 0:
+        raise ValueError(f"K={k} must be a multiple of tile_k={tile_k}")
+
+
+def compile_moe_gemm1(
+    *, model_dim, inter_dim, experts, topk, tile_m, tile_n, tile_k, doweight_stage1, out_dtype="f16", in_dtype="fp8"
+):
+    """Stage 1 (gate-up + silu): ``out[token, slot, inter_dim] = silu(x.Wg) * (x.Wu)``."""
+    if out_dtype not in ("f16", "bf16"):
+        raise ValueError(f"out_dtype must be 'f16' or 'bf16', got {out_dtype!r}")
+    _check_common(model_dim, inter_dim, experts, topk, tile_m, tile_n, tile_k, in_dtype, int(model_dim))
+    if int(inter_dim) % 16 != 0:
+        raise ValueError(f"inter_dim={inter_dim} must be a multiple of 16")
+    return _MoeStage(1, model_dim, inter_dim, experts, topk, tile_m, in_dtype, out_dtype, doweight_stage1, False)
+
+
+def compile_moe_gemm2(
+    *, model_dim, inter_dim, experts, topk, tile_m, tile_n, tile_k, doweight_stage2, out_dtype="f16",
+    accumulate=True, in_dtype="fp8",
+):
+    """Stage 2 (down projection): atomic accumulation into ``[tokens, model_dim]``
+    or per-(token, slot) rows ``[tokens * topk, model_dim]`` for a separate reduction."""
+    out_s = str(out_dtype).strip().lower()
+    if out_s not in _OUT:
+        raise ValueError(f"out_dtype must be 'f16', 'bf16', or 'f32', got {out_dtype!r}")
+    if (not bool(accumulate)) and _OUT[out_s][0] == _lib.OUT_F32:
+        raise ValueError("compile_moe_gemm2(accumulate=False) only supports out_dtype in {'f16','bf16'}")
+    _check_common(model_dim, inter_dim, experts, topk, tile_m, tile_n, tile_k, in_dtype, int(inter_dim))
+    if int(model_dim) % 16 != 0:
+        raise ValueError(f"model_dim={model_dim} must be a multiple of 16")
+    return _MoeStage(2, model_dim, inter_dim, experts, topk, tile_m, in_dtype, out_s, doweight_stage2, accumulate)
+
+
+def compile_moe_reduction(*, topk, model_dim, dtype_str="f16", use_mask=False, num_experts=0, out_dtype_str=None):
+    """Top-k reduction ``Y[t, :] = sum_slot X[t, slot, :]``; returns
+    ``launch(X, Y, expert_mask, topk_ids, m_tokens, stream)`` as the reference does."""
+    if use_mask:
+        raise ValueError("use_mask=True (expert-parallel masking) is not built for B200")
+    if dtype_str not in ("f16", "bf16") or (out_dtype_str or dtype_str) != dtype_str:
+        raise ValueError("the reduction is built for f16 and bf16 with the output type of the input")
+    code, tdt = _OUT[dtype_str]
+    topk, model_dim = int(topk), int(model_dim)
+    if model_dim % 2 != 0:
+        raise ValueError("model_dim must be even")
+
+    def launch(X, Y, expert_mask, topk_ids, m_tokens, stream=None):
+        m = int(m_tokens)
+        if X.dtype != tdt or Y.dtype != tdt or not X.is_cuda or not Y.is_cuda:
+            raise ValueError(f"X and Y must be CUDA tensors of {tdt}")
+        if X.numel() < m * topk * model_dim or Y.numel() < m * model_dim:
+            raise ValueError("X or Y is smaller than the launch needs")
+        with torch.cuda.device(X.device):
+            _lib.check(
+                _lib.load().flyb200_moe_reduce(Y.data_ptr(), X.data_ptr(), m, topk, model_dim, code, _stream_handle(stream)),
+                "moe_reduce",
+            )
+
+    return launch
+
+
+__all__ = ["compile_moe_gemm1", "compile_moe_gemm2", "compile_moe_reduction", "moe_sorting"]

@@ -216,6 +216,54 @@ int flyb200_read_status(int* out_status);
  * (lib/Runtime/ROCm/FlyRocmRuntimeWrappers.cpp:23-31 prints host errors only). */
 int flyb200_selftest_bounded_wait(unsigned int limit_us, void* stream);
 
+/* ---- Grouped (mixture-of-experts) two-stage GEMM on the same weight image ----
+ * Replaces the launchers returned by compile_moe_gemm1 / compile_moe_gemm2 and
+ * compile_moe_reduction (kernels/moe/moe_gemm_2stage/gemm1.py:366-580,
+ * gemm2.py:350-643, moe_reduce.py:164-205; call convention pinned by
+ * tests/kernels/test_moe_gemm_2stage.py:161-193).  Routing input is what the
+ * reference's moe_sorting produces (tests/kernels/test_moe_gemm_2stage.py:99-137):
+ *   sorted_ids[P]      (slot << 24) | token per sorted row, every expert's rows
+ *                      padded to a multiple of tile_m with token >= tokens
+ *   expert_ids[blocks] expert of each block of tile_m sorted rows (-1: none)
+ *   sorted_weights[P]  routed weight per sorted row
+ *   num_valid_ids[1]   sorted rows in use
+ * Weights: one image per expert (flyb200_shuffle_weight applied to each
+ * [rows_per_expert, K] matrix), stored back to back in expert order. */
+#define FLYB200_OUT_F32 2 /* flyb200_moe_gemm stage 2 with accumulate only */
+
+/* Activation rows and their scales gathered into sorted order (the A-gather the
+ * reference does inside its kernels, gemm1.py:403-460 / gemm2.py:374-380):
+ *   dst[p, :] = src[r, :], dst_scale[p] = src_scale[r], r = token (by_slot = 0,
+ *   stage 1) or token * topk + slot (by_slot = 1, stage 2); padding rows and rows
+ *   >= num_valid_ids[0] become zero with scale zero.  rows = blocks * tile_m,
+ *   row_bytes a multiple of 16. */
+int flyb200_moe_gather_rows(void* dst, float* dst_scale, const void* src, const float* src_scale, const int* sorted_ids,
+                            const int* num_valid_ids, int tokens, int topk, int by_slot, int row_bytes, int rows,
+                            void* stream);
+
+/* stage 1: out[token, slot, inter_dim] = silu(g) * u [* routed weight],
+ *          g/u = (x . W1[e, gate/up rows]^T) * scale_w * scale_x
+ * stage 2: accumulate = 1: out[token, model_dim] += y (atomic adds; the caller zeroes out),
+ *          accumulate = 0: out[token * topk + slot, model_dim] = y,
+ *          y = (a2 . W2[e]^T) * scale_w * scale_x [* routed weight]
+ *   a_sorted        [blocks * tile_m, K] activations in sorted order (flyb200_moe_gather_rows)
+ *   scale_a_sorted  [blocks * tile_m] their scales
+ *   w_shuf          per-expert images of [2 * inter_dim, model_dim] (stage 1, gate rows
+ *                   first) or [model_dim, inter_dim] (stage 2)
+ *   scale_w         one fp32 per weight row
+ *   in_dtype        FLYB200_DT_FP8 or FLYB200_DT_INT8; out_dtype FLYB200_OUT_BF16 /
+ *                   _FP16, or FLYB200_OUT_F32 for stage 2 with accumulate
+ * Requirements: K (model_dim in stage 1, inter_dim in stage 2) a multiple of
+ * 128, output row length a multiple of 16, tile_m a multiple of 16 in [16, 256]. */
+int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_shuf, const float* scale_a_sorted,
+                     const float* scale_w, const int* sorted_ids, const int* expert_ids, const float* sorted_weights,
+                     const int* num_valid_ids, int tokens, int topk, int experts, int model_dim, int inter_dim,
+                     int tile_m, int blocks, int in_dtype, int out_dtype, int doweight, int accumulate, void* stream);
+
+/* y[token, dim] = sum over slots of x[token, slot, dim] (fp32 sum, one rounding);
+ * dtype FLYB200_OUT_BF16 or FLYB200_OUT_FP16, dim even. */
+int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, void* stream);
+
 const char* flyb200_strerror(int code);
 const char* flyb200_last_cuda_error(void);
 int flyb200_version(void);

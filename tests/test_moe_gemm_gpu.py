@@ -1,0 +1,280 @@
+"""GPU parity of the two-stage mixture-of-experts GEMM against the CPU oracle,
+through the reference's operator surface (compile_moe_gemm1 / compile_moe_gemm2 /
+compile_moe_reduction).  The cases follow tests/kernels/test_moe_gemm_2stage.py
+of the reference: numeric checks for both stages (atomic and per-slot output),
+the output canary, padded-row sentinels and the num_valid_ids guard.
+
+Tolerances: the reference accepts cosine similarity > 0.99.  Here, in addition,
+every element must be within 2e-2 of the fp32 oracle relative to the largest
+reference magnitude (the outputs are 16-bit; atomic accumulation in 16 bits
+rounds once per added slot)."""
+
+import pytest
+import torch
+
+from flydsl_b200 import _lib, compiler as flyc, shuffle_weight
+from flydsl_b200.kernels.moe.moe_gemm_2stage import (
+    compile_moe_gemm1,
+    compile_moe_gemm2,
+    compile_moe_reduction,
+    moe_sorting,
+)
+from oracle import moe_oracle
+
+pytestmark = pytest.mark.gpu
+
+OUT_T = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+SHAPE = dict(model_dim=256, inter_dim=128, experts=4, topk=2)  # the reference's small tile-valid shape
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda:0")
+
+
+def close_enough(got, ref, what, rel=2e-2):
+    got = got.float().cpu()
+    cos = moe_oracle.cosine_sim(got, ref)
+    assert cos > 0.99, f"{what}: cosine {cos:.5f}"
+    bound = rel * float(ref.abs().max())
+    err = float((got - ref).abs().max())
+    assert err <= bound, f"{what}: max abs error {err:.4g} > {bound:.4g}"
+
+
+def routing_on(dev, d, experts, tile_m):
+    ids, w, e_ids, post = moe_sorting(d["topk_ids"].to(dev), d["topk_weights"].to(dev), num_experts=experts, block_size=tile_m)
+    return ids, w, e_ids, post[:1].contiguous(), int(e_ids.numel())
+
+
+def run_stage1(dev, d, *, model_dim, inter_dim, experts, topk, tile_m, in_dtype, out_dtype, doweight=False, tile_n=64,
+               extra_rows=0, routing=None, use_compile=False):
+    tokens = d["x_q"].shape[0]
+    ids, w, e_ids, n_valid, blocks = routing or routing_on(dev, d, experts, tile_m)
+    x = d["x_q"].to(dev)
+    w1 = shuffle_weight(d["w1_q"].to(dev)).view(experts * 2 * inter_dim, model_dim).contiguous()
+    out = torch.full((tokens * topk + extra_rows, inter_dim), 7.0, dtype=OUT_T[out_dtype], device=dev)
+    exe = compile_moe_gemm1(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m,
+                            tile_n=tile_n, tile_k=128, doweight_stage1=doweight, out_dtype=out_dtype, in_dtype=in_dtype)
+    args = (out, x.view(-1), w1.view(-1), d["scale_x"].to(dev).view(-1), d["scale_w1"].to(dev).view(-1), ids, e_ids,
+            w.view(-1), n_valid, tokens, inter_dim, model_dim, blocks, torch.cuda.current_stream())
+    fn = flyc.compile(exe, *args) if use_compile else exe
+    fn(*args)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    return out
+
+
+def run_stage2(dev, d, *, model_dim, inter_dim, experts, topk, tile_m, in_dtype, out_dtype, accumulate, doweight=True,
+               tile_n=64, extra_rows=0, routing=None):
+    tokens = d["x_q"].shape[0]
+    ids, w, e_ids, n_valid, blocks = routing or routing_on(dev, d, experts, tile_m)
+    a2 = d["a2_q"].to(dev)
+    w2 = shuffle_weight(d["w2_q"].to(dev)).view(experts * model_dim, inter_dim).contiguous()
+    rows = tokens if accumulate else tokens * topk
+    out = torch.zeros((rows + extra_rows, model_dim), dtype=OUT_T[out_dtype], device=dev)
+    if extra_rows:
+        out[rows:] = 7.0
+    exe = compile_moe_gemm2(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m,
+                            tile_n=tile_n, tile_k=128, doweight_stage2=doweight, out_dtype=out_dtype,
+                            accumulate=accumulate, in_dtype=in_dtype)
+    exe(out, a2.view(-1), w2.view(-1), d["scale_a2"].to(dev).view(-1), d["scale_w2"].to(dev).view(-1), ids, e_ids,
+        w.view(-1), n_valid, tokens, model_dim, inter_dim, blocks, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    return out
+
+
+def ref_stage1(d, inter_dim, doweight=False):
+    experts = d["w1_q"].shape[0]
+    return moe_oracle.moe_gemm1(d["x_q"], d["w1_q"].view(experts * 2 * inter_dim, -1), d["scale_x"],
+                                d["scale_w1"].view(-1, 1), d["topk_ids"].long(), d["topk_weights"], inter_dim, doweight)
+
+
+def ref_stage2(d, model_dim, doweight=True):
+    return moe_oracle.moe_gemm2(d["a2_q"], d["w2_q"], d["scale_a2"], d["scale_w2"], d["topk_ids"].long(),
+                                d["topk_weights"], model_dim, doweight)
+
+
+# --- the reference's numeric tests --------------------------------------------------------
+
+
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+@pytest.mark.parametrize("out_dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("tile_m,tokens", [(64, 128), (16, 8)])
+def test_moe_gemm1_numeric(dev, in_dtype, out_dtype, tile_m, tokens):
+    d = moe_oracle.make_inputs(tokens, SHAPE["model_dim"], SHAPE["inter_dim"], SHAPE["experts"], SHAPE["topk"], in_dtype, seed=tokens)
+    out = run_stage1(dev, d, **SHAPE, tile_m=tile_m, in_dtype=in_dtype, out_dtype=out_dtype, use_compile=True)
+    close_enough(out.view(tokens, SHAPE["topk"], -1), ref_stage1(d, SHAPE["inter_dim"]), "stage 1")
+
+
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+@pytest.mark.parametrize("accumulate,out_dtype", [(True, "f16"), (True, "bf16"), (True, "f32"), (False, "f16"), (False, "bf16")])
+@pytest.mark.parametrize("tile_m,tokens", [(16, 8), (64, 128)])
+def test_moe_gemm2_numeric(dev, accumulate, out_dtype, tile_m, tokens, in_dtype):
+    d = moe_oracle.make_inputs(tokens, SHAPE["model_dim"], SHAPE["inter_dim"], SHAPE["experts"], SHAPE["topk"], in_dtype, seed=100 + tokens)
+    out = run_stage2(dev, d, **SHAPE, tile_m=tile_m, in_dtype=in_dtype, out_dtype=out_dtype, accumulate=accumulate)
+    got = out if accumulate else out.view(tokens, SHAPE["topk"], -1).float().sum(dim=1)
+    close_enough(got, ref_stage2(d, SHAPE["model_dim"]), "stage 2")
+
+
+# --- wider shapes: several blocks per expert, partial channel tiles, odd routing block sizes ---
+
+
+@pytest.mark.parametrize(
+    "tokens,model_dim,inter_dim,experts,topk,tile_m",
+    [
+        (300, 1024, 512, 8, 2, 32),    # many blocks per expert
+        (300, 512, 256, 8, 4, 128),
+        (1000, 512, 256, 4, 2, 256),   # widest routing block
+        (40, 384, 256, 4, 2, 48),      # tile_m not a power of two; odd number of 128-channel tiles in stage 2
+        (5, 256, 128, 16, 4, 16),      # more experts than routed rows: most experts have no block
+        (1, 128, 128, 2, 1, 16),       # one token, topk 1
+    ],
+)
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+def test_both_stages_wider_shapes(dev, in_dtype, tokens, model_dim, inter_dim, experts, topk, tile_m):
+    d = moe_oracle.make_inputs(tokens, model_dim, inter_dim, experts, topk, in_dtype, seed=tokens + experts)
+    kw = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, in_dtype=in_dtype)
+    out1 = run_stage1(dev, d, **kw, out_dtype="bf16")
+    close_enough(out1.view(tokens, topk, -1), ref_stage1(d, inter_dim), "stage 1")
+    out2 = run_stage2(dev, d, **kw, out_dtype="bf16", accumulate=False)
+    per_slot = moe_oracle.moe_gemm2_per_slot(d["a2_q"], d["w2_q"], d["scale_a2"], d["scale_w2"], d["topk_ids"].long(),
+                                             d["topk_weights"], model_dim, True)
+    close_enough(out2.view(tokens, topk, -1), per_slot, "stage 2 per slot")
+    out2a = run_stage2(dev, d, **kw, out_dtype="f32", accumulate=True)
+    close_enough(out2a, ref_stage2(d, model_dim), "stage 2 accumulated", rel=2e-3)
+
+
+def test_stage1_partial_channel_tile(dev):
+    """inter_dim = 192: the second channel tile of stage 1 has 64 of its 128 channels."""
+    tokens, model_dim, inter_dim, experts, topk = 50, 256, 192, 4, 2
+    g = torch.Generator().manual_seed(12)
+    ids, wts = moe_oracle.make_routing(tokens, experts, topk, g)
+    x_q, sx = moe_oracle.pertoken_quant(torch.randn(tokens, model_dim, generator=g), torch.float8_e4m3fn)
+    w1_q, sw1 = moe_oracle.pertoken_quant(torch.randn(experts, 2 * inter_dim, model_dim, generator=g) / 16, torch.float8_e4m3fn)
+    d = dict(topk_ids=ids, topk_weights=wts, x_q=x_q, scale_x=sx, w1_q=w1_q, scale_w1=sw1)
+    out = run_stage1(dev, d, model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=32,
+                     in_dtype="fp8", out_dtype="bf16", extra_rows=8)
+    close_enough(out[: tokens * topk].view(tokens, topk, -1), ref_stage1(d, inter_dim), "stage 1, inter_dim 192")
+    assert torch.all(out[tokens * topk:] == 7.0)
+
+
+def test_stage1_routed_weight(dev):
+    d = moe_oracle.make_inputs(64, 256, 128, 4, 2, "fp8", seed=9)
+    out = run_stage1(dev, d, **SHAPE, tile_m=32, in_dtype="fp8", out_dtype="bf16", doweight=True)
+    close_enough(out.view(64, 2, -1), ref_stage1(d, 128, doweight=True), "stage 1 with routed weight")
+
+
+def test_stage2_without_routed_weight(dev):
+    d = moe_oracle.make_inputs(64, 256, 128, 4, 2, "int8", seed=10)
+    out = run_stage2(dev, d, **SHAPE, tile_m=32, in_dtype="int8", out_dtype="f32", accumulate=True, doweight=False)
+    close_enough(out, ref_stage2(d, 256, doweight=False), "stage 2 without routed weight", rel=2e-3)
+
+
+# --- guards: rows that are not routed stay untouched -----------------------------------------
+
+
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+@pytest.mark.parametrize("tile_m,tokens", [(16, 8), (64, 100)])
+def test_output_canary(dev, in_dtype, tile_m, tokens):
+    d = moe_oracle.make_inputs(tokens, SHAPE["model_dim"], SHAPE["inter_dim"], SHAPE["experts"], SHAPE["topk"], in_dtype, seed=3)
+    out1 = run_stage1(dev, d, **SHAPE, tile_m=tile_m, in_dtype=in_dtype, out_dtype="bf16", extra_rows=64)
+    assert torch.all(out1[tokens * SHAPE["topk"]:] == 7.0)
+    for accumulate in (True, False):
+        out2 = run_stage2(dev, d, **SHAPE, tile_m=tile_m, in_dtype=in_dtype, out_dtype="bf16", accumulate=accumulate, extra_rows=64)
+        rows = tokens if accumulate else tokens * SHAPE["topk"]
+        assert torch.all(out2[rows:] == 7.0)
+
+
+def test_num_valid_ids_guard(dev):
+    """Blocks at or past num_valid_ids[0] do no work (tests/kernels/test_moe_gemm_2stage.py:1810-1866)."""
+    tokens, tile_m = 64, 16
+    d = moe_oracle.make_inputs(tokens, SHAPE["model_dim"], SHAPE["inter_dim"], SHAPE["experts"], SHAPE["topk"], "fp8", seed=4)
+    ids, w, e_ids, n_valid, blocks = routing_on(dev, d, SHAPE["experts"], tile_m)
+    cut = (int(n_valid[0]) // tile_m // 2) * tile_m  # only the first half of the blocks is in use
+    n_cut = torch.tensor([cut], dtype=torch.int32, device=dev)
+    out1 = run_stage1(dev, d, **SHAPE, tile_m=tile_m, in_dtype="fp8", out_dtype="bf16", routing=(ids, w, e_ids, n_cut, blocks))
+    ref = ref_stage1(d, SHAPE["inter_dim"]).view(tokens * SHAPE["topk"], -1)
+    keep = torch.zeros(tokens * SHAPE["topk"], dtype=torch.bool)
+    srt = ids.cpu()[:cut]
+    tok, slot = srt & 0xFFFFFF, srt >> 24
+    ok = tok < tokens
+    keep[(tok[ok] * SHAPE["topk"] + slot[ok]).long()] = True
+    got = out1.float().cpu()
+    assert torch.all(got[~keep] == 7.0)
+    close_enough(got[keep], ref[keep], "rows of the blocks in use")
+
+
+def test_expert_id_minus_one_blocks_are_skipped(dev):
+    tokens, tile_m = 32, 16
+    d = moe_oracle.make_inputs(tokens, SHAPE["model_dim"], SHAPE["inter_dim"], SHAPE["experts"], SHAPE["topk"], "int8", seed=6)
+    ids, w, e_ids, n_valid, blocks = routing_on(dev, d, SHAPE["experts"], tile_m)
+    e_ids = e_ids.clone()
+    e_ids[0] = -1  # the first block loses its expert
+    out = run_stage2(dev, d, **SHAPE, tile_m=tile_m, in_dtype="int8", out_dtype="bf16", accumulate=False,
+                     routing=(ids, w, e_ids, n_valid, blocks))
+    srt = ids.cpu()[:tile_m]
+    tok, slot = srt & 0xFFFFFF, srt >> 24
+    ok = tok < tokens
+    rows = (tok[ok] * SHAPE["topk"] + slot[ok]).long()
+    assert torch.all(out.cpu()[rows] == 0)
+
+
+# --- the pieces around the GEMM ---------------------------------------------------------------
+
+
+def test_gather_rows_bit_exact(dev):
+    lib = _lib.load()
+    tokens, topk, experts, tile_m, k = 37, 2, 4, 16, 256
+    g = torch.Generator().manual_seed(1)
+    ids_t, w_t = moe_oracle.make_routing(tokens, experts, topk, g)
+    ids, _, e_ids, post = moe_sorting(ids_t.to(dev), w_t.to(dev), num_experts=experts, block_size=tile_m)
+    rows = int(e_ids.numel()) * tile_m
+    for by_slot in (0, 1):
+        n_src = tokens * (topk if by_slot else 1)
+        src = torch.randint(0, 256, (n_src, k), dtype=torch.uint8, generator=g).to(dev)
+        ssc = torch.rand(n_src, generator=g).to(dev)
+        dst = torch.full((rows, k), 0xAB, dtype=torch.uint8, device=dev)
+        dsc = torch.full((rows,), -1.0, device=dev)
+        _lib.check(lib.flyb200_moe_gather_rows(dst.data_ptr(), dsc.data_ptr(), src.data_ptr(), ssc.data_ptr(), ids.data_ptr(),
+                                               post.data_ptr(), tokens, topk, by_slot, k, rows, None), "gather")
+        torch.cuda.synchronize()
+        srt = torch.full((rows,), (topk << 24) | tokens, dtype=torch.int64)  # the id list may end inside the last block
+        srt[: min(rows, ids.numel())] = ids.cpu()[:rows].long()
+        tok, slot = srt & 0xFFFFFF, srt >> 24
+        valid = (tok < tokens) & (torch.arange(rows) < int(post[0]))
+        want = torch.zeros((rows, k), dtype=torch.uint8)
+        want_s = torch.zeros(rows)
+        r = (tok * topk + slot) if by_slot else tok
+        want[valid] = src.cpu()[r[valid]]
+        want_s[valid] = ssc.cpu()[r[valid]]
+        assert torch.equal(dst.cpu(), want) and torch.equal(dsc.cpu(), want_s)
+
+
+@pytest.mark.parametrize("dtype_str", ["f16", "bf16"])
+def test_topk_reduction(dev, dtype_str):
+    tokens, topk, dim = 77, 4, 384
+    x = torch.randn(tokens, topk, dim, device=dev).to(OUT_T[dtype_str])
+    y = torch.full((tokens + 3, dim), 7.0, dtype=OUT_T[dtype_str], device=dev)
+    compile_moe_reduction(topk=topk, model_dim=dim, dtype_str=dtype_str)(x, y, None, None, tokens, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert torch.equal(y[:tokens], x.float().sum(dim=1).to(OUT_T[dtype_str]))
+    assert torch.all(y[tokens:] == 7.0)
+
+
+def test_two_stage_pipeline_end_to_end(dev):
+    """x -> stage 1 -> per-token quantisation on the GPU -> stage 2 (per slot) -> top-k reduction."""
+    from flydsl_b200 import pertoken_quant
+
+    tokens, model_dim, inter_dim, experts, topk, tile_m = 200, 512, 256, 8, 2, 64
+    d = moe_oracle.make_inputs(tokens, model_dim, inter_dim, experts, topk, "fp8", seed=21)
+    kw = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, in_dtype="fp8")
+    out1 = run_stage1(dev, d, **kw, out_dtype="bf16")
+    a2_q, a2_s = pertoken_quant(out1.view(tokens, topk, inter_dim), quant_dtype=torch.float8_e4m3fn)
+    d2 = dict(d, a2_q=a2_q.cpu(), scale_a2=a2_s.cpu())
+    out2 = run_stage2(dev, d2, **kw, out_dtype="bf16", accumulate=False)
+    y = torch.empty(tokens, model_dim, dtype=torch.bfloat16, device=dev)
+    compile_moe_reduction(topk=topk, model_dim=model_dim, dtype_str="bf16")(out2, y, None, None, tokens, None)
+    torch.cuda.synchronize()
+    # oracle on the same chain, with its own (fp32) stage-1 output quantised
+    close_enough(y, ref_stage2(d, model_dim), "two-stage pipeline", rel=5e-2)
