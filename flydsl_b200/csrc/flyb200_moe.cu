@@ -22,10 +22,14 @@ constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Ring depth: as many stages of two weight tiles and one token tile as fit, at most 8.
+// Ring depth.  Up to 128 tokens per block two CTAs share an SM (half of its
+// shared memory and of its 512 TMEM columns each), so that one CTA's set-up and
+// epilogue overlap the other's mainloop and a grid of up to 296 CTAs runs as one
+// wave; 256-token blocks need all TMEM columns and get the whole SM.
 inline int moe_stages(int bn) {
   const int stage = 2 * BLOCK_ROWS * KBLOCK_BYTES + bn * KBLOCK_BYTES;
-  int n = (SMEM_LIMIT - 1024 - 12 * bn) / stage;
+  const int budget = bn <= 128 ? (SMEM_LIMIT + 1024) / 2 - 1024 : SMEM_LIMIT;
+  int n = (budget - 1024 - 12 * bn) / stage;
   return n > 8 ? 8 : n;
 }
 
