@@ -5,6 +5,7 @@
 #include "moe_kernel.cuh"
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -51,6 +52,63 @@ int launch_moe(const CUtensorMap& tmA, MoeParams p, int blocks, cudaStream_t s) 
   kernel<<<dim3(blocks, tiles, 1), MOE_THREADS, L.total, s>>>(tmA, p);
   CUDA_TRY(cudaGetLastError());
   return FLYB200_OK;
+}
+
+int sm_count(int* out) {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FLYB200_E_UNSUPPORTED;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  *out = n;
+  return FLYB200_OK;
+}
+
+// Persistent form for routing blocks that are a multiple of 128 rows.
+template <int KIND, int STAGE, int OUTMODE, bool ACCUM>
+int launch_moe_rows(const CUtensorMap& tmA, const MoeParams& p, int blocks, cudaStream_t s) {
+  static std::atomic<uint64_t> done{0};
+  auto kernel = moe_rows_kernel<KIND, STAGE, OUTMODE, ACCUM>;
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  const uint64_t bit = 1ull << dev;
+  if (!(done.load(std::memory_order_acquire) & bit)) {
+    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MoeRowsSmem::TOTAL));
+    done.fetch_or(bit, std::memory_order_release);
+  }
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc) return rc;
+  const long long row_blocks = static_cast<long long>(blocks) * p.tile_m / BLOCK_ROWS;
+  const int pairs = STAGE == 1 ? (p.n_out + BLOCK_ROWS - 1) / BLOCK_ROWS : (p.n_out + MOE_ROWS_BN - 1) / MOE_ROWS_BN;
+  const long long items = row_blocks * pairs;
+  const int grid = static_cast<int>(items < sms ? items : sms);
+  kernel<<<grid, NUM_THREADS, MoeRowsSmem::TOTAL, s>>>(tmA, p);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+template <int KIND>
+int launch_moe_rows_variant(int stage, int out_dtype, bool accumulate, const CUtensorMap& tmA, const MoeParams& p,
+                            int blocks, cudaStream_t s) {
+  if (stage == 1) {
+    if (out_dtype == FLYB200_OUT_BF16) return launch_moe_rows<KIND, 1, MOE_OUT_BF16, false>(tmA, p, blocks, s);
+    if (out_dtype == FLYB200_OUT_FP16) return launch_moe_rows<KIND, 1, MOE_OUT_FP16, false>(tmA, p, blocks, s);
+    return FLYB200_E_UNSUPPORTED;
+  }
+  if (accumulate) {
+    if (out_dtype == FLYB200_OUT_BF16) return launch_moe_rows<KIND, 2, MOE_OUT_BF16, true>(tmA, p, blocks, s);
+    if (out_dtype == FLYB200_OUT_FP16) return launch_moe_rows<KIND, 2, MOE_OUT_FP16, true>(tmA, p, blocks, s);
+    if (out_dtype == FLYB200_OUT_F32) return launch_moe_rows<KIND, 2, MOE_OUT_F32, true>(tmA, p, blocks, s);
+    return FLYB200_E_UNSUPPORTED;
+  }
+  if (out_dtype == FLYB200_OUT_BF16) return launch_moe_rows<KIND, 2, MOE_OUT_BF16, false>(tmA, p, blocks, s);
+  if (out_dtype == FLYB200_OUT_FP16) return launch_moe_rows<KIND, 2, MOE_OUT_FP16, false>(tmA, p, blocks, s);
+  return FLYB200_E_UNSUPPORTED;
 }
 
 template <int KIND, int BN>
@@ -148,12 +206,22 @@ int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_s
   int rc = host::status_word(&p.status);
   if (rc) return rc;
 
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUtensorMap tmA;
+  // Routing blocks of 128 or 256 rows: persistent kernel with the tokens on the
+  // UMMA M side (FLYB200_MOE_KERNEL=1 in the environment forces the other form, for tests and tuning).
+  const char* force = getenv("FLYB200_MOE_KERNEL");
+  const bool rows_form = tile_m % BLOCK_ROWS == 0 && !(force && force[0] == '1');
+  if (rows_form) {
+    rc = host::byte_matrix_map(&tmA, a_sorted, static_cast<uint64_t>(K), static_cast<uint64_t>(blocks) * tile_m, BLOCK_ROWS);
+    if (rc) return rc;
+    if (in_dtype == FLYB200_DT_FP8) return launch_moe_rows_variant<KIND_F8>(stage, out_dtype, accumulate != 0, tmA, p, blocks, s);
+    return launch_moe_rows_variant<KIND_I8>(stage, out_dtype, accumulate != 0, tmA, p, blocks, s);
+  }
   int bn = 16;
   while (bn < tile_m) bn *= 2;
-  CUtensorMap tmA;
   rc = host::byte_matrix_map(&tmA, a_sorted, static_cast<uint64_t>(K), static_cast<uint64_t>(blocks) * tile_m, bn);
   if (rc) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (in_dtype == FLYB200_DT_FP8) return launch_moe_bn<KIND_F8>(bn, stage, out_dtype, accumulate != 0, tmA, p, blocks, s);
   return launch_moe_bn<KIND_I8>(bn, stage, out_dtype, accumulate != 0, tmA, p, blocks, s);
 }

@@ -70,8 +70,9 @@ __device__ __forceinline__ uint64_t l2_policy_evict_normal() {
   return p;
 }
 
-// x * sigmoid(x)
-__device__ __forceinline__ float silu_f32(float x) { return x * (1.0f / (1.0f + __expf(-x))); }
+// x * sigmoid(x), with the fast exponential and reciprocal as in the reference's
+// epilogue (exp2 and rcp, kernels/moe/moe_gemm_2stage/layout_helpers.py:247-248)
+__device__ __forceinline__ float silu_f32(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // Two neighbouring channels (lo at `col`, hi at `col + 1`) of one output row.
 template <int OUTMODE, bool ACCUM>
@@ -351,6 +352,350 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gemm_kernel(const __grid_cons
           if (has_b) moe_emit16<OUTMODE, ACCUM>(p.out, vb, row_s, c0, p.tile_m, ch, n_valid[1], col0[1], p.n_out);
         }
       }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Large routing blocks (tile_m a multiple of 128): persistent form
+// ---------------------------------------------------------------------------
+// Tokens on the UMMA M side (128 sorted rows per work item), the two weight
+// tiles side by side on the N side (256 channels: stage 1 gate | up, stage 2 two
+// neighbouring tiles), one CTA per SM walking the (row block, channel pair)
+// items, a shared-memory ring that keeps streaming across items and two TMEM
+// accumulators so that the epilogue of an item overlaps the mainloop of the
+// next.  A thread of the epilogue owns one token row: it reads the gate and up
+// columns of the same channel from its own TMEM lane and writes 64 contiguous
+// bytes of its output row per 32-channel chunk.
+constexpr int MOE_ROWS_STAGES = 4;
+constexpr int MOE_ROWS_BN = 2 * BLOCK_ROWS;
+constexpr int MOE_ROWS_GROUP = 32;  // row blocks per rasterisation group (16 MiB of activations at K = 4096)
+
+struct MoeRowsSmem {
+  static constexpr int A_STAGE = BLOCK_ROWS * KBLOCK_BYTES;
+  static constexpr int B_STAGE = MOE_ROWS_BN * KBLOCK_BYTES;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + MOE_ROWS_STAGES * A_STAGE;
+  static constexpr int OFF_SW = OFF_B + MOE_ROWS_STAGES * B_STAGE;   // 4 warps x 256 weight scales
+  static constexpr int OFF_BAR = OFF_SW + 4 * MOE_ROWS_BN * 4;       // full[S], empty[S], tfull[2], tempty[2]
+  static constexpr int OFF_MISC = OFF_BAR + 8 * (2 * MOE_ROWS_STAGES + 4);
+  static constexpr int TOTAL = OFF_MISC + 16;
+};
+
+template <int OUTMODE, bool ACCUM>
+__device__ __forceinline__ void moe_store_row32(void* out, size_t elem, const float (&y)[32], int n_ok) {
+  // 32 consecutive channels of one output row; n_ok (a multiple of 16) of them exist
+  if constexpr (!ACCUM && OUTMODE != MOE_OUT_F32) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if constexpr (OUTMODE == MOE_OUT_BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+        pk[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
+        pk[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + elem);
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      if (8 * v < n_ok) dst[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (2 * i < n_ok) moe_store_pair<OUTMODE, ACCUM>(out, elem + 2 * i, y[2 * i], y[2 * i + 1]);
+  }
+}
+
+template <int KIND, int STAGE, int OUTMODE, bool ACCUM>
+__global__ void __launch_bounds__(NUM_THREADS, 1) moe_rows_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                  const MoeParams p) {
+  static_assert(STAGE == 2 || !ACCUM, "only the down projection accumulates");
+  using L = MoeRowsSmem;
+  using KT = KindTraits<KIND>;
+  constexpr int STAGES = MOE_ROWS_STAGES;
+  constexpr int BN = MOE_ROWS_BN;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = smem_u32(smem_raw);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L::OFF_MISC + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L::OFF_MISC);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t bar_full = smem_base + L::OFF_BAR;
+  const uint32_t bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+
+  if ((smem_base & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_SMEM_ALIGN);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 4);
+    }
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+  }
+  constexpr uint32_t TMEM_COLS = 512;
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Work items: (row block of 128 sorted rows, channel pair).  Row blocks run
+  // fastest, so CTAs working side by side share the weight tiles of an expert,
+  // and they are taken in groups of MOE_ROWS_GROUP whose activation rows stay in
+  // L2 while the group walks all channel pairs.
+  const int n_rows = __ldg(p.num_valid);
+  const int row_blocks = (n_rows + BLOCK_ROWS - 1) / BLOCK_ROWS;
+  const int pairs = STAGE == 1 ? (p.n_out + BLOCK_ROWS - 1) / BLOCK_ROWS : (p.n_out + BN - 1) / BN;
+  const int items = row_blocks * pairs;
+  const int num_kb = p.K_bytes / KBLOCK_BYTES;
+  auto item_coords = [&](int t, int& rb, int& pair) {
+    const int per_group = MOE_ROWS_GROUP * pairs;
+    const int g = t / per_group;
+    const int first = g * MOE_ROWS_GROUP;
+    const int gm = min(MOE_ROWS_GROUP, row_blocks - first);
+    const int r = t - g * per_group;
+    rb = first + r % gm;
+    pair = r / gm;
+  };
+  // expert of a row block, or -1 when the block has none
+  auto expert_of = [&](int rb) {
+    const int e = __ldg(p.expert_ids + (rb * BLOCK_ROWS) / p.tile_m);
+    return (e < 0 || e >= p.experts) ? -1 : e;
+  };
+  // rows of the image and channels that exist for the two tiles of a pair
+  auto tiles_of = [&](int pair, int (&w_row)[2], int (&n_valid)[2]) {
+    if constexpr (STAGE == 1) {
+      const int c = pair * BLOCK_ROWS;
+      w_row[0] = c;
+      w_row[1] = p.n_out + c;
+      n_valid[0] = n_valid[1] = min(BLOCK_ROWS, p.n_out - c);
+    } else {
+      const int c = pair * BN;
+      w_row[0] = c;
+      w_row[1] = c + BLOCK_ROWS;
+      n_valid[0] = min(BLOCK_ROWS, p.n_out - c);
+      n_valid[1] = max(0, min(BLOCK_ROWS, p.n_out - c - BLOCK_ROWS));
+    }
+  };
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      const uint64_t pol = l2_policy_evict_last();
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
+        int rb, pair;
+        item_coords(t, rb, pair);
+        const int expert = expert_of(rb);
+        if (expert < 0) continue;
+        int w_row[2], n_valid[2];
+        tiles_of(pair, w_row, n_valid);
+        const uint8_t* w_expert = p.w + static_cast<size_t>(expert) * p.n_expert * p.K_bytes;
+        const uint32_t b0 = static_cast<uint32_t>(n_valid[0]) * KBLOCK_BYTES, b1 = static_cast<uint32_t>(n_valid[1]) * KBLOCK_BYTES;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+            report_failure(p.status, ST_TIMEOUT, abort_flag);
+            ok = false;
+            break;
+          }
+          const uint32_t fb = bar_full + 8 * stage;
+          mbar_expect_tx(fb, L::A_STAGE + b0 + b1);
+          tma_load_2d(smem_base + L::OFF_A + stage * L::A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, rb * BLOCK_ROWS, pol);
+          const uint32_t bdst = smem_base + L::OFF_B + stage * L::B_STAGE;
+          bulk_load_1d(bdst, w_expert + (static_cast<size_t>(kb) * p.n_expert + w_row[0]) * KBLOCK_BYTES, b0, fb, pol);
+          if (b1)
+            bulk_load_1d(bdst + BLOCK_ROWS * KBLOCK_BYTES,
+                         w_expert + (static_cast<size_t>(kb) * p.n_expert + w_row[1]) * KBLOCK_BYTES, b1, fb, pol);
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        const int pending = min(issued, STAGES);
+        for (int i = 0; i < pending; ++i) {
+          int s = stage - 1 - i;
+          uint32_t ph = phase;
+          if (s < 0) {
+            s += STAGES;
+            ph ^= 1u;
+          }
+          mbar_wait(bar_full + 8 * s, ph, abort_flag + 1);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issue -----------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, BLOCK_ROWS, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
+        int rb, pair;
+        item_coords(t, rb, pair);
+        if (expert_of(rb) < 0) continue;
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+          report_failure(p.status, ST_TIMEOUT, abort_flag);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+            report_failure(p.status, ST_TIMEOUT, abort_flag);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L::OFF_A + stage * L::A_STAGE);
+          const uint64_t bdesc = umma_desc_sw128_kmajor(smem_base + L::OFF_B + stage * L::B_STAGE);
+#pragma unroll
+          for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
+            umma_ss<KIND>(d_tmem, adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                          bdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(bar_tfull + 8 * acc);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    float* sw_s = reinterpret_cast<float*>(smem_raw + L::OFF_SW) + (warp - 2) * BN;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
+      int rb, pair;
+      item_coords(t, rb, pair);
+      const int expert = expert_of(rb);
+      if (expert < 0) continue;
+      int w_row[2], n_valid[2];
+      tiles_of(pair, w_row, n_valid);
+      // this thread's token row
+      const int srow = rb * BLOCK_ROWS + q * 32 + lane;
+      long long orow = -1;
+      float sa = 0.0f, tw = 1.0f;
+      if (srow < n_rows) {
+        const int id = __ldg(p.sorted_ids + srow);
+        const int tok = id & 0xFFFFFF;
+        const int slot = static_cast<int>(static_cast<uint32_t>(id) >> 24);
+        if (tok < p.tokens && slot < p.topk) {
+          orow = (STAGE == 2 && ACCUM) ? tok : static_cast<long long>(tok) * p.topk + slot;
+          sa = __ldg(p.sa + srow);
+          if (p.doweight) tw = __ldg(p.sorted_w + srow);
+        }
+      }
+      // weight scales of the 256 columns, one copy per warp
+      const float* sw_expert = p.sw + static_cast<size_t>(expert) * p.n_expert;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < BN / 32; ++i) {
+        const int c = i * 32 + lane;
+        const int h = c >> 7, cc = c & 127;
+        sw_s[c] = cc < n_valid[h] ? __ldg(sw_expert + w_row[h] + cc) : 0.0f;
+      }
+      __syncwarp();
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+        if (lane == 0) report_failure(p.status, ST_TIMEOUT, abort_flag);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      auto to_f = [](uint32_t r) { return KT::is_int ? static_cast<float>(static_cast<int32_t>(r)) : __uint_as_float(r); };
+      if constexpr (STAGE == 1) {
+        const int col0 = pair * BLOCK_ROWS;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BLOCK_ROWS; c0 += 32) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_x32(t_row + c0, rg);
+          tmem_ld_x32(t_row + BLOCK_ROWS + c0, ru);
+          tmem_ld_wait();
+          if (c0 + 32 >= BLOCK_ROWS) {  // last read of this accumulator: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+          }
+          float y[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float g = (to_f(rg[j]) * sw_s[c0 + j]) * sa;
+            const float u = (to_f(ru[j]) * sw_s[BLOCK_ROWS + c0 + j]) * sa;
+            float v = silu_f32(g) * u;
+            if (p.doweight) v *= tw;
+            y[j] = v;
+          }
+          const int n_ok = min(32, n_valid[0] - c0);
+          if (orow >= 0 && n_ok > 0)
+            moe_store_row32<OUTMODE, ACCUM>(p.out, static_cast<size_t>(orow) * p.n_out + col0 + c0, y, n_ok);
+        }
+      } else {
+        const int col0 = pair * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t ra[32];
+          tmem_ld_x32(t_row + c0, ra);
+          tmem_ld_wait();
+          if (c0 + 32 >= BN) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+          }
+          float y[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = (to_f(ra[j]) * sw_s[c0 + j]) * sa;
+            y[j] = p.doweight ? v * tw : v;
+          }
+          const int h = c0 >> 7;
+          const int n_ok = min(32, n_valid[h] - (c0 & 127));
+          if (orow >= 0 && n_ok > 0)
+            moe_store_row32<OUTMODE, ACCUM>(p.out, static_cast<size_t>(orow) * p.n_out + col0 + c0, y, n_ok);
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
     }
   }
 

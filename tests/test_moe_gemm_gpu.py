@@ -159,6 +159,51 @@ def test_stage1_partial_channel_tile(dev):
     assert torch.all(out[tokens * topk:] == 7.0)
 
 
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+@pytest.mark.parametrize("out_dtype", ["f16", "bf16"])
+def test_large_routing_blocks_all_outputs(dev, in_dtype, out_dtype):
+    """tile_m = 128 runs the persistent form (tokens on the UMMA M side): every output mode,
+    a last channel tile of 64 channels in stage 1 and an odd number of tiles in stage 2."""
+    tokens, model_dim, inter_dim, experts, topk, tile_m = 333, 384, 256, 4, 2, 128
+    d = moe_oracle.make_inputs(tokens, model_dim, inter_dim, experts, topk, in_dtype, seed=33)
+    kw = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, in_dtype=in_dtype)
+    out1 = run_stage1(dev, d, **kw, out_dtype=out_dtype, extra_rows=16)
+    close_enough(out1[: tokens * topk].view(tokens, topk, -1), ref_stage1(d, inter_dim), "stage 1")
+    assert torch.all(out1[tokens * topk:] == 7.0)
+    for accumulate in (True, False):
+        out2 = run_stage2(dev, d, **kw, out_dtype=out_dtype, accumulate=accumulate, extra_rows=16)
+        rows = tokens if accumulate else tokens * topk
+        got = out2[:rows] if accumulate else out2[:rows].view(tokens, topk, -1).float().sum(dim=1)
+        close_enough(got, ref_stage2(d, model_dim), f"stage 2 accumulate={accumulate}")
+        assert torch.all(out2[rows:] == 7.0)
+
+
+def test_both_kernel_forms_agree(dev, monkeypatch):
+    """The persistent form and the two-tiles-per-CTA form do the same arithmetic per output element."""
+    tokens, model_dim, inter_dim, experts, topk, tile_m = 500, 512, 384, 4, 2, 128
+    d = moe_oracle.make_inputs(tokens, model_dim, inter_dim, experts, topk, "fp8", seed=34)
+    kw = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, in_dtype="fp8")
+    a1 = run_stage1(dev, d, **kw, out_dtype="bf16")
+    a2 = run_stage2(dev, d, **kw, out_dtype="bf16", accumulate=False)
+    monkeypatch.setenv("FLYB200_MOE_KERNEL", "1")
+    b1 = run_stage1(dev, d, **kw, out_dtype="bf16")
+    b2 = run_stage2(dev, d, **kw, out_dtype="bf16", accumulate=False)
+    assert torch.equal(a1, b1) and torch.equal(a2, b2)
+
+
+def test_stage1_partial_tile_large_block(dev):
+    tokens, model_dim, inter_dim, experts, topk = 150, 256, 192, 2, 2
+    g = torch.Generator().manual_seed(13)
+    ids, wts = moe_oracle.make_routing(tokens, experts, topk, g)
+    x_q, sx = moe_oracle.pertoken_quant(torch.randn(tokens, model_dim, generator=g), torch.int8)
+    w1_q, sw1 = moe_oracle.pertoken_quant(torch.randn(experts, 2 * inter_dim, model_dim, generator=g) / 16, torch.int8)
+    d = dict(topk_ids=ids, topk_weights=wts, x_q=x_q, scale_x=sx, w1_q=w1_q, scale_w1=sw1)
+    out = run_stage1(dev, d, model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=256,
+                     in_dtype="int8", out_dtype="bf16", extra_rows=8)
+    close_enough(out[: tokens * topk].view(tokens, topk, -1), ref_stage1(d, inter_dim), "stage 1, inter_dim 192, tile_m 256")
+    assert torch.all(out[tokens * topk:] == 7.0)
+
+
 def test_stage1_routed_weight(dev):
     d = moe_oracle.make_inputs(64, 256, 128, 4, 2, "fp8", seed=9)
     out = run_stage1(dev, d, **SHAPE, tile_m=32, in_dtype="fp8", out_dtype="bf16", doweight=True)
