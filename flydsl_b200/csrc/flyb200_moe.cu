@@ -49,8 +49,18 @@ int launch_moe(const CUtensorMap& tmA, MoeParams p, int blocks, cudaStream_t s) 
   const MoeLayout L = moe_layout(BN, p.stages);
   if (p.stages < 2 || L.total > SMEM_LIMIT) return FLYB200_E_UNSUPPORTED;
   const int tiles = STAGE == 1 ? (p.n_out + BLOCK_ROWS - 1) / BLOCK_ROWS : (p.n_out + 2 * BLOCK_ROWS - 1) / (2 * BLOCK_ROWS);
-  kernel<<<dim3(blocks, tiles, 1), MOE_THREADS, L.total, s>>>(tmA, p);
-  CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(blocks, tiles, 1);
+  cfg.blockDim = dim3(MOE_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = L.total;
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmA, p));
   return FLYB200_OK;
 }
 
@@ -168,7 +178,8 @@ int flyb200_moe_gather_rows(void* dst, float* dst_scale, const void* src, const 
 int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_shuf, const float* scale_a_sorted,
                      const float* scale_w, const int* sorted_ids, const int* expert_ids, const float* sorted_weights,
                      const int* num_valid_ids, int tokens, int topk, int experts, int model_dim, int inter_dim,
-                     int tile_m, int blocks, int in_dtype, int out_dtype, int doweight, int accumulate, void* stream) {
+                     int tile_m, int blocks, int in_dtype, int out_dtype, int doweight, int accumulate, int after_gather,
+                     void* stream) {
   if (stage != 1 && stage != 2) return FLYB200_E_BAD_ARG;
   if (!out || !a_sorted || !w_shuf || !scale_a_sorted || !scale_w || !sorted_ids || !expert_ids || !num_valid_ids)
     return FLYB200_E_BAD_ARG;
@@ -203,6 +214,7 @@ int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_s
   p.K_bytes = K;
   p.tile_m = tile_m;
   p.doweight = doweight ? 1 : 0;
+  p.pdl = 0;
   int rc = host::status_word(&p.status);
   if (rc) return rc;
 
@@ -220,6 +232,10 @@ int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_s
   }
   int bn = 16;
   while (bn < tile_m) bn *= 2;
+  {
+    const char* e = getenv("FLYB200_PDL");
+    p.pdl = (after_gather && !(e && e[0] == '0')) ? 1 : 0;
+  }
   rc = host::byte_matrix_map(&tmA, a_sorted, static_cast<uint64_t>(K), static_cast<uint64_t>(blocks) * tile_m, bn);
   if (rc) return rc;
   if (in_dtype == FLYB200_DT_FP8) return launch_moe_bn<KIND_F8>(bn, stage, out_dtype, accumulate != 0, tmA, p, blocks, s);

@@ -45,6 +45,7 @@ struct MoeParams {
   int tile_m;              // routing block size (<= BN)
   int stages;              // ring depth
   int doweight;            // multiply by the routed weight in this stage
+  int pdl;                 // launched as a programmatic dependent of the gather pass that writes a_sorted and sa
   int* status;
 };
 
@@ -220,20 +221,34 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gemm_kernel(const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      auto load_weights = [&](int kb, int st, uint32_t fb) {
+        mbar_expect_tx(fb, A_STAGE + w_bytes0 + w_bytes1);
+        const uint32_t wdst = smem_base + L.off_w + st * W_STAGE;
+        bulk_load_1d(wdst, w_expert + (static_cast<size_t>(kb) * p.n_expert + w_row[0]) * KBLOCK_BYTES, w_bytes0, fb,
+                     pol_w);
+        if (has_b)
+          bulk_load_1d(wdst + W_TILE, w_expert + (static_cast<size_t>(kb) * p.n_expert + w_row[1]) * KBLOCK_BYTES,
+                       w_bytes1, fb, pol_w);
+      };
+      // As a programmatic dependent of the gather pass the kernel may run before
+      // the gathered activations exist.  The weights are model state: the ring is
+      // filled with them first; everything the gather pass writes is touched only
+      // after griddepcontrol.wait.
+      const int pre = p.pdl ? min(stages, num_kb) : 0;
+      for (int i = 0; i < pre; ++i) load_weights(i, i, bar_full + 8 * i);
+      if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem_base + L.off_a + i * A_STAGE, &tmA, bar_full + 8 * i, i * KBLOCK_BYTES, row0, pol_a);
+      issued = pre;
+      if (pre == stages) phase = 1u; else stage = pre;
+      for (int kb = pre; kb < num_kb; ++kb) {
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
           report_failure(p.status, ST_TIMEOUT, abort_flag);
           ok = false;
           break;
         }
         const uint32_t fb = bar_full + 8 * stage;
-        mbar_expect_tx(fb, A_STAGE + w_bytes0 + w_bytes1);
-        const uint32_t wdst = smem_base + L.off_w + stage * W_STAGE;
-        bulk_load_1d(wdst, w_expert + (static_cast<size_t>(kb) * p.n_expert + w_row[0]) * KBLOCK_BYTES, w_bytes0, fb,
-                     pol_w);
-        if (has_b)
-          bulk_load_1d(wdst + W_TILE, w_expert + (static_cast<size_t>(kb) * p.n_expert + w_row[1]) * KBLOCK_BYTES,
-                       w_bytes1, fb, pol_w);
+        load_weights(kb, stage, fb);
         tma_load_2d(smem_base + L.off_a + stage * A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, row0, pol_a);
         ++issued;
         if (++stage == stages) {
@@ -294,6 +309,7 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gemm_kernel(const __grid_cons
     const int ch = q * 32 + lane;
     const int et = threadIdx.x - 64;
     const int n_rows = __ldg(p.num_valid);
+    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");  // p.sa is written by the gather pass
     for (int i = et; i < BN; i += 128) {
       int row = -1;
       float sa = 0.0f, tw = 1.0f;
@@ -717,6 +733,8 @@ __global__ void moe_gather_rows_kernel(uint8_t* __restrict__ dst, float* __restr
                                        const uint8_t* __restrict__ src, const float* __restrict__ src_scale,
                                        const int* __restrict__ sorted_ids, const int* __restrict__ num_valid, int tokens,
                                        int topk, int by_slot, int K_bytes, int rows) {
+  // a GEMM launched as programmatic dependent may start its weight stream now
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_valid = __ldg(num_valid);

@@ -165,7 +165,7 @@ class _MoeStage:
                     scale_w.data_ptr(), sorted_token_ids.data_ptr(), sorted_expert_ids.data_ptr(),
                     sorted_weights.data_ptr() if sorted_weights is not None and sorted_weights.numel() else None,
                     num_valid_ids.data_ptr(), tokens, self.topk, self.experts, self.model_dim, self.inter_dim,
-                    self.tile_m, blocks, self._dt, self._out, int(self.doweight), int(self.accumulate), s,
+                    self.tile_m, blocks, self._dt, self._out, int(self.doweight), int(self.accumulate), 1, s,
                 ),
                 "moe_gemm",
             )

@@ -253,12 +253,20 @@ int flyb200_moe_gather_rows(void* dst, float* dst_scale, const void* src, const 
  *   scale_w         one fp32 per weight row
  *   in_dtype        FLYB200_DT_FP8 or FLYB200_DT_INT8; out_dtype FLYB200_OUT_BF16 /
  *                   _FP16, or FLYB200_OUT_F32 for stage 2 with accumulate
+ *   after_gather    1: this call directly follows, on the same stream, the
+ *                   flyb200_moe_gather_rows call that writes a_sorted and
+ *                   scale_a_sorted, and no kernel on the stream writes the weights:
+ *                   the GEMM is then launched as a programmatic dependent of the
+ *                   gather pass and streams its first weight tiles while that pass
+ *                   still runs (it reads the gathered rows only after the pass has
+ *                   completed).  0: plain stream order.
  * Requirements: K (model_dim in stage 1, inter_dim in stage 2) a multiple of
  * 128, output row length a multiple of 16, tile_m a multiple of 16 in [16, 256]. */
 int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_shuf, const float* scale_a_sorted,
                      const float* scale_w, const int* sorted_ids, const int* expert_ids, const float* sorted_weights,
                      const int* num_valid_ids, int tokens, int topk, int experts, int model_dim, int inter_dim,
-                     int tile_m, int blocks, int in_dtype, int out_dtype, int doweight, int accumulate, void* stream);
+                     int tile_m, int blocks, int in_dtype, int out_dtype, int doweight, int accumulate, int after_gather,
+                     void* stream);
 
 /* y[token, dim] = sum over slots of x[token, slot, dim] (fp32 sum, one rounding);
  * dtype FLYB200_OUT_BF16 or FLYB200_OUT_FP16, dim even. */
