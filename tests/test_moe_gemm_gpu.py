@@ -323,3 +323,68 @@ def test_two_stage_pipeline_end_to_end(dev):
     torch.cuda.synchronize()
     # oracle on the same chain, with its own (fp32) stage-1 output quantised
     close_enough(y, ref_stage2(d, model_dim), "two-stage pipeline", rel=5e-2)
+
+
+@pytest.mark.parametrize("tile_m", [16, 128])
+def test_graph_replay_equals_eager(dev, tile_m):
+    """Both stages capture into a CUDA graph (no allocation or synchronisation on the launch path
+    once the gather scratch exists) and the replay reproduces the eager result bit for bit."""
+    tokens, model_dim, inter_dim, experts, topk = 96, 256, 128, 4, 2
+    d = moe_oracle.make_inputs(tokens, model_dim, inter_dim, experts, topk, "fp8", seed=40 + tile_m)
+    ids, w, e_ids, n_valid, blocks = routing_on(dev, d, experts, tile_m)
+    kw = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, tile_n=64, tile_k=128,
+              out_dtype="bf16", in_dtype="fp8")
+    g1 = compile_moe_gemm1(**kw, doweight_stage1=False)
+    g2 = compile_moe_gemm2(**kw, doweight_stage2=True, accumulate=False)
+    x, a2 = d["x_q"].to(dev), d["a2_q"].to(dev)
+    w1 = shuffle_weight(d["w1_q"].to(dev))
+    w2 = shuffle_weight(d["w2_q"].to(dev))
+    sx, sa2 = d["scale_x"].to(dev).view(-1), d["scale_a2"].to(dev).view(-1)
+    sw1, sw2 = d["scale_w1"].to(dev).view(-1), d["scale_w2"].to(dev).view(-1)
+    out1 = torch.zeros(tokens * topk, inter_dim, dtype=torch.bfloat16, device=dev)
+    out2 = torch.zeros(tokens * topk, model_dim, dtype=torch.bfloat16, device=dev)
+    st = torch.cuda.Stream()
+
+    def both():
+        g1(out1, x.view(-1), w1.view(-1), sx, sw1, ids, e_ids, w, n_valid, tokens, inter_dim, model_dim, blocks, st)
+        g2(out2, a2.view(-1), w2.view(-1), sa2, sw2, ids, e_ids, w, n_valid, tokens, model_dim, inter_dim, blocks, st.cuda_stream)
+
+    with torch.cuda.stream(st):
+        both()  # eager: also creates the gather scratch
+        st.synchronize()
+        eager1, eager2 = out1.clone(), out2.clone()
+        out1.zero_()
+        out2.zero_()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            both()
+        out1.zero_()
+        out2.zero_()
+        graph.replay()
+        st.synchronize()
+    assert torch.equal(out1, eager1) and torch.equal(out2, eager2)
+    assert _lib.read_status() == 0
+    close_enough(out1.view(tokens, topk, -1), ref_stage1(d, inter_dim), "stage 1 from the graph")
+
+
+def test_launch_argument_checks(dev):
+    d = moe_oracle.make_inputs(8, 256, 128, 4, 2, "fp8", seed=2)
+    ids, w, e_ids, n_valid, blocks = routing_on(dev, d, 4, 16)
+    exe = compile_moe_gemm1(**SHAPE, tile_m=16, tile_n=64, tile_k=128, doweight_stage1=False, out_dtype="bf16", in_dtype="fp8")
+    x = d["x_q"].to(dev)
+    w1 = shuffle_weight(d["w1_q"].to(dev))
+    sx, sw1 = d["scale_x"].to(dev).view(-1), d["scale_w1"].to(dev).view(-1)
+    out = torch.zeros(16, 128, dtype=torch.bfloat16, device=dev)
+    good = (out, x.view(-1), w1.view(-1), sx, sw1, ids, e_ids, w, n_valid, 8, 128, 256, blocks, None)
+    exe(*good)
+    with pytest.raises(ValueError, match="dims"):
+        exe(*good[:10], 256, 128, blocks, None)
+    with pytest.raises(ValueError, match="out must be"):
+        exe(out.half(), *good[1:])
+    with pytest.raises(ValueError, match="holds"):
+        exe(out[:4], *good[1:])
+    with pytest.raises(ValueError, match="int32"):
+        exe(*good[:5], ids.long(), *good[6:])
+    with pytest.raises(TypeError):
+        exe(*good[:13], "stream")
+    torch.cuda.synchronize()
