@@ -242,6 +242,34 @@ int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_s
   return launch_moe_bn<KIND_I8>(bn, stage, out_dtype, accumulate != 0, tmA, p, blocks, s);
 }
 
+int flyb200_moe_sorting(const int* topk_ids, const float* topk_weights, int tokens, int topk, int experts, int block_size,
+                        int* sorted_ids, float* sorted_weights, int* sorted_expert_ids, int* num_tokens_post_pad,
+                        int* counts_scratch, void* stream) {
+  if (!topk_ids || !topk_weights || !sorted_ids || !sorted_weights || !sorted_expert_ids || !num_tokens_post_pad ||
+      !counts_scratch)
+    return FLYB200_E_BAD_ARG;
+  if (tokens < 0 || topk <= 0 || topk > 255 || experts <= 0 || block_size <= 0) return FLYB200_E_BAD_ARG;
+  if (tokens >= (1 << 24)) return FLYB200_E_UNSUPPORTED;
+  const long long n_pairs = static_cast<long long>(tokens) * topk;
+  const long long max_padded = n_pairs + static_cast<long long>(experts) * block_size - topk;
+  if (max_padded > 0x7fffffffLL || max_padded <= 0) return FLYB200_E_UNSUPPORTED;
+  const int max_blocks = static_cast<int>((max_padded + block_size - 1) / block_size);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUDA_TRY(cudaMemsetAsync(counts_scratch, 0, sizeof(int) * experts, s));
+  long long work = max_padded > n_pairs ? max_padded : n_pairs;
+  int grid = static_cast<int>((work + 255) / 256);
+  if (grid > 148 * 4) grid = 148 * 4;
+  moe_sort_count_kernel<<<grid, 256, 0, s>>>(topk_ids, static_cast<int>(n_pairs), experts, counts_scratch, sorted_ids,
+                                             sorted_weights, static_cast<int>(max_padded), sorted_expert_ids, max_blocks,
+                                             (topk << 24) | tokens);
+  CUDA_TRY(cudaGetLastError());
+  moe_sort_place_kernel<<<experts, MOE_SORT_THREADS, 0, s>>>(topk_ids, topk_weights, static_cast<int>(n_pairs), topk,
+                                                             tokens, experts, block_size, counts_scratch, sorted_ids,
+                                                             sorted_weights, sorted_expert_ids, num_tokens_post_pad);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
 int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, void* stream) {
   if (!y || !x || tokens < 0 || topk <= 0 || dim <= 0) return FLYB200_E_BAD_ARG;
   if (dim % 2 != 0) return FLYB200_E_UNSUPPORTED;

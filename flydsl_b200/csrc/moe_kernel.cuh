@@ -758,6 +758,87 @@ __global__ void moe_gather_rows_kernel(uint8_t* __restrict__ dst, float* __restr
   }
 }
 
+// ---------------------------------------------------------------------------
+// Routing table (the layout tests/kernels/test_moe_gemm_2stage.py:99-137 of the
+// reference describes): counting sort of the (token, slot) pairs by expert,
+// stable, every expert's run padded to a multiple of block_size.
+// ---------------------------------------------------------------------------
+// Pass 1: fill the outputs with their padding values and count the pairs of every expert
+// (`counts` must be zero on entry).
+__global__ void moe_sort_count_kernel(const int* __restrict__ topk_ids, int n_pairs, int experts, int* __restrict__ counts,
+                                      int* __restrict__ sorted_ids, float* __restrict__ sorted_weights, int max_padded,
+                                      int* __restrict__ sorted_expert_ids, int max_blocks, int sentinel) {
+  const int stride = gridDim.x * blockDim.x;
+  const int t0 = blockIdx.x * blockDim.x + threadIdx.x;
+  for (int i = t0; i < max_padded; i += stride) {
+    sorted_ids[i] = sentinel;
+    sorted_weights[i] = 0.0f;
+  }
+  for (int i = t0; i < max_blocks; i += stride) sorted_expert_ids[i] = -1;
+  for (int i = t0; i < n_pairs; i += stride) {
+    const int e = __ldg(topk_ids + i);
+    if (e >= 0 && e < experts) atomicAdd(counts + e, 1);
+  }
+}
+
+// Pass 2: one CTA per expert walks the pairs in order and writes its run.
+constexpr int MOE_SORT_THREADS = 256;
+__global__ void __launch_bounds__(MOE_SORT_THREADS)
+moe_sort_place_kernel(const int* __restrict__ topk_ids, const float* __restrict__ topk_weights, int n_pairs, int topk,
+                      int tokens, int experts, int block_size, const int* __restrict__ counts,
+                      int* __restrict__ sorted_ids, float* __restrict__ sorted_weights,
+                      int* __restrict__ sorted_expert_ids, int* __restrict__ post_pad) {
+  __shared__ int warp_sums[MOE_SORT_THREADS / 32];
+  __shared__ int s_start;
+  const int e = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // first row of this expert: padded sizes of the experts before it
+  int part = 0;
+  for (int i = tid; i < e; i += MOE_SORT_THREADS) {
+    const int c = __ldg(counts + i);
+    part += (c + block_size - 1) / block_size * block_size;
+  }
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) warp_sums[warp] = part;
+  __syncthreads();
+  if (tid == 0) {
+    int t = 0;
+    for (int w = 0; w < MOE_SORT_THREADS / 32; ++w) t += warp_sums[w];
+    s_start = t;
+  }
+  __syncthreads();
+  const int start = s_start;
+  const int mine = __ldg(counts + e);
+  const int n_blk = (mine + block_size - 1) / block_size;
+  for (int i = tid; i < n_blk; i += MOE_SORT_THREADS) sorted_expert_ids[start / block_size + i] = e;
+  if (e == experts - 1 && tid == 0) {
+    post_pad[0] = start + n_blk * block_size;
+    post_pad[1] = tokens;
+  }
+  int base = 0;  // pairs of this expert seen so far
+  for (int c0 = 0; c0 < n_pairs && base < mine; c0 += MOE_SORT_THREADS) {
+    const int i = c0 + tid;
+    const bool hit = i < n_pairs && __ldg(topk_ids + i) == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+    const int in_warp = __popc(ballot & ((1u << lane) - 1u));
+    __syncthreads();  // warp_sums of the previous chunk have been read
+    if (lane == 0) warp_sums[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, total = 0;
+    for (int w = 0; w < MOE_SORT_THREADS / 32; ++w) {
+      const int v = warp_sums[w];
+      if (w < warp) before += v;
+      total += v;
+    }
+    if (hit) {
+      const int dst = start + base + before + in_warp;
+      sorted_ids[dst] = ((i % topk) << 24) | (i / topk);
+      sorted_weights[dst] = __ldg(topk_weights + i);
+    }
+    base += total;
+  }
+}
+
 // y[t, :] = sum over the top-k slots of x[t, slot, :] (fp32 sum, one rounding).
 template <typename T>
 __global__ void moe_reduce_kernel(T* __restrict__ y, const T* __restrict__ x, int tokens, int topk, int dim) {

@@ -17,9 +17,9 @@ otherwise hints (a CTA always takes two 128-channel weight tiles and 128-byte
 k-blocks).  ``in_dtype`` "fp8" and "int8" are built; "int8smooth" and "int4"
 raise ``ValueError``.
 
-``moe_sorting`` restates the routing-table layout the kernels consume
-(tests/kernels/test_moe_gemm_2stage.py:99-137) with torch ops on the tensors'
-own device.
+``moe_sorting`` builds the routing table the kernels consume (layout:
+tests/kernels/test_moe_gemm_2stage.py:99-137): on CUDA tensors with the
+library's counting-sort kernels, on CPU tensors with torch ops.
 """
 
 from __future__ import annotations
@@ -62,6 +62,25 @@ def moe_sorting(
     e, bs = int(num_experts), int(block_size)
     max_padded = int(topk_ids.numel() + e * bs - topk)
     max_blocks = (max_padded + bs - 1) // bs
+    if topk_ids.is_cuda:
+        # device kernels (flyb200_moe_sorting): no host synchronisation, capturable
+        ids32 = topk_ids.to(torch.int32).contiguous()
+        w32 = topk_weights.to(torch.float32).contiguous()
+        sorted_ids = torch.empty((max_padded,), dtype=torch.int32, device=dev)
+        sorted_weights = torch.empty((max_padded,), dtype=torch.float32, device=dev)
+        sorted_expert_ids = torch.empty((max_blocks,), dtype=torch.int32, device=dev)
+        post_pad = torch.empty((2,), dtype=torch.int32, device=dev)
+        counts = torch.empty((e,), dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(
+                _lib.load().flyb200_moe_sorting(
+                    ids32.data_ptr(), w32.data_ptr(), tokens, topk, e, bs, sorted_ids.data_ptr(), sorted_weights.data_ptr(),
+                    sorted_expert_ids.data_ptr(), post_pad.data_ptr(), counts.data_ptr(),
+                    torch.cuda.current_stream(dev).cuda_stream,
+                ),
+                "moe_sorting",
+            )
+        return sorted_ids, sorted_weights, sorted_expert_ids, post_pad
     flat = topk_ids.reshape(-1).to(torch.int64)
     order = torch.sort(flat, stable=True).indices  # by expert, then (token, slot)
     counts = torch.bincount(flat, minlength=e)[:e]

@@ -268,6 +268,20 @@ int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_s
                      int tile_m, int blocks, int in_dtype, int out_dtype, int doweight, int accumulate, int after_gather,
                      void* stream);
 
+/* Routing table from the router's choice: the device form of the reference's
+ * moe_sorting (layout stated in tests/kernels/test_moe_gemm_2stage.py:99-137; the
+ * reference's own device kernel is kernels/moe/moe_sorting_kernel.py).  A stable
+ * counting sort of the (token, slot) pairs by expert; three small launches on
+ * the stream, no host synchronisation, so the whole MoE layer can be captured.
+ *   topk_ids[tokens, topk] int32, topk_weights[tokens, topk] fp32
+ *   sorted_ids / sorted_weights  [tokens * topk + experts * block_size - topk]
+ *   sorted_expert_ids            [ceil(that / block_size)]
+ *   num_tokens_post_pad          [2] = { sorted rows in use, tokens }
+ *   counts_scratch               [experts] int32 (contents irrelevant on entry) */
+int flyb200_moe_sorting(const int* topk_ids, const float* topk_weights, int tokens, int topk, int experts, int block_size,
+                        int* sorted_ids, float* sorted_weights, int* sorted_expert_ids, int* num_tokens_post_pad,
+                        int* counts_scratch, void* stream);
+
 /* y[token, dim] = sum over slots of x[token, slot, dim] (fp32 sum, one rounding);
  * dtype FLYB200_OUT_BF16 or FLYB200_OUT_FP16, dim even. */
 int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, void* stream);

@@ -388,3 +388,31 @@ def test_launch_argument_checks(dev):
     with pytest.raises(TypeError):
         exe(*good[:13], "stream")
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize(
+    "tokens,experts,topk,block",
+    [(8, 4, 2, 16), (128, 4, 2, 64), (1000, 8, 2, 128), (5, 16, 4, 16), (1, 2, 1, 16), (4096, 64, 8, 32), (300, 256, 6, 16)],
+)
+def test_device_sorting_matches_oracle(dev, tokens, experts, topk, block):
+    g = torch.Generator().manual_seed(tokens + experts)
+    ids, wts = moe_oracle.make_routing(tokens, experts, topk, g)
+    want = moe_oracle.moe_sorting(ids, wts, experts, block)
+    got = moe_sorting(ids.to(dev), wts.to(dev), num_experts=experts, block_size=block)
+    torch.cuda.synchronize()
+    for name, a, b in zip(("sorted_ids", "sorted_weights", "sorted_expert_ids", "post_pad"), got, want):
+        assert torch.equal(a.cpu(), b), name
+
+
+def test_device_sorting_skewed_routing(dev):
+    """Everything routed to one expert; an expert id outside the range is ignored."""
+    ids = torch.full((70, 2), 3, dtype=torch.int32)
+    ids[:, 1] = 0
+    wts = torch.rand(70, 2)
+    want = moe_oracle.moe_sorting(ids, wts, 5, 32)
+    got = moe_sorting(ids.to(dev), wts.to(dev), num_experts=5, block_size=32)
+    for a, b in zip(got, want):
+        assert torch.equal(a.cpu(), b)
+    ids[0, 0] = 9
+    got = moe_sorting(ids.to(dev), wts.to(dev), num_experts=5, block_size=32)
+    assert int(got[3][0]) == 96 + 96  # 69 -> 96 rows for expert 3, 70 -> 96 for expert 0
