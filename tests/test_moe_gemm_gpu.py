@@ -416,3 +416,47 @@ def test_device_sorting_skewed_routing(dev):
     ids[0, 0] = 9
     got = moe_sorting(ids.to(dev), wts.to(dev), num_experts=5, block_size=32)
     assert int(got[3][0]) == 96 + 96  # 69 -> 96 rows for expert 3, 70 -> 96 for expert 0
+
+
+def test_whole_layer_in_one_graph(dev):
+    """Routing table, both stages, the quantiser in between and the top-k reduction captured into
+    ONE CUDA graph: nothing on the path synchronises with the host."""
+    from flydsl_b200 import pertoken_quant
+
+    tokens, model_dim, inter_dim, experts, topk, tile_m = 64, 256, 128, 4, 2, 32
+    d = moe_oracle.make_inputs(tokens, model_dim, inter_dim, experts, topk, "fp8", seed=50)
+    kw = dict(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, tile_n=64, tile_k=128,
+              out_dtype="bf16", in_dtype="fp8")
+    g1 = compile_moe_gemm1(**kw, doweight_stage1=False)
+    g2 = compile_moe_gemm2(**kw, doweight_stage2=True, accumulate=False)
+    red = compile_moe_reduction(topk=topk, model_dim=model_dim, dtype_str="bf16")
+    x = d["x_q"].to(dev)
+    w1, w2 = shuffle_weight(d["w1_q"].to(dev)), shuffle_weight(d["w2_q"].to(dev))
+    sx, sw1, sw2 = d["scale_x"].to(dev).view(-1), d["scale_w1"].to(dev).view(-1), d["scale_w2"].to(dev).view(-1)
+    t_ids, t_w = d["topk_ids"].to(dev), d["topk_weights"].to(dev)
+    y = torch.zeros(tokens, model_dim, dtype=torch.bfloat16, device=dev)
+    st = torch.cuda.Stream()
+
+    def layer():
+        ids, w, e_ids, post = moe_sorting(t_ids, t_w, num_experts=experts, block_size=tile_m)
+        blocks = int(e_ids.numel())
+        out1 = torch.empty(tokens * topk, inter_dim, dtype=torch.bfloat16, device=dev)
+        g1(out1, x.view(-1), w1.view(-1), sx, sw1, ids, e_ids, w, post, tokens, inter_dim, model_dim, blocks, st)
+        a2, sa2 = pertoken_quant(out1, quant_dtype=torch.float8_e4m3fn)
+        out2 = torch.empty(tokens * topk, model_dim, dtype=torch.bfloat16, device=dev)
+        g2(out2, a2.view(-1), w2.view(-1), sa2.view(-1), sw2, ids, e_ids, w, post, tokens, model_dim, inter_dim, blocks, st)
+        red(out2, y, None, None, tokens, st)
+
+    with torch.cuda.stream(st):
+        layer()
+        st.synchronize()
+        eager = y.clone()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            layer()
+        y.zero_()
+        graph.replay()
+        st.synchronize()
+    assert torch.equal(y, eager)
+    close_enough(y, ref_stage2(d, model_dim), "whole layer", rel=5e-2)
+    assert _lib.read_status() == 0
