@@ -161,7 +161,8 @@ int flyb200_moe_gather_rows(void* dst, float* dst_scale, const void* src, const 
                             const int* num_valid_ids, int tokens, int topk, int by_slot, int row_bytes, int rows,
                             void* stream) {
   if (!dst || !dst_scale || !src || !src_scale || !sorted_ids || !num_valid_ids) return FLYB200_E_BAD_ARG;
-  if (tokens < 0 || topk <= 0 || topk > 255 || row_bytes <= 0 || rows < 0) return FLYB200_E_BAD_ARG;
+  if (tokens < 0 || topk <= 0 || topk > 255 || row_bytes <= 0 || rows < 0 || by_slot < 0 || by_slot > 2)
+    return FLYB200_E_BAD_ARG;
   if (row_bytes % 16 != 0) return FLYB200_E_UNSUPPORTED;
   if (!aligned16(dst) || !aligned16(src)) return FLYB200_E_BAD_ALIGN;
   if (rows == 0) return FLYB200_OK;
@@ -170,7 +171,7 @@ int flyb200_moe_gather_rows(void* dst, float* dst_scale, const void* src, const 
   if (grid > 148 * 8) grid = 148 * 8;
   moe_gather_rows_kernel<<<grid, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<uint8_t*>(dst), dst_scale, static_cast<const uint8_t*>(src), src_scale, sorted_ids, num_valid_ids,
-      tokens, topk, by_slot ? 1 : 0, row_bytes, rows);
+      tokens, topk, by_slot, row_bytes, rows);
   CUDA_TRY(cudaGetLastError());
   return FLYB200_OK;
 }

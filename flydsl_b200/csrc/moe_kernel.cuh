@@ -726,8 +726,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) moe_rows_kernel(const __grid_c
 
 // Gather the activation rows (and their scales) into sorted order:
 //   dst[p, :] = src[row(p), :], dst_scale[p] = src_scale[row(p)]
-// with row(p) = token (by_slot == 0, stage 1) or token * topk + slot (stage 2);
-// rows that are padding, or past num_valid, become zero with scale zero.
+// with row(p) = token (by_slot == 0, stage 1), token * topk + slot (by_slot == 1,
+// stage 2) or slot * tokens + token (by_slot == 2: slot-major activations, the
+// reference's "int8smooth" stage 1); rows that are padding, or past num_valid,
+// become zero with scale zero.
 // One warp per row, 16 bytes per lane and step.
 __global__ void moe_gather_rows_kernel(uint8_t* __restrict__ dst, float* __restrict__ dst_scale,
                                        const uint8_t* __restrict__ src, const float* __restrict__ src_scale,
@@ -744,7 +746,9 @@ __global__ void moe_gather_rows_kernel(uint8_t* __restrict__ dst, float* __restr
       const int id = __ldg(sorted_ids + r);
       const int tok = id & 0xFFFFFF;
       const int slot = static_cast<int>(static_cast<uint32_t>(id) >> 24);
-      if (tok < tokens && slot < topk) srow = by_slot ? static_cast<long long>(tok) * topk + slot : tok;
+      if (tok < tokens && slot < topk)
+        srow = by_slot == 1 ? static_cast<long long>(tok) * topk + slot
+                            : by_slot == 2 ? static_cast<long long>(slot) * tokens + tok : tok;
     }
     uint4* d = reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * K_bytes);
     if (srow >= 0) {

@@ -14,8 +14,8 @@ The positional arguments are the reference's
 per expert.  ``tile_m`` is the routing block size the sorted ids were padded
 to; ``tile_n`` / ``tile_k`` are validated as the reference does and are
 otherwise hints (a CTA always takes two 128-channel weight tiles and 128-byte
-k-blocks).  ``in_dtype`` "fp8" and "int8" are built; "int8smooth" and "int4"
-raise ``ValueError``.
+k-blocks).  ``in_dtype`` "fp8", "int8" and "int8smooth" are built; "int4"
+(packed W4A8 weights) raises ``ValueError``.
 
 ``moe_sorting`` builds the routing table the kernels consume (layout:
 tests/kernels/test_moe_gemm_2stage.py:99-137): on CUDA tensors with the
@@ -41,7 +41,13 @@ _OUT = {
     "fp32": (_lib.OUT_F32, torch.float32),
     "float": (_lib.OUT_F32, torch.float32),
 }
-_IN = {"fp8": (_lib.DT_FP8, torch.float8_e4m3fn), "int8": (_lib.DT_INT8, torch.int8)}
+_IN = {
+    "fp8": (_lib.DT_FP8, torch.float8_e4m3fn),
+    "int8": (_lib.DT_INT8, torch.int8),
+    # int8 with per-route ("smooth-quantised") activations: stage 1 reads x and scale_x
+    # slot-major, [topk * tokens, ...] with row = slot * tokens + token; stage 2 is plain int8
+    "int8smooth": (_lib.DT_INT8, torch.int8),
+}
 _REFERENCE_IN_DTYPES = ("fp8", "int8", "int8smooth", "int4")
 
 
@@ -117,6 +123,7 @@ class _MoeStage:
         self._dt, self._torch_in = _IN[in_dtype]
         self._out, self._torch_out = _OUT[out_dtype]
         self._k = self.model_dim if stage == 1 else self.inter_dim
+        self._slot_major = stage == 1 and in_dtype == "int8smooth"
         self._scratch: dict = {}
 
     def _sorted_buffers(self, device, rows):
@@ -142,7 +149,7 @@ class _MoeStage:
                 raise ValueError(f"{name} must be a contiguous CUDA tensor")
         if out.dtype != self._torch_out:
             raise ValueError(f"out must be {self._torch_out}, got {out.dtype}")
-        x_rows = tokens if self.stage == 1 else tokens * self.topk
+        x_rows = tokens if (self.stage == 1 and not self._slot_major) else tokens * self.topk
         out_rows = tokens if (self.stage == 2 and self.accumulate) else tokens * self.topk
         w_rows = self.experts * (2 * self.inter_dim if self.stage == 1 else self.model_dim)
         need = (
@@ -174,7 +181,7 @@ class _MoeStage:
                 lib.flyb200_moe_gather_rows(
                     a_sorted.data_ptr(), sa_sorted.data_ptr(), x.data_ptr(), scale_x.data_ptr(),
                     sorted_token_ids.data_ptr(), num_valid_ids.data_ptr(), tokens, self.topk,
-                    0 if self.stage == 1 else 1, k, rows, s,
+                    (2 if self._slot_major else 0) if self.stage == 1 else 1, k, rows, s,
                 ),
                 "moe_gather_rows",
             )
@@ -195,7 +202,7 @@ def _check_common(model_dim, inter_dim, experts, topk, tile_m, tile_n, tile_k, i
     if in_dtype not in _REFERENCE_IN_DTYPES:
         raise ValueError(f"in_dtype must be 'fp8', 'int8', 'int8smooth', or 'int4', got {in_dtype!r}")
     if in_dtype not in _IN:
-        raise ValueError(f"in_dtype={in_dtype!r} is not built for B200 (fp8 and int8 are)")
+        raise ValueError(f"in_dtype={in_dtype!r} is not built for B200 (fp8, int8 and int8smooth are)")
     if min(int(model_dim), int(inter_dim), int(experts), int(topk)) <= 0:
         raise ValueError("model_dim, inter_dim, experts and topk must be positive")
     if not (16 <= int(tile_m) <= 256 and int(tile_m) % 16 == 0):

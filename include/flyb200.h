@@ -234,7 +234,9 @@ int flyb200_selftest_bounded_wait(unsigned int limit_us, void* stream);
 /* Activation rows and their scales gathered into sorted order (the A-gather the
  * reference does inside its kernels, gemm1.py:403-460 / gemm2.py:374-380):
  *   dst[p, :] = src[r, :], dst_scale[p] = src_scale[r], r = token (by_slot = 0,
- *   stage 1) or token * topk + slot (by_slot = 1, stage 2); padding rows and rows
+ *   stage 1), token * topk + slot (by_slot = 1, stage 2) or slot * tokens + token
+ *   (by_slot = 2: slot-major per-route activations, the reference's
+ *   in_dtype="int8smooth" in stage 1, gemm1.py:36-39,321-333); padding rows and rows
  *   >= num_valid_ids[0] become zero with scale zero.  rows = blocks * tile_m,
  *   row_bytes a multiple of 16. */
 int flyb200_moe_gather_rows(void* dst, float* dst_scale, const void* src, const float* src_scale, const int* sorted_ids,

@@ -54,7 +54,7 @@ def moe_gemm1(x_q, w1_q_flat, scale_x, scale_w1_flat, topk_ids, topk_weights, in
     tokens, topk = topk_ids.shape
     model_dim = x_q.shape[-1]
     experts = w1_q_flat.shape[0] // (2 * inter_dim)
-    x = _dequant(x_q, scale_x)
+    x = _dequant(x_q, scale_x)  # [tokens, K], or [tokens, topk, K] with one activation row per route
     w1 = _dequant(w1_q_flat, scale_w1_flat).view(experts, 2 * inter_dim, model_dim)
     out = torch.zeros((tokens, topk, inter_dim), dtype=torch.float32)
     for e in range(experts):
@@ -62,7 +62,7 @@ def moe_gemm1(x_q, w1_q_flat, scale_x, scale_w1_flat, topk_ids, topk_weights, in
         if idx.numel() == 0:
             continue
         t_idx, s_idx = idx[:, 0], idx[:, 1]
-        y2 = F.linear(x[t_idx, :], w1[e])
+        y2 = F.linear(x[t_idx, :] if x.dim() == 2 else x[t_idx, s_idx, :], w1[e])
         y = F.silu(y2[:, :inter_dim]) * y2[:, inter_dim:]
         if doweight_stage1:
             y = y * topk_weights[t_idx, s_idx].unsqueeze(-1)
@@ -126,6 +126,27 @@ def pertoken_quant(x, quant_dtype):
     scale = amax / qmax
     scale = torch.where(scale == 0, torch.ones_like(scale), scale)
     return (x / scale).to(quant_dtype), scale
+
+
+def smooth_stage1_inputs(x, w1, topk_ids, generator):
+    """Per-route ("int8smooth") stage-1 activations as the reference's test builds them
+    (tests/kernels/test_moe_gemm_2stage.py:487-519): x times a per-expert smoothing vector,
+    quantised per (token, slot).  Returns the token-major tensors the torch definition takes
+    and the slot-major ones the kernel takes."""
+    tokens, model_dim = x.shape
+    topk = topk_ids.shape[1]
+    experts = w1.shape[0]
+    smooth = 0.75 + 0.5 * torch.rand((experts, model_dim), generator=generator, dtype=torch.float32)
+    x_route = x[:, None, :].expand(tokens, topk, model_dim) * smooth[topk_ids.to(torch.int64)]
+    amax = torch.amax(torch.abs(x_route), dim=-1, keepdim=True)
+    scale_x = amax / 127.0
+    scale_x[scale_x == 0] = 1.0
+    x_q = (x_route / scale_x).to(torch.int8)
+    return dict(
+        x_ref=x_q.contiguous(), sx_ref=scale_x.contiguous(),
+        x_slot_major=x_q.permute(1, 0, 2).contiguous().view(tokens * topk, model_dim),
+        sx_slot_major=scale_x.permute(1, 0, 2).contiguous().view(-1),
+    )
 
 
 def make_routing(tokens, experts, topk, generator):

@@ -15,7 +15,9 @@ of the file and executed on its own.
 
 Fixtures written (inputs seeded here, outputs from the reference):
   moe_fp8.npz / moe_int8.npz   routing table, quantised inputs of both stages,
-                               stage-1 and stage-2 reference outputs
+                               stage-1 and stage-2 reference outputs; the int8 file
+                               also holds per-route ("int8smooth") stage-1 activations
+                               and their reference output
 """
 
 import ast
@@ -118,6 +120,19 @@ def main(ref_root):
             a2_q.as_subclass(OnGpuLookalike), w2_q.as_subclass(OnGpuLookalike), scale_a2, scale_w2,
             topk_ids.to(torch.int64), topk_weights, model_dim=model_dim, doweight_stage2=False,
         )
+        extra = {}
+        if name == "int8":
+            # per-route activations (token-major [tokens, topk, K]) as in the reference's int8smooth test
+            smooth = 0.75 + 0.5 * torch.rand((experts, model_dim), generator=g, dtype=torch.float32)
+            x_route = x[:, None, :].expand(tokens, topk, model_dim) * smooth[topk_ids.to(torch.int64)]
+            sx_r = torch.amax(torch.abs(x_route), dim=-1, keepdim=True) / 127.0
+            sx_r[sx_r == 0] = 1.0
+            xq_r = (x_route / sx_r).to(torch.int8)
+            out1_r = ref.torch_moe_gemm1(
+                xq_r, w1_q.view(experts * 2 * inter_dim, model_dim), sx_r, scale_w1.view(-1, 1), topk_ids.to(torch.int64),
+                topk_weights, inter_dim=inter_dim, doweight_stage1=False,
+            )
+            extra = dict(x_route_q=u8(xq_r), scale_x_route=sx_r.numpy(), out1_route=out1_r.numpy())
         np.savez_compressed(
             os.path.join(HERE, f"moe_{name}.npz"),
             dims=np.array([tokens, model_dim, inter_dim, experts, topk, block], dtype=np.int64),
@@ -128,6 +143,7 @@ def main(ref_root):
             w2_q=u8(w2_q), scale_w2=scale_w2.numpy(), a2_q=u8(a2_q), scale_a2=scale_a2.numpy(),
             out1=out1.numpy(), out1_weighted=out1_w.numpy(),
             out2=out2.as_subclass(torch.Tensor).numpy(), out2_unweighted=out2_nw.as_subclass(torch.Tensor).numpy(),
+            **extra,
         )
         print(name, "written: out1", tuple(out1.shape), "out2", tuple(out2.shape), "rows in use", n_valid)
 

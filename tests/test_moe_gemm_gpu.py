@@ -460,3 +460,35 @@ def test_whole_layer_in_one_graph(dev):
     assert torch.equal(y, eager)
     close_enough(y, ref_stage2(d, model_dim), "whole layer", rel=5e-2)
     assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("tile_m,tokens", [(16, 8), (64, 128), (128, 300)])
+def test_int8smooth_stage1(dev, tile_m, tokens):
+    """in_dtype="int8smooth": x and scale_x are slot-major [topk * tokens, ...] with one quantised row
+    per route (tests/kernels/test_moe_gemm_2stage.py:487-583 of the reference)."""
+    g = torch.Generator().manual_seed(60 + tokens)
+    ids, wts = moe_oracle.make_routing(tokens, SHAPE["experts"], SHAPE["topk"], g)
+    x = torch.randn(tokens, SHAPE["model_dim"], generator=g)
+    w1 = torch.randn(SHAPE["experts"], 2 * SHAPE["inter_dim"], SHAPE["model_dim"], generator=g) / 16
+    w1_q, sw1 = moe_oracle.pertoken_quant(w1, torch.int8)
+    sm = moe_oracle.smooth_stage1_inputs(x, w1, ids, g)
+    ref = moe_oracle.moe_gemm1(sm["x_ref"], w1_q.view(-1, SHAPE["model_dim"]), sm["sx_ref"], sw1.view(-1, 1), ids.long(), wts,
+                               SHAPE["inter_dim"], False)
+    d = dict(topk_ids=ids, topk_weights=wts, x_q=sm["x_slot_major"], scale_x=sm["sx_slot_major"], w1_q=w1_q, scale_w1=sw1)
+    tokens_topk = tokens * SHAPE["topk"]
+    srt, w, e_ids, post = moe_sorting(ids.to(dev), wts.to(dev), num_experts=SHAPE["experts"], block_size=tile_m)
+    out = torch.full((tokens_topk + 8, SHAPE["inter_dim"]), 7.0, dtype=torch.bfloat16, device=dev)
+    exe = compile_moe_gemm1(**SHAPE, tile_m=tile_m, tile_n=64, tile_k=128, doweight_stage1=False, out_dtype="bf16",
+                            in_dtype="int8smooth")
+    exe(out, d["x_q"].to(dev).view(-1), shuffle_weight(w1_q.to(dev)).view(-1), d["scale_x"].to(dev), sw1.to(dev).view(-1),
+        srt, e_ids, w, post[:1].contiguous(), tokens, SHAPE["inter_dim"], SHAPE["model_dim"], int(e_ids.numel()), None)
+    torch.cuda.synchronize()
+    close_enough(out[:tokens_topk].view(tokens, SHAPE["topk"], -1), ref, "int8smooth stage 1")
+    assert torch.all(out[tokens_topk:] == 7.0)
+
+
+def test_int8smooth_stage2_is_the_int8_path(dev):
+    d = moe_oracle.make_inputs(64, 256, 128, 4, 2, "int8", seed=61)
+    a = run_stage2(dev, d, **SHAPE, tile_m=32, in_dtype="int8", out_dtype="bf16", accumulate=False)
+    b = run_stage2(dev, d, **SHAPE, tile_m=32, in_dtype="int8smooth", out_dtype="bf16", accumulate=False)
+    assert torch.equal(a, b)

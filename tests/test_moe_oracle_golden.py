@@ -78,6 +78,17 @@ def test_stage2_input_is_quantised_stage1_output(name):
     assert torch.equal(scale_a2, d["scale_a2"])
 
 
+def test_stage1_per_route_activations_match_reference():
+    """The reference's torch definition with one activation row per (token, slot): the int8smooth case."""
+    d = load("int8")
+    _, model_dim, inter_dim, experts, _, _ = d["dims"]
+    got = moe_oracle.moe_gemm1(
+        d["x_route_q"].view(torch.int8), d["w1_q"].view(experts * 2 * inter_dim, model_dim), d["scale_x_route"],
+        d["scale_w1"].view(-1, 1), d["topk_ids"].long(), d["topk_weights"], inter_dim, False,
+    )
+    assert torch.equal(got, d["out1_route"])
+
+
 def test_make_inputs_is_seeded_and_consistent():
     a = moe_oracle.make_inputs(8, 128, 64, 4, 2, "fp8", seed=5)
     b = moe_oracle.make_inputs(8, 128, 64, 4, 2, "fp8", seed=5)
@@ -101,6 +112,7 @@ def test_builders_validate_like_the_reference():
     kw = dict(model_dim=256, inter_dim=128, experts=4, topk=2, tile_m=64, tile_n=64, tile_k=128)
     compile_moe_gemm1(**kw, doweight_stage1=False, out_dtype="bf16", in_dtype="fp8")
     compile_moe_gemm2(**kw, doweight_stage2=True, out_dtype="f32", accumulate=True, in_dtype="int8")
+    compile_moe_gemm1(**kw, doweight_stage1=False, out_dtype="f16", in_dtype="int8smooth")
     with pytest.raises(ValueError, match="out_dtype"):
         compile_moe_gemm1(**kw, doweight_stage1=False, out_dtype="f32")
     with pytest.raises(ValueError, match="in_dtype"):
