@@ -15,6 +15,7 @@ serves every M without recompiling, as the reference's runtime ``M`` does.
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -70,6 +71,12 @@ class PreshuffleGemm:
         self._elem_bytes = 1 if self._is_8bit else 2
         self._ws_bytes: dict = {}
 
+    def plan(self, M: int, sm_count: int = 148) -> dict:
+        """The prebuilt kernel variant a call with ``M`` rows runs on a GPU with
+        ``sm_count`` SMs (kernel, tile width, split-K, reduction, ring depth, ...):
+        a pure host function of the library, no CUDA call."""
+        return _lib.describe_plan(max(int(M), 1), self.N, self.K, self.in_dtype, self.variant_hint, sm_count)
+
     def _check_tensors(self, c, a, b, sa, sb, bias, M):
         N, K = self.N, self.K
         for name, t in (("c", c), ("a", a), ("b", b)):
@@ -102,6 +109,13 @@ class PreshuffleGemm:
             raise ValueError(f"N passed at call time ({n_rt}) differs from the N the launcher was built for ({self.N})")
         if M < 0:
             raise ValueError("M must be non-negative")
+        if os.environ.get("COMPILE_ONLY") == "1":
+            # The reference pre-compiles a configuration by calling the launcher with CPU
+            # placeholders under COMPILE_ONLY=1 (tests/python/examples/aot_example.py:38-64).
+            # Every kernel variant here is built ahead of time into the library, so this
+            # resolves the variant the call would run and launches nothing.
+            self.last_plan = self.plan(M)
+            return None
         self._check_tensors(arg_c, arg_a, arg_b, arg_scale_a, arg_scale_b, arg_bias, M)
         if M == 0:
             return None
