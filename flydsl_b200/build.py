@@ -15,8 +15,8 @@ import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libflyb200.so")
-SOURCES = ["flyb200.cu", "flyb200_moe.cu"]
-HEADERS = ["ptx.cuh", "gemm_kernels.cuh", "decode_kernel.cuh", "rows2_kernel.cuh", "quant_kernel.cuh", "moe_kernel.cuh", "host_common.h", os.path.join("..", "..", "include", "flyb200.h")]
+SOURCES = ["flyb200.cu", "flyb200_moe.cu", "flyb200_mx.cu"]
+HEADERS = ["ptx.cuh", "gemm_kernels.cuh", "decode_kernel.cuh", "rows2_kernel.cuh", "quant_kernel.cuh", "moe_kernel.cuh", "mx_kernel.cuh", "host_common.h", os.path.join("..", "..", "include", "flyb200.h")]
 
 NVCC_FLAGS = [
     "-gencode",

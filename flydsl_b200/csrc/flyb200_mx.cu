@@ -1,0 +1,92 @@
+// libflyb200: host side of the MXFP8 (block-scaled) entry points of
+// include/flyb200.h — argument checks, tensor map, launch.
+#include "../../include/flyb200.h"
+#include "host_common.h"
+#include "mx_kernel.cuh"
+
+#include <atomic>
+#include <cstring>
+
+using namespace flyb200;
+
+namespace {
+
+#define CUDA_TRY(expr)                                                  \
+  do {                                                                  \
+    cudaError_t _e = (expr);                                            \
+    if (_e != cudaSuccess) return host::record_cuda_error(_e, #expr);   \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int OUTMODE>
+int launch_mx(const CUtensorMap& tmA, const MxParams& p, cudaStream_t s) {
+  static std::atomic<uint64_t> done{0};
+  auto kernel = mx_gemm_kernel<OUTMODE>;
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  const uint64_t bit = 1ull << dev;
+  if (!(done.load(std::memory_order_acquire) & bit)) {
+    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem::TOTAL));
+    done.fetch_or(bit, std::memory_order_release);
+  }
+  int sms = 0;
+  CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const long long tiles = static_cast<long long>((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * (p.N / MX_BN);
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  kernel<<<grid, NUM_THREADS, MxSmem::TOTAL, s>>>(tmA, p);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t flyb200_mx_scale_image_bytes(int rows, int K) {
+  if (rows <= 0 || K <= 0 || K % KBLOCK_BYTES != 0) return 0;
+  return static_cast<size_t>(K / KBLOCK_BYTES) * ((rows + 127) / 128) * MX_SF_ATOM;
+}
+
+int flyb200_mx_scale_image(void* dst, const void* src, int rows, int K, void* stream) {
+  if (!dst || !src || rows <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (K % KBLOCK_BYTES != 0) return FLYB200_E_UNSUPPORTED;
+  const int row_tiles = (rows + 127) / 128;
+  const long long total = static_cast<long long>(flyb200_mx_scale_image_bytes(rows, K));
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  mx_scale_image_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), rows, K / 32, row_tiles);
+  CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
+                       int M, int N, int K, int out_dtype, void* stream) {
+  if (!c || !a || !w_shuf || !scale_a_image || !scale_w_image || M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (out_dtype != FLYB200_OUT_BF16 && out_dtype != FLYB200_OUT_FP16) return FLYB200_E_BAD_ARG;
+  if (K % KBLOCK_BYTES != 0 || N % MX_BN != 0) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(c) || !aligned16(a) || !aligned16(w_shuf) || !aligned16(scale_a_image) || !aligned16(scale_w_image))
+    return FLYB200_E_BAD_ALIGN;
+  if (M == 0) return FLYB200_OK;
+  MxParams p;
+  memset(&p, 0, sizeof(p));
+  p.w = static_cast<const uint8_t*>(w_shuf);
+  p.sfa = static_cast<const uint8_t*>(scale_a_image);
+  p.sfw = static_cast<const uint8_t*>(scale_w_image);
+  p.c = c;
+  p.M = M;
+  p.N = N;
+  p.K_bytes = K;
+  p.group_m = 16;
+  int rc = host::status_word(&p.status);
+  if (rc) return rc;
+  CUtensorMap tmA;
+  rc = host::byte_matrix_map(&tmA, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M), BLOCK_ROWS);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == FLYB200_OUT_BF16) return launch_mx<MOE_OUT_BF16>(tmA, p, s);
+  return launch_mx<MOE_OUT_FP16>(tmA, p, s);
+}
+
+}  // extern "C"

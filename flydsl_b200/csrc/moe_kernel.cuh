@@ -731,7 +731,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) moe_rows_kernel(const __grid_c
 // reference's "int8smooth" stage 1); rows that are padding, or past num_valid,
 // become zero with scale zero.
 // One warp per row, 16 bytes per lane and step.
-__global__ void moe_gather_rows_kernel(uint8_t* __restrict__ dst, float* __restrict__ dst_scale,
+static __global__ void moe_gather_rows_kernel(uint8_t* __restrict__ dst, float* __restrict__ dst_scale,
                                        const uint8_t* __restrict__ src, const float* __restrict__ src_scale,
                                        const int* __restrict__ sorted_ids, const int* __restrict__ num_valid, int tokens,
                                        int topk, int by_slot, int K_bytes, int rows) {
@@ -769,7 +769,7 @@ __global__ void moe_gather_rows_kernel(uint8_t* __restrict__ dst, float* __restr
 // ---------------------------------------------------------------------------
 // Pass 1: fill the outputs with their padding values and count the pairs of every expert
 // (`counts` must be zero on entry).
-__global__ void moe_sort_count_kernel(const int* __restrict__ topk_ids, int n_pairs, int experts, int* __restrict__ counts,
+static __global__ void moe_sort_count_kernel(const int* __restrict__ topk_ids, int n_pairs, int experts, int* __restrict__ counts,
                                       int* __restrict__ sorted_ids, float* __restrict__ sorted_weights, int max_padded,
                                       int* __restrict__ sorted_expert_ids, int max_blocks, int sentinel) {
   const int stride = gridDim.x * blockDim.x;
@@ -787,7 +787,7 @@ __global__ void moe_sort_count_kernel(const int* __restrict__ topk_ids, int n_pa
 
 // Pass 2: one CTA per expert walks the pairs in order and writes its run.
 constexpr int MOE_SORT_THREADS = 256;
-__global__ void __launch_bounds__(MOE_SORT_THREADS)
+static __global__ void __launch_bounds__(MOE_SORT_THREADS)
 moe_sort_place_kernel(const int* __restrict__ topk_ids, const float* __restrict__ topk_weights, int n_pairs, int topk,
                       int tokens, int experts, int block_size, const int* __restrict__ counts,
                       int* __restrict__ sorted_ids, float* __restrict__ sorted_weights,

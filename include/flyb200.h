@@ -288,6 +288,28 @@ int flyb200_moe_sorting(const int* topk_ids, const float* topk_weights, int toke
  * dtype FLYB200_OUT_BF16 or FLYB200_OUT_FP16, dim even. */
 int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, void* stream);
 
+/* ---- MXFP8: E4M3 codes with one E8M0 scale per 32 elements of K on both operands ----
+ * Replaces the MXFP8 x MXFP8 configuration of the reference's block-scaled
+ * preshuffle GEMM (kernels/gemm/mxfp4_preshuffle.py launch_gemm with a_dtype =
+ * b_dtype = "fp8"; call convention and data recipe pinned by
+ * tests/kernels/test_preshuffle_gemm.py:602-700 test_mfma_a8w8_preshuffle):
+ *   c[M, N] = sum_k a[m,k] * 2^(sa[m, k/32] - 127) * w[n,k] * 2^(sw[n, k/32] - 127)
+ * computed with tcgen05.mma kind::mxf8f6f4.block_scale, scale factors in TMEM.
+ *   a              [M, K] E4M3 codes, row-major
+ *   w_shuf         [N, K] E4M3 codes in the image of flyb200_shuffle_weight
+ *   scale_a_image, scale_w_image   the operands' E8M0 scales [rows, K/32] rearranged by
+ *                  flyb200_mx_scale_image (the counterpart of the reference's
+ *                  shuffle_scale_w4, tests/kernels/utils/gemm_common_utils.py:645-672):
+ *                  [K/128][ceil(rows/128)][512 bytes], byte (r % 32) * 16 + (r / 32) * 4 + j of
+ *                  an atom = scale of row r of the 128-row tile for the j-th 32-element
+ *                  block of the 128-element k-block; rows past the end are zero
+ *   out_dtype      FLYB200_OUT_BF16 or FLYB200_OUT_FP16
+ * Requirements: K % 128 == 0, N % 128 == 0, pointers 16-byte aligned. */
+int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
+                       int M, int N, int K, int out_dtype, void* stream);
+int flyb200_mx_scale_image(void* dst, const void* src, int rows, int K, void* stream);
+size_t flyb200_mx_scale_image_bytes(int rows, int K);
+
 const char* flyb200_strerror(int code);
 const char* flyb200_last_cuda_error(void);
 int flyb200_version(void);

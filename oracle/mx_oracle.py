@@ -1,0 +1,82 @@
+"""TEST INFRASTRUCTURE — CPU restatement of the reference's MXFP8 (per-1x32 E8M0
+block-scaled E4M3) quantiser and of its dequantise-and-matmul check.  Only
+tests, the smoke check and the benchmark's CPU-baseline leg may import this
+module; the product never does.
+
+Parity status: PINNED.  ``tests/golden/mx_fp8.npz`` was produced by the
+reference's own ``per_1x32_f8_quant`` / ``e8m0_to_f32``
+(tests/kernels/utils/gemm_common_utils.py:53-72, 773-790) and the reference
+formula of tests/kernels/test_preshuffle_gemm.py:651-654, run on CPU by
+``tests/golden/make_golden_mx.py``; ``tests/test_mx_oracle_golden.py`` checks
+the functions below against it bit for bit.
+"""
+
+from __future__ import annotations
+
+import torch
+
+BLOCK = 32  # elements that share one scale
+
+
+def f32_to_e8m0(x):
+    """Biased power-of-two exponent of x, rounded up when the mantissa is >= 1.5
+    (tests/kernels/utils/gemm_common_utils.py:53-60)."""
+    u32 = x.contiguous().view(torch.int32)
+    exponent = ((u32 >> 23) & 0xFF).to(torch.int32)
+    nan_case = exponent == 0xFF
+    round_case = ((u32 & 0x400000) > 0) & (((u32 & 0x200000) > 0) | ((u32 & 0x1FFFFF) > 0) | (exponent > 0))
+    exponent = torch.where(round_case, exponent + 1, exponent)
+    exponent = torch.where(nan_case, torch.full_like(exponent, 0xFF), exponent)
+    return (exponent & 0xFF).to(torch.uint8)
+
+
+def e8m0_to_f32(scale):
+    """2 ** (byte - 127); byte 0 is 2 ** -127, byte 255 NaN (gemm_common_utils.py:63-71)."""
+    b = scale.view(torch.uint8).to(torch.int32)
+    bits = b << 23
+    bits = torch.where(b == 0, torch.full_like(bits, 0x00400000), bits)
+    bits = torch.where(b == 0xFF, torch.full_like(bits, 0x7F800001), bits)
+    return bits.view(torch.float32)
+
+
+def per_1x32_f8_quant(x):
+    """(codes float8_e4m3fn [..., K], scales uint8 E8M0 [..., K/32]) (gemm_common_utils.py:773-790)."""
+    fp8_max = float(torch.finfo(torch.float8_e4m3fn).max)
+    shape = x.shape
+    flat = x.contiguous().view(-1, BLOCK).float()
+    max_abs = torch.amax(torch.abs(flat), dim=-1).clamp_min(1e-30)
+    scale = f32_to_e8m0(max_abs / fp8_max)
+    scale_f32 = e8m0_to_f32(scale).clamp_min(1e-30)
+    q = (flat / scale_f32.view(-1, 1)).clamp(-fp8_max, fp8_max).to(torch.float8_e4m3fn)
+    return q.view(shape).contiguous(), scale.view(*shape[:-1], shape[-1] // BLOCK).contiguous()
+
+
+def dequant(codes, scale):
+    return codes.float() * e8m0_to_f32(scale).repeat_interleave(BLOCK, dim=-1)
+
+
+def mx_gemm(a_codes, scale_a, b_codes, scale_b):
+    """fp32 [M, N]: dequantise both operands, torch.mm (tests/kernels/test_preshuffle_gemm.py:651-654)."""
+    return torch.mm(dequant(a_codes, scale_a), dequant(b_codes, scale_b).T).to(torch.float32)
+
+
+def scale_image(scale):
+    """The scale layout the B200 kernel reads, stated with torch ops: rows padded to
+    a multiple of 128, then [K/128][rows/128][32][4][4] bytes with
+    byte ((r % 32) * 16 + (r // 32) * 4 + j) of a 512-byte atom holding the scale of
+    row r of the 128-row tile for the j-th 32-element block of the 128-element k-block."""
+    rows, kb32 = scale.shape
+    assert kb32 % 4 == 0
+    pad = (-rows) % 128
+    s = torch.cat([scale.view(torch.uint8), torch.zeros(pad, kb32, dtype=torch.uint8)]) if pad else scale.view(torch.uint8)
+    t = s.view(-1, 4, 32, kb32 // 4, 4)  # [row tile, r // 32, r % 32, k-block, j]
+    return t.permute(3, 0, 2, 1, 4).contiguous().view(-1)
+
+
+def make_inputs(m, n, k, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = torch.randn(m, k, generator=g, dtype=torch.float32)
+    b = torch.randn(n, k, generator=g, dtype=torch.float32)
+    a_q, sa = per_1x32_f8_quant(a)
+    b_q, sb = per_1x32_f8_quant(b)
+    return a_q, sa, b_q, sb

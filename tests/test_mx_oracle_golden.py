@@ -1,0 +1,44 @@
+"""The MXFP8 oracle against the fixture produced by the reference's own utilities. CPU only."""
+
+import os
+
+import numpy as np
+import torch
+
+from oracle import mx_oracle
+
+Z = np.load(os.path.join(os.path.dirname(__file__), "golden", "mx_fp8.npz"))
+
+
+def t(name):
+    return torch.from_numpy(Z[name])
+
+
+def test_e8m0_table():
+    got = mx_oracle.e8m0_to_f32(torch.arange(256, dtype=torch.uint8)).view(torch.int32)
+    assert torch.equal(got, t("e8m0_table"))
+
+
+def test_quantiser_matches_reference():
+    for x, q, s in (("a", "a_q", "sa"), ("b", "b_q", "sb")):
+        codes, scale = mx_oracle.per_1x32_f8_quant(t(x))
+        assert torch.equal(codes.view(torch.uint8), t(q))
+        assert torch.equal(scale, t(s))
+
+
+def test_gemm_reference_matches():
+    c = mx_oracle.mx_gemm(t("a_q").view(torch.float8_e4m3fn), t("sa"), t("b_q").view(torch.float8_e4m3fn), t("sb"))
+    assert torch.equal(c, t("c"))
+
+
+def test_scale_image_layout():
+    rows, kb32 = 130, 8  # two row tiles (the second mostly padding), two 128-element k-blocks
+    s = torch.arange(rows * kb32, dtype=torch.int32).remainder(251).to(torch.uint8).view(rows, kb32)
+    img = mx_oracle.scale_image(s)
+    assert img.numel() == 2 * 2 * 512
+    for r, kb in ((0, 0), (31, 3), (32, 4), (77, 5), (129, 7), (128, 0)):
+        tile, rr = divmod(r, 128)
+        k_block, j = divmod(kb, 4)
+        off = (k_block * 2 + tile) * 512 + (rr % 32) * 16 + (rr // 32) * 4 + j
+        assert int(img[off]) == int(s[r, kb])
+    assert int(img[(0 * 2 + 1) * 512 + (5 % 32) * 16 + 0 + 0]) == 0  # padding row 128 + 5
