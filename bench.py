@@ -269,6 +269,37 @@ def time_config(m, n, k, in_dtype, dev, iters=40, hint=0):
     return us, copies
 
 
+def time_mx(m, n, k, dev, iters=10):
+    """Device time of the MXFP8 block-scaled GEMM (operands larger than L2, back-to-back launches);
+    algorithmic bytes as in the reference's test (tests/kernels/test_preshuffle_gemm.py:695)."""
+    from flydsl_b200 import shuffle_weight
+    from flydsl_b200.kernels.gemm.mxfp8_preshuffle import compile_mxfp8_preshuffle_gemm, shuffle_scale
+
+    g = torch.Generator(device=dev).manual_seed(78)
+    a = (torch.randn(m, k, generator=g, device=dev) * 64).clamp_(-448, 448).to(FP8)
+    w = shuffle_weight((torch.randn(n, k, generator=g, device=dev) * 64).clamp_(-448, 448).to(FP8))
+    sa = shuffle_scale(torch.randint(120, 130, (m, k // 32), generator=g, dtype=torch.uint8, device=dev))
+    sw = shuffle_scale(torch.randint(120, 130, (n, k // 32), generator=g, dtype=torch.uint8, device=dev))
+    c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    fn = compile_mxfp8_preshuffle_gemm(N=n, K=k)
+    st = torch.cuda.Stream()
+    args = (c.view(-1), a.view(torch.uint8).view(-1), w.view(torch.uint8).view(-1), sa, sw, None, m, n, st)
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            fn(*args)
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(iters):
+            fn(*args)
+        e1.record(st)
+        st.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    byts = m * k + n * k + 2 * m * n + (m + n) * (k // 32)
+    return {"us": round(us, 2), "tflops": round(2.0 * m * n * k / us / 1e6, 1), "hbm_gbs": round(byts / us / 1e3, 1),
+            "frac_of_nominal_fp8": round(2.0 * m * n * k / us / 1e6 / NOMINAL_FP8_TFLOPS, 3), "algorithmic_bytes": int(byts)}
+
+
 def time_moe(tokens, model_dim, inter_dim, experts, topk, tile_m, dev, iters=20):
     """Device time of the two mixture-of-experts GEMM stages (activation gather
     included) on seeded synthetic routing, with the algorithmic bytes of the
@@ -546,6 +577,8 @@ def main():
                 "frac_of_nominal_fp8": round(2.0 * em * en * ek / us / 1e6 / NOMINAL_FP8_TFLOPS, 3),
                 "rotating_copies": copies,
             }
+        # the MXFP8 block-scaled GEMM on the prefill shape of configuration 3 (halved N to bound the run)
+        extras["mxfp8_8192x14336x8192"] = time_mx(8192, 14336, 8192, dev)
         # the grouped (mixture-of-experts) stages: a decode-sized and a prefill-sized batch
         for name, mt, mtile in (("moe_fp8_decode_32tok", 32, 16), ("moe_fp8_prefill_4096tok", 4096, 128)):
             r = time_moe(mt, 4096, 2048, 8, 2, mtile, dev)
