@@ -5,6 +5,7 @@
 #include "mx_kernel.cuh"
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 
 using namespace flyb200;
@@ -19,22 +20,22 @@ namespace {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <int OUTMODE>
+template <int OUTMODE, int BN>
 int launch_mx(const CUtensorMap& tmA, const MxParams& p, cudaStream_t s) {
   static std::atomic<uint64_t> done{0};
-  auto kernel = mx_gemm_kernel<OUTMODE>;
+  auto kernel = mx_gemm_kernel<OUTMODE, BN>;
   int dev = 0;
   CUDA_TRY(cudaGetDevice(&dev));
   const uint64_t bit = 1ull << dev;
   if (!(done.load(std::memory_order_acquire) & bit)) {
-    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem::TOTAL));
+    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<BN>::TOTAL));
     done.fetch_or(bit, std::memory_order_release);
   }
   int sms = 0;
   CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const long long tiles = static_cast<long long>((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * (p.N / MX_BN);
+  const long long tiles = static_cast<long long>((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * (p.N / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, NUM_THREADS, MxSmem::TOTAL, s>>>(tmA, p);
+  kernel<<<grid, NUM_THREADS, MxSmem<BN>::TOTAL, s>>>(tmA, p);
   CUDA_TRY(cudaGetLastError());
   return FLYB200_OK;
 }
@@ -65,7 +66,7 @@ int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* s
                        int M, int N, int K, int out_dtype, void* stream) {
   if (!c || !a || !w_shuf || !scale_a_image || !scale_w_image || M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
   if (out_dtype != FLYB200_OUT_BF16 && out_dtype != FLYB200_OUT_FP16) return FLYB200_E_BAD_ARG;
-  if (K % KBLOCK_BYTES != 0 || N % MX_BN != 0) return FLYB200_E_UNSUPPORTED;
+  if (K % KBLOCK_BYTES != 0 || N % 128 != 0) return FLYB200_E_UNSUPPORTED;
   if (!aligned16(c) || !aligned16(a) || !aligned16(w_shuf) || !aligned16(scale_a_image) || !aligned16(scale_w_image))
     return FLYB200_E_BAD_ALIGN;
   if (M == 0) return FLYB200_OK;
@@ -85,8 +86,21 @@ int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* s
   rc = host::byte_matrix_map(&tmA, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M), BLOCK_ROWS);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (out_dtype == FLYB200_OUT_BF16) return launch_mx<MOE_OUT_BF16>(tmA, p, s);
-  return launch_mx<MOE_OUT_FP16>(tmA, p, s);
+  // 256-channel tiles (one accumulator, exposed epilogue) win as soon as a tile's
+  // mainloop is a few times longer than its epilogue: measured 2.44-2.47 against
+  // 1.82-1.88 PFLOP/s at K = 8192, M >= 4096, and level at M = 128.  FLYB200_MX_BN
+  // forces a shape (tuning and tests).
+  bool wide = N % 256 == 0 && K >= 2048;
+  if (const char* e = getenv("FLYB200_MX_BN")) {
+    if (e[0] == '1') wide = false;
+    if (e[0] == '2' && N % 256 == 0) wide = true;
+  }
+  if (wide) {
+    if (out_dtype == FLYB200_OUT_BF16) return launch_mx<MOE_OUT_BF16, 256>(tmA, p, s);
+    return launch_mx<MOE_OUT_FP16, 256>(tmA, p, s);
+  }
+  if (out_dtype == FLYB200_OUT_BF16) return launch_mx<MOE_OUT_BF16, 128>(tmA, p, s);
+  return launch_mx<MOE_OUT_FP16, 128>(tmA, p, s);
 }
 
 }  // extern "C"

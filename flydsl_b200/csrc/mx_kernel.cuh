@@ -17,11 +17,15 @@
 // the instruction expects; j is selected per instruction by the scale-factor id
 // fields of the instruction descriptor.
 //
-// Kernel: persistent, tokens on the UMMA M side (128 per tile), 128 output
-// channels on the N side, 6-stage ring of {A tile, W tile, scale atom of A, scale
-// atom of W}, two TMEM accumulators (epilogue of tile i overlaps the mainloop of
-// tile i + 1), a rotating set of TMEM columns for the scale atoms of the stages
-// in flight.  Threads as in the large-M kernel: warp 0 producer, warp 1 MMA
+// Kernel: persistent, tokens on the UMMA M side (128 per tile), BN output
+// channels on the N side, a ring of {A tile, W tile, scale atom of A, scale
+// atoms of W}, a rotating set of TMEM columns for the scale atoms of the stages
+// in flight.  Two shapes: BN = 128 with two TMEM accumulators (the epilogue of
+// tile i overlaps the mainloop of tile i + 1; 6 stages), and BN = 256 with one
+// accumulator (the wider MMA needs fewer operand bytes per flop, but 2 x 256
+// accumulator columns plus scale columns exceed the 512 columns of TMEM, so the
+// epilogue is exposed; 4 stages) for long K, where the epilogue is a small part
+// of a tile.  Threads as in the large-M kernel: warp 0 producer, warp 1 MMA
 // (copies the two scale atoms to TMEM, then issues the four MMAs of a k-block),
 // warps 2..5 epilogue (thread = token row, 64 contiguous output bytes per chunk).
 #pragma once
@@ -29,8 +33,6 @@
 
 namespace flyb200 {
 
-constexpr int MX_BN = 128;
-constexpr int MX_STAGES = 6;
 constexpr int MX_SF_ATOM = 512;  // bytes of scales per 128 rows x 128 elements of K
 
 struct MxParams {
@@ -43,15 +45,20 @@ struct MxParams {
   int* status;
 };
 
+template <int BN>
 struct MxSmem {
+  static constexpr int STAGES = BN == 128 ? 6 : 4;
+  static constexpr int NACC = BN == 128 ? 2 : 1;          // TMEM accumulators
+  static constexpr int SFB_ATOMS = BN / 128;
   static constexpr int A_STAGE = BLOCK_ROWS * KBLOCK_BYTES;
-  static constexpr int B_STAGE = MX_BN * KBLOCK_BYTES;
+  static constexpr int B_STAGE = BN * KBLOCK_BYTES;
+  static constexpr int SFB_STAGE = SFB_ATOMS * MX_SF_ATOM;
   static constexpr int OFF_A = 0;
-  static constexpr int OFF_B = OFF_A + MX_STAGES * A_STAGE;
-  static constexpr int OFF_SFA = OFF_B + MX_STAGES * B_STAGE;
-  static constexpr int OFF_SFB = OFF_SFA + MX_STAGES * MX_SF_ATOM;
-  static constexpr int OFF_BAR = OFF_SFB + MX_STAGES * MX_SF_ATOM;  // full[S], empty[S], tfull[2], tempty[2]
-  static constexpr int OFF_MISC = OFF_BAR + 8 * (2 * MX_STAGES + 4);
+  static constexpr int OFF_B = OFF_A + STAGES * A_STAGE;
+  static constexpr int OFF_SFA = OFF_B + STAGES * B_STAGE;
+  static constexpr int OFF_SFB = OFF_SFA + STAGES * MX_SF_ATOM;
+  static constexpr int OFF_BAR = OFF_SFB + STAGES * SFB_STAGE;  // full[S], empty[S], tfull[2], tempty[2]
+  static constexpr int OFF_MISC = OFF_BAR + 8 * (2 * STAGES + 4);
   static constexpr int TOTAL = OFF_MISC + 16;
 };
 
@@ -89,11 +96,12 @@ __device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t adesc, uint6
       : "memory");
 }
 
-template <int OUTMODE>
+template <int OUTMODE, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const MxParams p) {
-  using L = MxSmem;
-  constexpr int STAGES = MX_STAGES;
-  constexpr int BN = MX_BN;
+  using L = MxSmem<BN>;
+  constexpr int STAGES = L::STAGES;
+  constexpr int NACC = L::NACC;
+  constexpr int SF_COLS = 4 + 4 * L::SFB_ATOMS;  // TMEM columns of the scale atoms of one stage
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = smem_u32(smem_raw);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L::OFF_MISC + 4);
@@ -123,10 +131,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
     fence_mbar_init();
     prefetch_tensormap(&tmA);
   }
-  // TMEM: columns [0, 256) two accumulators, [256, 256 + 8 * STAGES) the scale atoms
-  // of the stages in flight (4 columns for A, 4 for W per stage)
+  // TMEM: columns [0, 256) the accumulator(s), then per stage in flight the scale
+  // atoms (4 columns for A, 4 per 128 channels for W)
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t SF_COL0 = 2 * BN;
+  constexpr uint32_t SF_COL0 = NACC * BN;
+  static_assert(SF_COL0 + STAGES * SF_COLS <= TMEM_COLS, "accumulators and scale columns must fit TMEM");
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
@@ -168,14 +177,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
             break;
           }
           const uint32_t fb = bar_full + 8 * stage;
-          mbar_expect_tx(fb, L::A_STAGE + L::B_STAGE + 2 * MX_SF_ATOM);
+          mbar_expect_tx(fb, L::A_STAGE + L::B_STAGE + MX_SF_ATOM + L::SFB_STAGE);
           tma_load_2d(smem_base + L::OFF_A + stage * L::A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, m_blk * BLOCK_ROWS, pol);
           bulk_load_1d(smem_base + L::OFF_B + stage * L::B_STAGE,
                        p.w + (static_cast<size_t>(kb) * p.N + n_blk * BN) * KBLOCK_BYTES, L::B_STAGE, fb, pol);
           bulk_load_1d(smem_base + L::OFF_SFA + stage * MX_SF_ATOM,
                        p.sfa + (static_cast<size_t>(kb) * num_m + m_blk) * MX_SF_ATOM, MX_SF_ATOM, fb, pol);
-          bulk_load_1d(smem_base + L::OFF_SFB + stage * MX_SF_ATOM,
-                       p.sfw + (static_cast<size_t>(kb) * num_n + n_blk) * MX_SF_ATOM, MX_SF_ATOM, fb, pol);
+          bulk_load_1d(smem_base + L::OFF_SFB + stage * L::SFB_STAGE,
+                       p.sfw + (static_cast<size_t>(kb) * (p.N / 128) + n_blk * L::SFB_ATOMS) * MX_SF_ATOM, L::SFB_STAGE,
+                       fb, pol);
           ++issued;
           if (++stage == STAGES) {
             stage = 0;
@@ -220,10 +230,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
           }
           tc_fence_after();
           // scale atoms of this stage: shared memory -> their TMEM columns
-          const uint32_t sfa_t = tmem_base + SF_COL0 + static_cast<uint32_t>(stage * 8);
+          const uint32_t sfa_t = tmem_base + SF_COL0 + static_cast<uint32_t>(stage * SF_COLS);
           const uint32_t sfb_t = sfa_t + 4;
           tmem_cp_sf(sfa_t, sf_smem_desc(smem_base + L::OFF_SFA + stage * MX_SF_ATOM));
-          tmem_cp_sf(sfb_t, sf_smem_desc(smem_base + L::OFF_SFB + stage * MX_SF_ATOM));
+#pragma unroll
+          for (int at = 0; at < L::SFB_ATOMS; ++at)
+            tmem_cp_sf(sfb_t + 4 * at, sf_smem_desc(smem_base + L::OFF_SFB + stage * L::SFB_STAGE + at * MX_SF_ATOM));
           const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L::OFF_A + stage * L::A_STAGE);
           const uint64_t bdesc = umma_desc_sw128_kmajor(smem_base + L::OFF_B + stage * L::B_STAGE);
 #pragma unroll
@@ -241,7 +253,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
         }
         if (!ok) break;
         umma_commit(bar_tfull + 8 * acc);
-        acc ^= 1;
+        acc = (acc + 1) % NACC;
         if (acc == 0) acc_phase ^= 1u;
       }
     }
@@ -278,7 +290,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
         if (row < p.M)
           moe_store_row32<OUTMODE, false>(p.c, static_cast<size_t>(row) * p.N + n_blk * BN + c0, y, 32);
       }
-      acc ^= 1;
+      acc = (acc + 1) % NACC;
       if (acc == 0) acc_phase ^= 1u;
     }
   }

@@ -91,3 +91,13 @@ def test_device_quantiser_matches_oracle(dev):
     q, s = per_1x32_f8_quant(x.to(dev))
     q0, s0 = mx_oracle.per_1x32_f8_quant(x)
     assert torch.equal(q.cpu().view(torch.uint8), q0.view(torch.uint8)) and torch.equal(s.cpu(), s0)
+
+
+@pytest.mark.parametrize("shape", ["1", "2"], ids=["tiles128x128", "tiles128x256"])
+@pytest.mark.parametrize("m,n,k", [(300, 512, 1024), (130, 256, 256), (2048, 2048, 4096)])
+def test_both_tile_shapes(dev, monkeypatch, shape, m, n, k):
+    """FLYB200_MX_BN forces the 128-channel (two accumulators) or the 256-channel (one accumulator) kernel."""
+    monkeypatch.setenv("FLYB200_MX_BN", shape)
+    a_q, sa, b_q, sb = mx_oracle.make_inputs(m, n, k, seed=m + k)
+    c = run(dev, a_q, sa, b_q, sb)
+    check(c, mx_oracle.mx_gemm(a_q, sa, b_q, sb))
