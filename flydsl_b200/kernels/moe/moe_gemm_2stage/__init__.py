@@ -88,13 +88,15 @@ def moe_sorting(
             )
         return sorted_ids, sorted_weights, sorted_expert_ids, post_pad
     flat = topk_ids.reshape(-1).to(torch.int64)
+    flat = torch.where((flat >= 0) & (flat < e), flat, torch.full_like(flat, e))  # ids outside [0, e) are dropped
     order = torch.sort(flat, stable=True).indices  # by expert, then (token, slot)
-    counts = torch.bincount(flat, minlength=e)[:e]
+    counts = torch.bincount(flat, minlength=e + 1)[:e]
     padded = (counts + bs - 1) // bs * bs
     starts = torch.cumsum(padded, 0) - padded
     first = torch.cumsum(counts, 0) - counts
+    order = order[: int(counts.sum())]
     expert_of = flat[order]
-    dest = starts[expert_of] + (torch.arange(flat.numel(), device=dev) - first[expert_of])
+    dest = starts[expert_of] + (torch.arange(order.numel(), device=dev) - first[expert_of])
     sorted_ids = torch.full((max_padded,), (topk << 24) | tokens, dtype=torch.int32, device=dev)
     sorted_weights = torch.zeros((max_padded,), dtype=torch.float32, device=dev)
     tok = (order // topk).to(torch.int32)
