@@ -27,9 +27,10 @@ constexpr int MAX_CLUSTER_SPLIT = 8;
 
 // Shared-memory carve-up for a given ring depth (computed identically on host and device).
 struct DecodeLayout {
-  int off_w, off_a, off_bar, off_misc, off_sa, total;
+  int off_w, off_a, off_bar, off_misc, off_sa, off_sf, total;
 };
-__host__ __device__ inline DecodeLayout decode_layout(int bn, int stages, int w_rows = BLOCK_ROWS) {
+// `mx`: reserve per stage the scale atoms of the block-scaled kind (weights, tokens).
+__host__ __device__ inline DecodeLayout decode_layout(int bn, int stages, int w_rows = BLOCK_ROWS, bool mx = false) {
   DecodeLayout l;
   l.off_w = 0;
   l.off_a = stages * w_rows * KBLOCK_BYTES;
@@ -38,6 +39,11 @@ __host__ __device__ inline DecodeLayout decode_layout(int bn, int stages, int w_
   l.off_misc = (l.off_misc + 15) & ~15;
   l.off_sa = l.off_misc + 32;
   l.total = l.off_sa + bn * 4;
+  l.off_sf = 0;
+  if (mx) {
+    l.off_sf = (l.total + 15) & ~15;
+    l.total = l.off_sf + stages * 2 * MX_SF_ATOM;
+  }
   return l;
 }
 
@@ -164,7 +170,10 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = smem_u32(smem_raw);
   const int stages = p.stages;
-  const DecodeLayout L = decode_layout(BN, stages, WROWS);
+  constexpr bool MX = KIND == KIND_MXF8;  // block-scaled: two 512-byte scale atoms ride along with every stage
+  static_assert(!MX || (WROWS == BLOCK_ROWS && BN <= 128), "MX kind: 128-channel tiles, at most 128 tokens");
+  const DecodeLayout L = decode_layout(BN, stages, WROWS, MX);
+  constexpr uint32_t SF_BYTES = MX ? 2 * MX_SF_ATOM : 0;
   constexpr int W_STAGE = WROWS * KBLOCK_BYTES;
   constexpr int A_STAGE = BN * KBLOCK_BYTES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L.off_misc);
@@ -235,19 +244,31 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
     const uint64_t pol_a = l2_policy_evict_last();
     if (p.pdl == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < pre; ++i) {
-      mbar_expect_tx(bar_full + 8 * i, A_STAGE + w_bytes);
+      mbar_expect_tx(bar_full + 8 * i, A_STAGE + w_bytes + SF_BYTES);
       bulk_load_1d(smem_base + L.off_w + i * W_STAGE,
                    p.w + (static_cast<size_t>(kb_begin + i) * p.N + n0) * KBLOCK_BYTES, w_bytes, bar_full + 8 * i, pol_w);
+      if constexpr (MX)
+        bulk_load_1d(smem_base + L.off_sf + i * 2 * MX_SF_ATOM,
+                     p.sf_w + (static_cast<size_t>(kb_begin + i) * (p.N / BLOCK_ROWS) + blockIdx.x) * MX_SF_ATOM, MX_SF_ATOM,
+                     bar_full + 8 * i, pol_w);
     }
     if (p.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int i = 0; i < pre; ++i)
+    for (int i = 0; i < pre; ++i) {
       tma_load_2d(smem_base + L.off_a + i * A_STAGE, &tmA, bar_full + 8 * i, (kb_begin + i) * KBLOCK_BYTES, m_base, pol_a);
+      if constexpr (MX)
+        bulk_load_1d(smem_base + L.off_sf + i * 2 * MX_SF_ATOM + MX_SF_ATOM,
+                     p.sf_a + static_cast<size_t>(kb_begin + i) * p.sf_a_tiles * MX_SF_ATOM, MX_SF_ATOM, bar_full + 8 * i, pol_a);
+    }
   }
   // Two accumulators (columns [0, BN) and [BN, 2 BN)): even k-blocks are issued by
   // warp 1 into the first, odd k-blocks by warp 6 into the second, so that the
   // ~290 cycles one thread needs to issue a k-block's MMAs are spent by two
   // threads in parallel; the epilogue adds the two.
-  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  // MX kind: 8 more columns per ring stage (at most 8 stages) for the scale atoms in flight
+  constexpr int MX_MAX_STAGES = 8;
+  constexpr uint32_t SF_COL0 = 2 * BN;
+  constexpr uint32_t TMEM_NEED = 2 * BN + (MX ? 8 * MX_MAX_STAGES : 0);
+  constexpr uint32_t TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
@@ -273,10 +294,16 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
           break;
         }
         const uint32_t fb = bar_full + 8 * stage;
-        mbar_expect_tx(fb, A_STAGE + w_bytes);
+        mbar_expect_tx(fb, A_STAGE + w_bytes + SF_BYTES);
         bulk_load_1d(smem_base + L.off_w + stage * W_STAGE, p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES,
                      w_bytes, fb, pol_w);
         tma_load_2d(smem_base + L.off_a + stage * A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, m_base, pol_a);
+        if constexpr (MX) {
+          const uint32_t sf = smem_base + L.off_sf + stage * 2 * MX_SF_ATOM;
+          bulk_load_1d(sf, p.sf_w + (static_cast<size_t>(kb) * (p.N / BLOCK_ROWS) + blockIdx.x) * MX_SF_ATOM, MX_SF_ATOM, fb,
+                       pol_w);
+          bulk_load_1d(sf + MX_SF_ATOM, p.sf_a + static_cast<size_t>(kb) * p.sf_a_tiles * MX_SF_ATOM, MX_SF_ATOM, fb, pol_a);
+        }
         ++issued;
         if (++stage == stages) {
           stage = 0;
@@ -316,10 +343,26 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
         if (kb == 0) FLYB200_STAMP(1);  // first stage landed
         const uint64_t wdesc = umma_desc_sw128_kmajor(smem_base + L.off_w + stage * W_STAGE);
         const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L.off_a + stage * A_STAGE);
+        if constexpr (MX) {
+          // scale atoms of this stage -> their TMEM columns; the weights are the M-side operand here
+          const uint32_t sfw_t = tmem_base + SF_COL0 + static_cast<uint32_t>(stage * 8);
+          const uint32_t sfa_t = sfw_t + 4;
+          const uint32_t sf = smem_base + L.off_sf + stage * 2 * MX_SF_ATOM;
+          tmem_cp_sf(sfw_t, sf_smem_desc(sf));
+          tmem_cp_sf(sfa_t, sf_smem_desc(sf + MX_SF_ATOM));
+          constexpr uint32_t mx_idesc = umma_idesc_mxf8(WROWS, BN);
 #pragma unroll
-        for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
-          umma_ss<KIND>(d_tmem, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
-                        adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb >= 2 || k != 0) ? 1u : 0u);
+          for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
+            const uint32_t id = mx_idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
+            umma_mxf8(d_tmem, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                      adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), id, sfw_t, sfa_t, (kb >= 2 || k != 0) ? 1u : 0u);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
+            umma_ss<KIND>(d_tmem, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                          adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb >= 2 || k != 0) ? 1u : 0u);
+          }
         }
         umma_commit(bar_empty + 8 * stage);
       }

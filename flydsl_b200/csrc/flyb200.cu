@@ -245,8 +245,9 @@ int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
   auto kernel = gemm_decode_kernel<KIND, BN, OUTMODE, WROWS>;
   int rc = ensure_smem(kernel, SMEM_LIMIT, done);
   if (rc) return rc;
-  const DecodeLayout L = decode_layout(BN, p.stages, WROWS);
+  const DecodeLayout L = decode_layout(BN, p.stages, WROWS, KIND == KIND_MXF8);
   if (L.total > SMEM_LIMIT || BN * BLOCK_ROWS * 4 > L.off_bar) return FLYB200_E_UNSUPPORTED;
+  if (KIND == KIND_MXF8 && p.stages > 8) return FLYB200_E_UNSUPPORTED;  // scale columns in TMEM for 8 stages
   if (WROWS != BLOCK_ROWS && p.reduce_mode != REDUCE_NONE) return FLYB200_E_UNSUPPORTED;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -276,6 +277,16 @@ int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
 
 template <int KIND, int OUTMODE>
 int launch_decode_bn(int bn, int w_rows, const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
+  if constexpr (KIND == KIND_MXF8) {  // block-scaled kind: 128-channel tiles, up to 128 tokens
+    if (w_rows != BLOCK_ROWS) return FLYB200_E_UNSUPPORTED;
+    switch (bn) {
+      case 16: return launch_decode<KIND, 16, OUTMODE>(tmA, p, s);
+      case 32: return launch_decode<KIND, 32, OUTMODE>(tmA, p, s);
+      case 64: return launch_decode<KIND, 64, OUTMODE>(tmA, p, s);
+      case 128: return launch_decode<KIND, 128, OUTMODE>(tmA, p, s);
+    }
+    return FLYB200_E_UNSUPPORTED;
+  } else {
   if (w_rows == 64) {  // half-height weight tiles: built for the token counts where they pay off
     switch (bn) {
       case 16: return launch_decode<KIND, 16, OUTMODE, 64>(tmA, p, s);
@@ -292,6 +303,7 @@ int launch_decode_bn(int bn, int w_rows, const CUtensorMap& tmA, const GemmParam
     case 256: return launch_decode<KIND, 256, OUTMODE>(tmA, p, s);
   }
   return FLYB200_E_UNSUPPORTED;
+  }
 }
 
 inline int decode_bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
@@ -672,6 +684,43 @@ int static_scratch_address(void** out) {
 
 namespace flyb200 {
 namespace host {
+// MXFP8 GEMM for up to 128 tokens on the small-M (weight-streaming) kernel.
+int gemm_mx_small(void* c, const void* a, const void* w, const void* sf_a, const void* sf_w, int M, int N, int K,
+                  int outmode, void* stream) {
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc) return rc;
+  Plan plan;
+  rc = make_plan(&plan, M, N, K, 1 << 8, 0, false, st->sms);
+  if (rc) return rc;
+  if (!plan.decode || plan.token_blocks != 1 || plan.w_rows != BLOCK_ROWS || plan.bn > 128) return FLYB200_E_UNSUPPORTED;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.w = static_cast<const uint8_t*>(w);
+  p.c = c;
+  p.M = M;
+  p.N = N;
+  p.K_bytes = K;
+  p.epilogue = EPI_NONE;
+  p.group_m = plan.group_m;
+  p.split_k = plan.split_k;
+  p.kb_per_split = plan.kb_per_split;
+  p.reduce_mode = plan.reduce_mode;
+  p.stages = plan.stages > 8 ? 8 : plan.stages;
+  p.pdl = plan.pdl;
+  p.token_blocks = 1;
+  p.sf_w = static_cast<const uint8_t*>(sf_w);
+  p.sf_a = static_cast<const uint8_t*>(sf_a);
+  p.sf_a_tiles = (M + 127) / 128;
+  p.status = st->status;
+  CUtensorMap tmA;
+  rc = make_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M), KBLOCK_BYTES,
+                plan.bn);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (outmode == OUT_FP16) return launch_decode_bn<KIND_MXF8, OUT_FP16>(plan.bn, plan.w_rows, tmA, p, s);
+  return launch_decode_bn<KIND_MXF8, OUT_BF16>(plan.bn, plan.w_rows, tmA, p, s);
+}
 int byte_matrix_map(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
   return make_map(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, row_bytes, rows, KBLOCK_BYTES, box_rows);
 }

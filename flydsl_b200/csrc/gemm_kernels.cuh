@@ -50,6 +50,9 @@ struct GemmParams {
   float* ws_partials;    // decode kernel, REDUCE_WORKSPACE
   int* ws_tickets;       // decode kernel, REDUCE_WORKSPACE (zero before first use; self-resetting)
   int token_blocks;      // decode kernel: grid.z, blocks of BN tokens
+  const uint8_t* sf_w;   // decode kernel, MX kind: scale image of the weights [K/128][N/128][512]
+  const uint8_t* sf_a;   // decode kernel, MX kind: scale image of the activations [K/128][sf_a_tiles][512]
+  int sf_a_tiles;        // ceil(M / 128)
   int n_dst;             // scatter kernel: number of output buffers
   int dst_first;         // scatter kernel: buffer stored to first
   int* status;           // device status word (first failure wins)
@@ -69,6 +72,11 @@ template <>
 struct KindTraits<KIND_I8> {
   static constexpr uint32_t dfmt = 2, abfmt = 1;
   static constexpr bool is_int = true;
+};
+template <>
+struct KindTraits<KIND_MXF8> {  // E4M3 codes with E8M0 block scales: fp32 accumulators, scaled inside the MMA
+  static constexpr uint32_t dfmt = 1, abfmt = 0;
+  static constexpr bool is_int = false;
 };
 template <>
 struct KindTraits<KIND_F16> {

@@ -228,7 +228,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t dfmt, uint32_t abfmt,
   return (dfmt << 4) | (abfmt << 7) | (abfmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-enum : int { KIND_F8 = 0, KIND_I8 = 1, KIND_F16 = 2, KIND_BF16 = 3 };
+enum : int { KIND_F8 = 0, KIND_I8 = 1, KIND_F16 = 2, KIND_BF16 = 3, KIND_MXF8 = 4 };
 
 template <int KIND>
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -265,6 +265,43 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_
 
 // Arrive on an mbarrier of this CTA once all UMMAs issued so far by this
 // thread have completed (implies tcgen05.fence::before_thread_sync).
+// ---- block-scaled UMMA (MX formats) -------------------------------------------
+constexpr int MX_SF_ATOM = 512;  // bytes of E8M0 scales per 128 rows x 128 elements of K
+
+// Instruction descriptor of the block-scaled kinds: bits [4,6) scale-factor id of
+// B, [7,10) A format, [10,13) B format (E4M3 = 0), 15/16 A/B major (K-major = 0),
+// [17,23) N >> 3, 23 scale format (1 = E8M0), [24,29) M >> 4, [29,31) scale-factor
+// id of A.  D is always fp32.
+__host__ __device__ constexpr uint32_t umma_idesc_mxf8(uint32_t m, uint32_t n) {
+  return ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
+}
+
+// Shared-memory descriptor of one scale atom for tcgen05.cp: 32 rows of 16
+// bytes, no swizzle; 8-row groups are 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(128u >> 4) << 32;  // stride between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;          // descriptor version of this architecture
+  return d;
+}
+
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa_tmem,
+                                          uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }

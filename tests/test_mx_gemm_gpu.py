@@ -64,7 +64,8 @@ def test_golden_fixture(dev):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (16, 256, 512), (300, 384, 1024), (1, 128, 256), (1000, 1024, 2048),
-                                   (128, 8192, 8192)])
+                                   (128, 8192, 8192), (64, 8192, 8192), (32, 8192, 8192), (1024, 8192, 8192),  # the reference's shapes
+                                   (17, 1024, 4096), (100, 512, 8192), (129, 256, 1024)])
 @pytest.mark.parametrize("out_dtype", ["bf16", "fp16"])
 def test_mxfp8_gemm(dev, m, n, k, out_dtype):
     a_q, sa, b_q, sb = mx_oracle.make_inputs(m, n, k, seed=m + n)
@@ -101,3 +102,15 @@ def test_both_tile_shapes(dev, monkeypatch, shape, m, n, k):
     a_q, sa, b_q, sb = mx_oracle.make_inputs(m, n, k, seed=m + k)
     c = run(dev, a_q, sa, b_q, sb)
     check(c, mx_oracle.mx_gemm(a_q, sa, b_q, sb))
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 1024, 2048), (128, 512, 1024), (5, 256, 256)])
+def test_small_m_kernel_and_large_m_kernel_agree(dev, monkeypatch, m, n, k):
+    """Up to 128 tokens run the weight-streaming kernel (FLYB200_MX_SMALL=0 forces the other one)."""
+    a_q, sa, b_q, sb = mx_oracle.make_inputs(m, n, k, seed=3 * m + k)
+    small = run(dev, a_q, sa, b_q, sb)
+    monkeypatch.setenv("FLYB200_MX_SMALL", "0")
+    large = run(dev, a_q, sa, b_q, sb)
+    ref = mx_oracle.mx_gemm(a_q, sa, b_q, sb)
+    check(small, ref)
+    check(large, ref)
