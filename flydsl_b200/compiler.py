@@ -15,6 +15,9 @@ from . import _lib
 
 def compile(launch_fn, *args, **kwargs):  # noqa: A001 - name fixed by the reference API
     _lib.load()
+    specialise = getattr(launch_fn, "_compile_for", None)
+    if specialise is not None:  # the mixture-of-experts stage launchers
+        return specialise(*args)
     check = getattr(launch_fn, "_check_tensors", None)
     if check is None:
         return launch_fn  # not one of this package's launchers: nothing to specialise

@@ -126,6 +126,7 @@ class _MoeStage:
         self._out, self._torch_out = _OUT[out_dtype]
         self._k = self.model_dim if stage == 1 else self.inter_dim
         self._slot_major = stage == 1 and in_dtype == "int8smooth"
+        self._gather_mode = (2 if self._slot_major else 0) if stage == 1 else 1  # how a sorted row finds its activation row
         self._scratch: dict = {}
 
     def _sorted_buffers(self, device, rows):
@@ -142,6 +143,28 @@ class _MoeStage:
         self, out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights, num_valid_ids,
         tokens, dim0, dim1, blocks, stream=None,
     ):
+        self._check(out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights, num_valid_ids,
+                    tokens, dim0, dim1, blocks)
+        return self._launch(out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights,
+                            num_valid_ids, int(tokens), int(blocks), stream)
+
+    def _compile_for(self, *args):
+        """``flyc.compile(exe, *args)``: check the example arguments once and return a callable with the
+        same signature that goes straight to the library, as the reference's compiled function checks
+        nothing per call (python/flydsl/compiler/jit_executor.py:185-214)."""
+        if len(args) >= 13:
+            self._check(*args[:13])
+        stage = self
+
+        def compiled(out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights, num_valid_ids,
+                     tokens, dim0, dim1, blocks, stream=None):
+            return stage._launch(out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights,
+                                 num_valid_ids, int(tokens), int(blocks), stream)
+
+        return compiled
+
+    def _check(self, out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights, num_valid_ids,
+               tokens, dim0, dim1, blocks):
         n_out, k = (self.inter_dim, self.model_dim) if self.stage == 1 else (self.model_dim, self.inter_dim)
         if (int(dim0), int(dim1)) != (n_out, k):
             raise ValueError(f"launch dims ({dim0}, {dim1}) do not match the compiled ({n_out}, {k})")
@@ -172,31 +195,33 @@ class _MoeStage:
             raise ValueError("routing tensors must be int32")
         if self.doweight and (sorted_weights is None or sorted_weights.numel() < sorted_token_ids.numel()):
             raise ValueError("sorted_weights is required when the routed weight is applied in this stage")
+
+    def _launch(self, out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights, num_valid_ids,
+                tokens, blocks, stream):
         if tokens == 0 or blocks == 0:
             return None
+        dev = out.device
+        if torch.cuda.current_device() != dev.index:
+            with torch.cuda.device(dev):
+                return self._launch(out, x, w, scale_x, scale_w, sorted_token_ids, sorted_expert_ids, sorted_weights,
+                                    num_valid_ids, tokens, blocks, stream)
         lib = _lib.load()
-        s = _stream_handle(stream)
+        s = _stream_handle(stream) or None
         rows = blocks * self.tile_m
-        with torch.cuda.device(out.device):
-            a_sorted, sa_sorted = self._sorted_buffers(out.device, rows)
-            _lib.check(
-                lib.flyb200_moe_gather_rows(
-                    a_sorted.data_ptr(), sa_sorted.data_ptr(), x.data_ptr(), scale_x.data_ptr(),
-                    sorted_token_ids.data_ptr(), num_valid_ids.data_ptr(), tokens, self.topk,
-                    (2 if self._slot_major else 0) if self.stage == 1 else 1, k, rows, s,
-                ),
-                "moe_gather_rows",
-            )
-            _lib.check(
-                lib.flyb200_moe_gemm(
-                    self.stage, out.data_ptr(), a_sorted.data_ptr(), w.data_ptr(), sa_sorted.data_ptr(),
-                    scale_w.data_ptr(), sorted_token_ids.data_ptr(), sorted_expert_ids.data_ptr(),
-                    sorted_weights.data_ptr() if sorted_weights is not None and sorted_weights.numel() else None,
-                    num_valid_ids.data_ptr(), tokens, self.topk, self.experts, self.model_dim, self.inter_dim,
-                    self.tile_m, blocks, self._dt, self._out, int(self.doweight), int(self.accumulate), 1, s,
-                ),
-                "moe_gemm",
-            )
+        a_sorted, sa_sorted = self._sorted_buffers(dev, rows)
+        a_ptr, sa_ptr, ids_ptr, nv_ptr = a_sorted.data_ptr(), sa_sorted.data_ptr(), sorted_token_ids.data_ptr(), num_valid_ids.data_ptr()
+        rc = lib.flyb200_moe_gather_rows(a_ptr, sa_ptr, x.data_ptr(), scale_x.data_ptr(), ids_ptr, nv_ptr, tokens, self.topk,
+                                         self._gather_mode, self._k, rows, s)
+        if rc:
+            _lib.check(rc, "moe_gather_rows")
+        rc = lib.flyb200_moe_gemm(
+            self.stage, out.data_ptr(), a_ptr, w.data_ptr(), sa_ptr, scale_w.data_ptr(), ids_ptr, sorted_expert_ids.data_ptr(),
+            sorted_weights.data_ptr() if sorted_weights is not None and sorted_weights.numel() else None, nv_ptr,
+            tokens, self.topk, self.experts, self.model_dim, self.inter_dim, self.tile_m, blocks, self._dt, self._out,
+            int(self.doweight), int(self.accumulate), 1, s,
+        )
+        if rc:
+            _lib.check(rc, "moe_gemm")
         return None
 
 
