@@ -63,8 +63,17 @@ def local_routing(topk_ids: torch.Tensor, shard: ExpertShard) -> torch.Tensor:
 class ExpertParallelMoe:
     """One rank's part of an expert-parallel MoE layer (fp8 or int8 weights)."""
 
-    def __init__(self, *, model_dim, inter_dim, experts, topk, tile_m=64, in_dtype="fp8", rank=None, world=None, group=None):
-        from .kernels.moe.moe_gemm_2stage import compile_moe_gemm1, compile_moe_gemm2
+    def __init__(self, *, model_dim, inter_dim, experts, topk, tile_m=64, in_dtype="fp8", out_dtype="bf16", rank=None,
+                 world=None, group=None):
+        """``out_dtype`` "bf16": stage 2 writes one bf16 row per route, the rows of a token are summed
+        (fp32, one rounding) and the ranks exchange bf16.  "f32": stage 2 accumulates with fp32 atomics
+        into a zero-filled fp32 output and the ranks exchange fp32 (twice the bytes, no bf16 rounding
+        between the partial sums)."""
+        from .kernels.moe.moe_gemm_2stage import compile_moe_gemm1, compile_moe_gemm2, compile_moe_reduction
+
+        if out_dtype not in ("bf16", "f32"):
+            raise ValueError(f"out_dtype must be 'bf16' or 'f32', got {out_dtype!r}")
+        self.out_dtype = out_dtype
 
         self.group = group
         self.rank = dist.get_rank(group) if rank is None else rank
@@ -74,7 +83,11 @@ class ExpertParallelMoe:
         kw = dict(model_dim=model_dim, inter_dim=inter_dim, experts=self.shard.experts_local, topk=topk, tile_m=tile_m,
                   tile_n=128, tile_k=128, in_dtype=in_dtype)
         self._g1 = compile_moe_gemm1(**kw, doweight_stage1=False, out_dtype="bf16")
-        self._g2 = compile_moe_gemm2(**kw, doweight_stage2=True, out_dtype="f32", accumulate=True)
+        if out_dtype == "f32":
+            self._g2 = compile_moe_gemm2(**kw, doweight_stage2=True, out_dtype="f32", accumulate=True)
+        else:
+            self._g2 = compile_moe_gemm2(**kw, doweight_stage2=True, out_dtype="bf16", accumulate=False)
+            self._reduce = compile_moe_reduction(topk=topk, model_dim=model_dim, dtype_str="bf16")
         self._w1 = self._w2 = self._sw1 = self._sw2 = None
 
     def describe(self) -> dict:
@@ -94,7 +107,7 @@ class ExpertParallelMoe:
         self._sw2 = scale_w2.reshape(-1).float().contiguous()
 
     def forward_local(self, x_q, scale_x, topk_ids, topk_weights):
-        """This rank's partial output [tokens, model_dim] fp32 (routes to other ranks' experts contribute nothing)."""
+        """This rank's partial output [tokens, model_dim] (routes to other ranks' experts contribute nothing)."""
         from . import pertoken_quant
         from .kernels.moe.moe_gemm_2stage import moe_sorting
 
@@ -112,16 +125,113 @@ class ExpertParallelMoe:
                  self.inter_dim, self.model_dim, blocks, st)
         qd = torch.float8_e4m3fn if self.in_dtype == "fp8" else torch.int8
         a2, sa2 = pertoken_quant(out1, quant_dtype=qd)
-        y = torch.zeros(tokens, self.model_dim, dtype=torch.float32, device=dev)
-        self._g2(y, a2.reshape(-1), self._w2.reshape(-1), sa2.reshape(-1), self._sw2, srt, e_ids, wts, post, tokens,
+        if self.out_dtype == "f32":
+            y = torch.zeros(tokens, self.model_dim, dtype=torch.float32, device=dev)
+            self._g2(y, a2.reshape(-1), self._w2.reshape(-1), sa2.reshape(-1), self._sw2, srt, e_ids, wts, post, tokens,
+                     self.model_dim, self.inter_dim, blocks, st)
+            return y
+        # rows of routes that belong to other ranks stay zero and add nothing to the token's sum
+        out2 = torch.zeros(tokens * self.topk, self.model_dim, dtype=torch.bfloat16, device=dev)
+        self._g2(out2, a2.reshape(-1), self._w2.reshape(-1), sa2.reshape(-1), self._sw2, srt, e_ids, wts, post, tokens,
                  self.model_dim, self.inter_dim, blocks, st)
+        y = torch.empty(tokens, self.model_dim, dtype=torch.bfloat16, device=dev)
+        self._reduce(out2, y, None, None, tokens, st)
         return y
 
     def forward(self, x_q, scale_x, topk_ids, topk_weights, handshake_group=None):
-        """The layer's output [tokens, model_dim] fp32 on every rank: local part, then one all-reduce (sum)."""
+        """The layer's output [tokens, model_dim] on every rank: local part, then one all-reduce (sum)."""
         if handshake_group is not None:
             check_agreement(dict(self.describe(), tokens=int(x_q.shape[0])), group=handshake_group)
         y = self.forward_local(x_q, scale_x, topk_ids, topk_weights)
         if self.world > 1:
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y
+
+
+def _bench_main():
+    """Timing driver: ``python -m torch.distributed.run --nproc-per-node W -m flydsl_b200.expert_parallel
+    [--tokens T]``: one rank per GPU, seeded synthetic weights and routing, device time of the whole
+    layer (routing table, both stages, quantiser, all-reduce) as the max over ranks; rank 0 prints one JSON line."""
+    import argparse
+    import json
+    import os
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--model-dim", type=int, default=4096)
+    ap.add_argument("--inter-dim", type=int, default=2048)
+    ap.add_argument("--experts", type=int, default=8)
+    ap.add_argument("--topk", type=int, default=2)
+    ap.add_argument("--tile-m", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--out-dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--graph", action="store_true", help="one GPU only: capture the layer into one CUDA graph and time replays")
+    a = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if a.graph and world > 1:
+        # capturing the NCCL all-reduce of this layer did not complete on the test machine: single GPU only
+        raise SystemExit("--graph times the single-GPU layer only")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    op = ExpertParallelMoe(model_dim=a.model_dim, inter_dim=a.inter_dim, experts=a.experts, topk=a.topk, tile_m=a.tile_m,
+                           in_dtype="fp8", out_dtype=a.out_dtype, rank=rank, world=world)
+    g = torch.Generator(device=dev).manual_seed(1234)  # the same routing and activations on every rank
+    fp8 = torch.float8_e4m3fn
+
+    def q8(*shape):
+        return (torch.randn(*shape, generator=g, device=dev) * 64).clamp_(-448, 448).to(fp8)
+
+    x, sx = q8(a.tokens, a.model_dim), torch.rand(a.tokens, generator=g, device=dev) * 1e-2
+    vals, ids = torch.topk(torch.rand(a.tokens, a.experts, generator=g, device=dev), k=a.topk, dim=1)
+    wts = torch.softmax(vals, dim=1)
+    el = op.shard.experts_local
+    gw = torch.Generator(device=dev).manual_seed(99 + rank)
+    w1 = (torch.randn(el, 2 * a.inter_dim, a.model_dim, generator=gw, device=dev) * 64).clamp_(-448, 448).to(fp8)
+    w2 = (torch.randn(el, a.model_dim, a.inter_dim, generator=gw, device=dev) * 64).clamp_(-448, 448).to(fp8)
+    op.load_expert_weights(w1, torch.full((el, 2 * a.inter_dim), 1e-3, device=dev), w2, torch.full((el, a.model_dim), 1e-3, device=dev))
+    for _ in range(3):
+        op.forward(x, sx, ids.int(), wts)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ids32 = ids.int()
+    if a.graph:
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            op.forward(x, sx, ids32, wts)
+            st.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=st):
+                op.forward(x, sx, ids32, wts)
+            graph.replay()
+            st.synchronize()
+            e0.record(st)
+            for _ in range(a.iters):
+                graph.replay()
+            e1.record(st)
+            st.synchronize()
+    else:
+        e0.record()
+        for _ in range(a.iters):
+            op.forward(x, sx, ids32, wts)
+        e1.record()
+        torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / a.iters], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        flops = 2.0 * a.tokens * a.topk * 3 * a.inter_dim * a.model_dim  # gate, up and down projections of every route
+        print(json.dumps({"layer": "expert-parallel MoE", "n_gpus": world, "tokens": a.tokens, "experts": a.experts,
+                          "topk": a.topk, "model_dim": a.model_dim, "inter_dim": a.inter_dim, "tile_m": a.tile_m, "out_dtype": a.out_dtype, "cuda_graph": bool(a.graph),
+                          "ms_per_layer": round(float(t[0]), 4), "tflops": round(flops / float(t[0]) / 1e9, 1)}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    _bench_main()

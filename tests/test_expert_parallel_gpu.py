@@ -29,18 +29,18 @@ def _worker(rank, world, port, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     ok, msg = True, ""
     try:
-        for in_dtype, tokens, tile_m in (("fp8", 200, 64), ("int8", 40, 16)):
+        for in_dtype, tokens, tile_m, out_dtype in (("fp8", 200, 64, "bf16"), ("int8", 40, 16, "f32"), ("fp8", 300, 128, "f32")):
             model_dim, inter_dim, experts, topk = 512, 256, 8, 2
             d = moe_oracle.make_inputs(tokens, model_dim, inter_dim, experts, topk, in_dtype, seed=17 + tokens)  # same on every rank
             op = ExpertParallelMoe(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m,
-                                   in_dtype=in_dtype, rank=rank, world=world)
+                                   in_dtype=in_dtype, out_dtype=out_dtype, rank=rank, world=world)
             sl = slice(op.shard.e0, op.shard.e1)
             op.load_expert_weights(d["w1_q"][sl].to(dev), d["scale_w1"][sl].to(dev), d["w2_q"][sl].to(dev), d["scale_w2"][sl].to(dev))
             y = op.forward(d["x_q"].to(dev), d["scale_x"].to(dev), d["topk_ids"].to(dev), d["topk_weights"].to(dev))
             torch.cuda.synchronize()
             ref = moe_oracle.moe_gemm2(d["a2_q"], d["w2_q"], d["scale_a2"], d["scale_w2"], d["topk_ids"].long(),
                                        d["topk_weights"], model_dim, True)
-            err = float((y.cpu() - ref).abs().max())
+            err = float((y.float().cpu() - ref).abs().max())
             if err > 5e-2 * float(ref.abs().max()):
                 ok, msg = False, f"{in_dtype}: max abs error {err} on rank {rank}"
             if _lib.read_status() != 0:
