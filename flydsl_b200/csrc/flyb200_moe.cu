@@ -93,7 +93,7 @@ int launch_moe_rows(const CUtensorMap& tmA, const MoeParams& p, int blocks, cuda
   int sms = 0;
   int rc = sm_count(&sms);
   if (rc) return rc;
-  const long long row_blocks = static_cast<long long>(blocks) * p.tile_m / BLOCK_ROWS;
+  const long long row_blocks = (static_cast<long long>(blocks) * p.tile_m + BLOCK_ROWS - 1) / BLOCK_ROWS;
   const int pairs = STAGE == 1 ? (p.n_out + BLOCK_ROWS - 1) / BLOCK_ROWS : (p.n_out + MOE_ROWS_BN - 1) / MOE_ROWS_BN;
   const long long items = row_blocks * pairs;
   const int grid = static_cast<int>(items < sms ? items : sms);
@@ -221,10 +221,10 @@ int flyb200_moe_gemm(int stage, void* out, const void* a_sorted, const void* w_s
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   CUtensorMap tmA;
-  // Routing blocks of 128 or 256 rows: persistent kernel with the tokens on the
+  // Routing blocks of 64, 128 or 256 rows: persistent kernel with the tokens on the
   // UMMA M side (FLYB200_MOE_KERNEL=1 in the environment forces the other form, for tests and tuning).
   const char* force = getenv("FLYB200_MOE_KERNEL");
-  const bool rows_form = tile_m % BLOCK_ROWS == 0 && !(force && force[0] == '1');
+  const bool rows_form = (tile_m % BLOCK_ROWS == 0 || tile_m == 64) && !(force && force[0] == '1');
   if (rows_form) {
     rc = host::byte_matrix_map(&tmA, a_sorted, static_cast<uint64_t>(K), static_cast<uint64_t>(blocks) * tile_m, BLOCK_ROWS);
     if (rc) return rc;

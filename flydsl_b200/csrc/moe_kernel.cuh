@@ -381,7 +381,7 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gemm_kernel(const __grid_cons
 }
 
 // ---------------------------------------------------------------------------
-// Large routing blocks (tile_m a multiple of 128): persistent form
+// Large routing blocks (tile_m a multiple of 128, or 64): persistent form
 // ---------------------------------------------------------------------------
 // Tokens on the UMMA M side (128 sorted rows per work item), the two weight
 // tiles side by side on the N side (256 channels: stage 1 gate | up, stage 2 two
@@ -486,7 +486,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) moe_rows_kernel(const __grid_c
   const int n_rows = __ldg(p.num_valid);
   const int row_blocks = (n_rows + BLOCK_ROWS - 1) / BLOCK_ROWS;
   const int pairs = STAGE == 1 ? (p.n_out + BLOCK_ROWS - 1) / BLOCK_ROWS : (p.n_out + BN - 1) / BN;
-  const int items = row_blocks * pairs;
+  // Routing blocks of 64 rows: a 128-row block holds two of them.  Where both have
+  // the same expert they are one item; where the expert changes inside the 128
+  // rows the block is worked on twice ("passes"), once per expert, each pass
+  // storing only its own 64 rows.  That happens once per expert boundary.
+  const int passes = p.tile_m == 64 ? 2 : 1;
+  const int items = row_blocks * pairs * passes;
   const int num_kb = p.K_bytes / KBLOCK_BYTES;
   auto item_coords = [&](int t, int& rb, int& pair) {
     const int per_group = MOE_ROWS_GROUP * pairs;
@@ -497,10 +502,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) moe_rows_kernel(const __grid_c
     rb = first + r % gm;
     pair = r / gm;
   };
-  // expert of a row block, or -1 when the block has none
-  auto expert_of = [&](int rb) {
-    const int e = __ldg(p.expert_ids + (rb * BLOCK_ROWS) / p.tile_m);
+  // expert of the routing block that starts at sorted row `row`, or -1 when there is none
+  auto expert_at = [&](int row) {
+    if (row >= n_rows) return -1;
+    const int e = __ldg(p.expert_ids + row / p.tile_m);
     return (e < 0 || e >= p.experts) ? -1 : e;
+  };
+  // Item t -> row block, channel pair, expert (-1: nothing to do) and the rows [lo, hi) it stores.
+  auto item_of = [&](int t, int& rb, int& pair, int& lo, int& hi) {
+    // all first passes come before the (few) second passes, so that the CTAs share the real work evenly
+    const int base = row_blocks * pairs;
+    item_coords(t % base, rb, pair);
+    lo = 0;
+    hi = BLOCK_ROWS;
+    if (passes == 1) return expert_at(rb * BLOCK_ROWS);
+    const int ea = expert_at(rb * BLOCK_ROWS), eb = expert_at(rb * BLOCK_ROWS + 64);
+    if (t < base) {
+      if (eb != ea) hi = 64;
+      return ea;
+    }
+    lo = 64;
+    return eb == ea ? -1 : eb;
   };
   // rows of the image and channels that exist for the two tiles of a pair
   auto tiles_of = [&](int pair, int (&w_row)[2], int (&n_valid)[2]) {
@@ -527,9 +549,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) moe_rows_kernel(const __grid_c
       int issued = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
-        int rb, pair;
-        item_coords(t, rb, pair);
-        const int expert = expert_of(rb);
+        int rb, pair, lo, hi;
+        const int expert = item_of(t, rb, pair, lo, hi);
         if (expert < 0) continue;
         int w_row[2], n_valid[2];
         tiles_of(pair, w_row, n_valid);
@@ -579,9 +600,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) moe_rows_kernel(const __grid_c
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
-        int rb, pair;
-        item_coords(t, rb, pair);
-        if (expert_of(rb) < 0) continue;
+        int rb, pair, lo, hi;
+        if (item_of(t, rb, pair, lo, hi) < 0) continue;
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
           report_failure(p.status, ST_TIMEOUT, abort_flag);
           break;
@@ -622,17 +642,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) moe_rows_kernel(const __grid_c
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
-      int rb, pair;
-      item_coords(t, rb, pair);
-      const int expert = expert_of(rb);
+      int rb, pair, lo, hi;
+      const int expert = item_of(t, rb, pair, lo, hi);
       if (expert < 0) continue;
       int w_row[2], n_valid[2];
       tiles_of(pair, w_row, n_valid);
       // this thread's token row
-      const int srow = rb * BLOCK_ROWS + q * 32 + lane;
+      const int trow = q * 32 + lane;
+      const int srow = rb * BLOCK_ROWS + trow;
       long long orow = -1;
       float sa = 0.0f, tw = 1.0f;
-      if (srow < n_rows) {
+      if (srow < n_rows && trow >= lo && trow < hi) {
         const int id = __ldg(p.sorted_ids + srow);
         const int tok = id & 0xFFFFFF;
         const int slot = static_cast<int>(static_cast<uint32_t>(id) >> 24);
