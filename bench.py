@@ -563,7 +563,7 @@ def main():
         "launch_ms_median": med_ms,
     }
     extras = {}
-    if not args.no_extras:
+    if not args.no_extras and world == 1:  # single-GPU side measurements: not repeated in the multi-GPU runs
         PDLW = 3 << 28  # small-M kernel: dependent launch with early prefetch of the (static) weights
         cases = [
             ("c1_fp8_128x4096x4096", 128, 4096, 4096, "fp8", 0),
