@@ -51,7 +51,7 @@ SIGNATURES = {
     "flyb200_selftest_bounded_wait": (_i, [ctypes.c_uint, _vp]),
     "flyb200_moe_gather_rows": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "flyb200_moe_gemm": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 12 + [_vp]),
-    "flyb200_moe_reduce": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
+    "flyb200_moe_reduce": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp]),
     "flyb200_moe_sorting": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flyb200_gemm_mxfp8": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_mx_scale_image": (_i, [_vp, _vp, _i, _i, _vp]),

@@ -271,8 +271,10 @@ int flyb200_moe_sorting(const int* topk_ids, const float* topk_weights, int toke
   return FLYB200_OK;
 }
 
-int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, void* stream) {
+int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, const int* expert_mask,
+                       const int* topk_ids, int num_experts, void* stream) {
   if (!y || !x || tokens < 0 || topk <= 0 || dim <= 0) return FLYB200_E_BAD_ARG;
+  if (expert_mask && (!topk_ids || num_experts <= 0)) return FLYB200_E_BAD_ARG;
   if (dim % 2 != 0) return FLYB200_E_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(y) & 3u) || (reinterpret_cast<uintptr_t>(x) & 3u)) return FLYB200_E_BAD_ALIGN;
   if (tokens == 0) return FLYB200_OK;
@@ -282,10 +284,12 @@ int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, in
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == FLYB200_OUT_BF16) {
     moe_reduce_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, s>>>(
-        static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x), tokens, topk, dim);
+        static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(x), tokens, topk, dim, expert_mask, topk_ids,
+        num_experts);
   } else if (dtype == FLYB200_OUT_FP16) {
     moe_reduce_kernel<__half><<<static_cast<int>(blocks), 256, 0, s>>>(static_cast<__half*>(y),
-                                                                       static_cast<const __half*>(x), tokens, topk, dim);
+                                                                       static_cast<const __half*>(x), tokens, topk, dim,
+                                                                       expert_mask, topk_ids, num_experts);
   } else {
     return FLYB200_E_UNSUPPORTED;
   }

@@ -864,8 +864,12 @@ moe_sort_place_kernel(const int* __restrict__ topk_ids, const float* __restrict_
 }
 
 // y[t, :] = sum over the top-k slots of x[t, slot, :] (fp32 sum, one rounding).
+// With a mask, slot k of token t counts only if expert_mask[topk_ids[t, k]] != 0
+// (the expert-parallel validity mask of kernels/moe/moe_gemm_2stage/moe_reduce.py:3-7
+// in the reference): rows of routes that another rank serves are never read.
 template <typename T>
-__global__ void moe_reduce_kernel(T* __restrict__ y, const T* __restrict__ x, int tokens, int topk, int dim) {
+__global__ void moe_reduce_kernel(T* __restrict__ y, const T* __restrict__ x, int tokens, int topk, int dim,
+                                  const int* __restrict__ expert_mask, const int* __restrict__ topk_ids, int num_experts) {
   const long long total = static_cast<long long>(tokens) * dim / 2;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -873,6 +877,10 @@ __global__ void moe_reduce_kernel(T* __restrict__ y, const T* __restrict__ x, in
     const long long c = (i * 2) % dim;
     float lo = 0.0f, hi = 0.0f;
     for (int s = 0; s < topk; ++s) {
+      if (expert_mask != nullptr) {
+        const int e = __ldg(topk_ids + t * topk + s);
+        if (e < 0 || e >= num_experts || __ldg(expert_mask + e) == 0) continue;
+      }
       const T* src = x + (t * topk + s) * dim + c;
       if constexpr (sizeof(T) == 2) {
         if constexpr (std::is_same<T, __nv_bfloat16>::value) {

@@ -87,7 +87,9 @@ class ExpertParallelMoe:
             self._g2 = compile_moe_gemm2(**kw, doweight_stage2=True, out_dtype="f32", accumulate=True)
         else:
             self._g2 = compile_moe_gemm2(**kw, doweight_stage2=True, out_dtype="bf16", accumulate=False)
-            self._reduce = compile_moe_reduction(topk=topk, model_dim=model_dim, dtype_str="bf16")
+            self._reduce = compile_moe_reduction(topk=topk, model_dim=model_dim, dtype_str="bf16", use_mask=True,
+                                                 num_experts=experts)
+            self._mask = None  # 1 for this rank's experts, built on first use on the layer's device
         self._w1 = self._w2 = self._sw1 = self._sw2 = None
 
     def describe(self) -> dict:
@@ -130,12 +132,16 @@ class ExpertParallelMoe:
             self._g2(y, a2.reshape(-1), self._w2.reshape(-1), sa2.reshape(-1), self._sw2, srt, e_ids, wts, post, tokens,
                      self.model_dim, self.inter_dim, blocks, st)
             return y
-        # rows of routes that belong to other ranks stay zero and add nothing to the token's sum
-        out2 = torch.zeros(tokens * self.topk, self.model_dim, dtype=torch.bfloat16, device=dev)
+        # rows of routes that belong to other ranks are never written; the masked reduction skips them
+        out2 = torch.empty(tokens * self.topk, self.model_dim, dtype=torch.bfloat16, device=dev)
         self._g2(out2, a2.reshape(-1), self._w2.reshape(-1), sa2.reshape(-1), self._sw2, srt, e_ids, wts, post, tokens,
                  self.model_dim, self.inter_dim, blocks, st)
+        if self._mask is None or self._mask.device != dev:
+            mask = torch.zeros(self.shard.experts_total, dtype=torch.int32, device=dev)
+            mask[self.shard.e0 : self.shard.e1] = 1
+            self._mask = mask
         y = torch.empty(tokens, self.model_dim, dtype=torch.bfloat16, device=dev)
-        self._reduce(out2, y, None, None, tokens, st)
+        self._reduce(out2, y, self._mask, topk_ids.to(torch.int32).contiguous(), tokens, st)
         return y
 
     def forward(self, x_q, scale_x, topk_ids, topk_weights, handshake_group=None):

@@ -273,15 +273,17 @@ def compile_moe_gemm2(
 
 def compile_moe_reduction(*, topk, model_dim, dtype_str="f16", use_mask=False, num_experts=0, out_dtype_str=None):
     """Top-k reduction ``Y[t, :] = sum_slot X[t, slot, :]``; returns
-    ``launch(X, Y, expert_mask, topk_ids, m_tokens, stream)`` as the reference does."""
-    if use_mask:
-        raise ValueError("use_mask=True (expert-parallel masking) is not built for B200")
+    ``launch(X, Y, expert_mask, topk_ids, m_tokens, stream)`` as the reference does.
+    With ``use_mask`` slot k of token t counts only if ``expert_mask[topk_ids[t, k]] != 0``
+    (int32 tensors; the expert-parallel validity mask): rows of masked routes are never read."""
     if dtype_str not in ("f16", "bf16") or (out_dtype_str or dtype_str) != dtype_str:
         raise ValueError("the reduction is built for f16 and bf16 with the output type of the input")
     code, tdt = _OUT[dtype_str]
-    topk, model_dim = int(topk), int(model_dim)
+    topk, model_dim, num_experts = int(topk), int(model_dim), int(num_experts)
     if model_dim % 2 != 0:
         raise ValueError("model_dim must be even")
+    if use_mask and num_experts <= 0:
+        raise ValueError("use_mask=True needs num_experts")
 
     def launch(X, Y, expert_mask, topk_ids, m_tokens, stream=None):
         m = int(m_tokens)
@@ -289,9 +291,16 @@ def compile_moe_reduction(*, topk, model_dim, dtype_str="f16", use_mask=False, n
             raise ValueError(f"X and Y must be CUDA tensors of {tdt}")
         if X.numel() < m * topk * model_dim or Y.numel() < m * model_dim:
             raise ValueError("X or Y is smaller than the launch needs")
+        mask_ptr = ids_ptr = None
+        if use_mask:
+            for name, t, n in (("expert_mask", expert_mask, num_experts), ("topk_ids", topk_ids, m * topk)):
+                if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.int32 or t.numel() < n or not t.is_contiguous():
+                    raise ValueError(f"{name} must be a contiguous int32 CUDA tensor of at least {n} elements")
+            mask_ptr, ids_ptr = expert_mask.data_ptr(), topk_ids.data_ptr()
         with torch.cuda.device(X.device):
             _lib.check(
-                _lib.load().flyb200_moe_reduce(Y.data_ptr(), X.data_ptr(), m, topk, model_dim, code, _stream_handle(stream)),
+                _lib.load().flyb200_moe_reduce(Y.data_ptr(), X.data_ptr(), m, topk, model_dim, code, mask_ptr, ids_ptr,
+                                               num_experts, _stream_handle(stream) or None),
                 "moe_reduce",
             )
 

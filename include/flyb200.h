@@ -285,8 +285,13 @@ int flyb200_moe_sorting(const int* topk_ids, const float* topk_weights, int toke
                         int* counts_scratch, void* stream);
 
 /* y[token, dim] = sum over slots of x[token, slot, dim] (fp32 sum, one rounding);
- * dtype FLYB200_OUT_BF16 or FLYB200_OUT_FP16, dim even. */
-int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, void* stream);
+ * dtype FLYB200_OUT_BF16 or FLYB200_OUT_FP16, dim even.  With expert_mask
+ * (int32[num_experts], else NULL) slot k of token t counts only if
+ * expert_mask[topk_ids[t, k]] != 0 — the expert-parallel validity mask of the
+ * reference's reduction (kernels/moe/moe_gemm_2stage/moe_reduce.py:3-7,100-150);
+ * rows of masked routes are never read.  topk_ids: int32[tokens, topk]. */
+int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, int dtype, const int* expert_mask,
+                       const int* topk_ids, int num_experts, void* stream);
 
 /* ---- MXFP8: E4M3 codes with one E8M0 scale per 32 elements of K on both operands ----
  * Replaces the MXFP8 x MXFP8 configuration of the reference's block-scaled

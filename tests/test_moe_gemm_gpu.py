@@ -495,3 +495,22 @@ def test_int8smooth_stage2_is_the_int8_path(dev):
     a = run_stage2(dev, d, **SHAPE, tile_m=32, in_dtype="int8", out_dtype="bf16", accumulate=False)
     b = run_stage2(dev, d, **SHAPE, tile_m=32, in_dtype="int8smooth", out_dtype="bf16", accumulate=False)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype_str", ["f16", "bf16"])
+def test_topk_reduction_with_expert_mask(dev, dtype_str):
+    """Slot k of token t counts only if expert_mask[topk_ids[t, k]] != 0; masked rows may hold anything (NaN here)."""
+    tokens, topk, dim, experts = 50, 3, 256, 6
+    g = torch.Generator().manual_seed(8)
+    ids, _ = moe_oracle.make_routing(tokens, experts, topk, g)
+    mask = torch.tensor([1, 0, 1, 1, 0, 0], dtype=torch.int32)
+    x = torch.randn(tokens, topk, dim, generator=g).to(OUT_T[dtype_str])
+    keep = mask[ids.long()].bool()
+    x_dev = x.clone()
+    x_dev[~keep] = float("nan")
+    y = torch.full((tokens, dim), 7.0, dtype=OUT_T[dtype_str], device=dev)
+    fn = compile_moe_reduction(topk=topk, model_dim=dim, dtype_str=dtype_str, use_mask=True, num_experts=experts)
+    fn(x_dev.to(dev), y, mask.to(dev), ids.to(dev), tokens, None)
+    torch.cuda.synchronize()
+    want = (x.float() * keep.unsqueeze(-1)).sum(dim=1).to(OUT_T[dtype_str])
+    assert torch.equal(y.cpu(), want)

@@ -125,5 +125,6 @@ def test_builders_validate_like_the_reference():
         compile_moe_gemm1(**{**kw, "tile_m": 24}, doweight_stage1=False)
     with pytest.raises(ValueError, match="tile_k"):
         compile_moe_gemm2(**{**kw, "tile_k": 64}, doweight_stage2=True)
-    with pytest.raises(ValueError, match="use_mask"):
+    with pytest.raises(ValueError, match="num_experts"):
         compile_moe_reduction(topk=2, model_dim=256, use_mask=True)
+    compile_moe_reduction(topk=2, model_dim=256, use_mask=True, num_experts=8)
