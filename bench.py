@@ -15,11 +15,18 @@ whole problem runs on that GPU.  The metric is aggregate TFLOP/s
             step's activations and token scales go pinned-host -> device and
             the output shard comes back device -> pinned-host inside the timed
             region (weights are model state: preshuffled and resident).
-`roofline`  the GEMM kernel's own launch time from CUDA events.
+`roofline`  the GEMM kernel's own launch time from CUDA events; `roofline.configs`
+            holds the single-GPU decode / prefill configurations (HBM- or
+            tensor-bound), timed after the main region (not part of `value`),
+            and `roofline.cublaslt_fp8_tflops` the library FP8 GEMM
+            (torch._scaled_mm) on the same shapes in the same run, for scale.
 `cpu_baseline` / `--impl reference`  the reference's torch dequantise-and-matmul
             check on the host cores, on a bounded sample of the same workload.
-`extras`    the single-GPU decode / prefill configurations (HBM- or
-            tensor-bound), timed after the main region (not part of `value`).
+`config.parity_check`  after the timed regions the outputs are compared with
+            the CPU reference on sampled rows and, on several GPUs, the fused
+            and the NCCL all-gather paths with each other; a mismatch makes the
+            run exit non-zero.
+`extras`    side figures (block-scaled and grouped GEMMs).
 """
 
 from __future__ import annotations
@@ -199,50 +206,50 @@ def run_reference_arm(args, m, n, k, in_dtype, workload):
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
-def quantised_on_gpu(m, n, k, in_dtype, dev, seed, weight_scale):
+def quantise_rows(x, in_dtype):
+    """Per-row symmetric quantisation as the benchmark configurations state it:
+    scale = amax / 448 (fp8) or amax / 127 with round-to-nearest (int8)."""
     from flydsl_b200 import pertoken_quant
 
+    if in_dtype == "int8":
+        s = x.abs().amax(dim=-1, keepdim=True) / 127.0
+        s.masked_fill_(s == 0, 1.0)
+        return torch.round(x / s).clamp_(-127, 127).to(torch.int8), s
+    return pertoken_quant(x, quant_dtype=FP8)
+
+
+def quantised_on_gpu(m, n, k, in_dtype, dev, seed, weight_scale):
+    """Seeded N(0,1) activations [m, k] and weights [n, k] (times weight_scale),
+    quantised per token / per output channel on the GPU."""
     g = torch.Generator(device=dev).manual_seed(seed)
-    a = torch.randn(m, k, generator=g, device=dev)
-    a_q, sa = pertoken_quant(a, quant_dtype=FP8 if in_dtype == "fp8" else torch.int8)
-    del a
+    a_q, sa = quantise_rows(torch.randn(m, k, generator=g, device=dev), in_dtype)
     # weights in row chunks to bound the fp32 temporary
     w_q = torch.empty(n, k, dtype=a_q.dtype, device=dev)
     sb = torch.empty(n, 1, dtype=torch.float32, device=dev)
     step = 8192
     for i in range(0, n, step):
-        w = torch.randn(min(step, n - i), k, generator=g, device=dev) * weight_scale
-        if in_dtype == "int8":  # round to nearest, as the INT8 configuration states
-            s = w.abs().amax(dim=-1, keepdim=True) / 127.0
-            s.masked_fill_(s == 0, 1.0)
-            q = torch.round(w / s).clamp_(-127, 127).to(torch.int8)
-        else:
-            q, s = pertoken_quant(w, quant_dtype=FP8)
+        q, s = quantise_rows(torch.randn(min(step, n - i), k, generator=g, device=dev) * weight_scale, in_dtype)
         w_q[i : i + q.shape[0]] = q
         sb[i : i + q.shape[0]] = s
     return a_q, sa.view(-1), w_q, sb.view(-1)
 
 
-def time_config(m, n, k, in_dtype, dev, iters=40, hint=0):
-    """Device time of one single-GPU configuration with operand copies rotated
-    so that consecutive launches do not find their weights in L2."""
+def time_config(m, n, k, in_dtype, dev, iters=40, hint=0, seed=0, weight_scale=1.0):
+    """Device time of one single-GPU configuration: CUDA events around a graph
+    replay of `iters` launches whose operand copies rotate, so that consecutive
+    launches do not find their weights in L2.  Operands: seeded N(0,1),
+    quantised per token / per channel as the configuration states."""
     from flydsl_b200 import compile_preshuffle_gemm, shuffle_weight
 
     per = m * k + n * k + 2 * m * n
     copies = max(1, min(8, int(400e6 // per) + 1))
-    qd = FP8 if in_dtype == "fp8" else torch.int8
     fn = compile_preshuffle_gemm(N=n, K=k, tile_m=128, tile_n=256, tile_k=128, in_dtype=in_dtype, variant_hint=hint)
-    A, W, C = [], [], []
-    for i in range(copies):
-        if in_dtype == "fp8":
-            A.append((torch.randn(m, k, device=dev) * 64).clamp_(-448, 448).to(qd).view(torch.int8))
-            W.append(shuffle_weight((torch.randn(n, k, device=dev) * 64).clamp_(-448, 448).to(qd)).view(torch.int8))
-        else:
-            A.append(torch.randint(-127, 128, (m, k), device=dev, dtype=torch.int8))
-            W.append(shuffle_weight(torch.randint(-127, 128, (n, k), device=dev, dtype=torch.int8)))
-        C.append(torch.empty(m, n, dtype=torch.bfloat16, device=dev))
-    sa = torch.rand(m, device=dev) + 0.5
-    sb = torch.rand(n, device=dev) + 0.5
+    a_q, sa, w_q, sb = quantised_on_gpu(m, n, k, in_dtype, dev, seed, weight_scale)
+    w_s = shuffle_weight(w_q).view(torch.int8)
+    del w_q
+    A = [a_q.view(torch.int8)] + [a_q.view(torch.int8).clone() for _ in range(copies - 1)]
+    W = [w_s] + [w_s.clone() for _ in range(copies - 1)]
+    C = [torch.empty(m, n, dtype=torch.bfloat16, device=dev) for _ in range(copies)]
     bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
     st = torch.cuda.Stream()
 
@@ -260,13 +267,49 @@ def time_config(m, n, k, in_dtype, dev, iters=40, hint=0):
                 launch(i)
         g.replay()
         st.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(st)
-        g.replay()
-        e1.record(st)
-        st.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / iters
-    return us, copies
+        best = None
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            g.replay()
+            e1.record(st)
+            st.synchronize()
+            t = e0.elapsed_time(e1) * 1e3 / iters
+            best = t if best is None else min(best, t)
+    return best, copies
+
+
+def time_scaled_mm(m, n, k, dev, iters=5, seed=0, weight_scale=1.0):
+    """The library FP8 GEMM (torch._scaled_mm -> cuBLASLt) on the same operands and
+    scales, bf16 output: the FP8 yardstick this machine offers, since no FP8 peak is
+    measured.  Returns (us, scaling mode) or (None, reason)."""
+    a_q, sa, w_q, sb = quantised_on_gpu(m, n, k, "fp8", dev, seed, weight_scale)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    modes = (("rowwise", sa.view(m, 1).contiguous(), sb.view(1, n).contiguous()),
+             ("tensorwise", sa.max().view(()), sb.max().view(())))
+    last = "no mode ran"
+    for name, s_a, s_b in modes:
+        try:
+            def run():
+                return torch._scaled_mm(a_q, w_q.t(), scale_a=s_a, scale_b=s_b, out_dtype=torch.bfloat16, out=out)
+
+            for _ in range(2):
+                run()
+            torch.cuda.synchronize()
+            best = None
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(iters):
+                    run()
+                e1.record()
+                torch.cuda.synchronize()
+                t = e0.elapsed_time(e1) * 1e3 / iters
+                best = t if best is None else min(best, t)
+            return best, name
+        except Exception as e:  # this build of the library lacks the mode: try the next
+            last = f"{name}: {repr(e)[:120]}"
+    return None, last
 
 
 def time_mx(m, n, k, dev, iters=10):
@@ -378,6 +421,66 @@ def time_moe(tokens, model_dim, inter_dim, experts, topk, tile_m, dev, iters=20)
     return res
 
 
+def parity_check(op, a_q, sa, w_q_local, sb_local, local, full_ag, full_fused, dev, world, rank):
+    """Checker, outside every timed region: (i) on sampled rows this rank's output
+    columns against the CPU reference (fp32 dequantise-and-matmul, rtol = atol =
+    1e-2, every sampled element must pass), on up to 8192 of its columns (first and
+    last 4096); (ii) on several GPUs the all-gathered and the fused full outputs
+    against each other (bitwise) and their local columns against the local shard
+    (bitwise).  Returns a dict; `ok` is the AND over all ranks."""
+    import torch.distributed as dist
+
+    from oracle import a8w8_oracle as oracle
+
+    m = a_q.shape[0]
+    nl = w_q_local.shape[0]
+    gen = torch.Generator().manual_seed(4242)  # the same rows on every rank
+    pick = torch.cat([torch.tensor([0, 1, 127, 128, m - 129, m - 2, m - 1]), torch.randint(0, m, (57,), generator=gen)])
+    pick = pick.clamp_(0, m - 1).unique().to(dev)
+    cols = torch.arange(nl, device=dev) if nl <= 8192 else torch.cat(
+        [torch.arange(0, 4096, device=dev), torch.arange(nl - 4096, nl, device=dev)])
+    ref = oracle.run_torch(a_q[pick].cpu(), w_q_local[cols].cpu(), sa[pick].cpu(), sb_local[cols].cpu())
+    got = local[pick][:, cols].float().cpu()
+    bad = int(oracle.strict_mismatches(got, ref, 1e-2, 1e-2))
+    res = {"oracle_rows": int(pick.numel()), "oracle_cols_per_rank": int(cols.numel()), "oracle_mismatches": bad,
+           "rtol_atol": 1e-2}
+    ok = bad == 0
+    if world > 1:
+        n0, n1 = op.spec.n0, op.spec.n1
+        eq_shard = bool(torch.equal(full_ag[:, n0:n1], local))
+        res["allgather_shard_equals_local"] = eq_shard
+        ok = ok and eq_shard
+        if full_fused is not None:
+            eq_fused = bool(torch.equal(full_fused, full_ag))
+            res["fused_equals_allgather"] = eq_fused
+            ok = ok and eq_fused
+        flag = torch.tensor([1 if ok else 0, bad], dtype=torch.int64, device=dev)
+        worst = flag.clone()
+        dist.all_reduce(worst[:1], op=dist.ReduceOp.MIN)
+        dist.all_reduce(flag[1:], op=dist.ReduceOp.SUM)
+        ok = bool(worst[0].item() == 1)
+        res["oracle_mismatches"] = int(flag[1].item())
+        res["ranks_checked"] = world
+    res["ok"] = ok
+    return res
+
+
+# DRAM traffic of the dominant kernel, from one ncu capture of a smaller case with the
+# same tile order (profiles/gemm_rows_fp8_traffic.md): bytes read + written per launch
+# there, and that case's algorithmic bytes.  The weights stream once per group of row
+# tiles and the activations once, so the full workload's traffic is estimated group by
+# group (see traffic_estimate), not by plain proportion.
+NCU_TRAFFIC_CASE = None  # filled in from the capture: {"m":..,"n":..,"k":..,"group_m":..,"read":..,"write":..}
+
+
+def traffic_estimate(m, n, k, group_m):
+    """DRAM bytes per launch of the large-M kernel under its tile order: weights once per
+    group of `group_m` row tiles (they do not survive in L2 from one group to the next,
+    apart from the turn-around tiles), activations once, output once."""
+    groups = -(-((m + 127) // 128) // group_m)
+    return groups * n * k + m * k + 2 * m * n + 4 * (m + n)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -385,9 +488,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--hint", type=lambda v: int(v, 0), default=0, help="variant_hint of the main workload (tuning sweeps)")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-GPU decode/prefill side measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="skip the fused GEMM + all-gather measurement (N > 1)")
+    ap.add_argument("--no-parity", action="store_true", help="skip the parity check after the timed regions")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     m, n, k, in_dtype, wscale, seed = WORKLOADS[args.workload]
@@ -400,7 +505,7 @@ def main():
     import torch.distributed as dist
 
     from flydsl_b200 import _lib
-    from flydsl_b200.column_parallel import ColumnParallelGemm
+    from flydsl_b200.column_parallel import ColumnParallelGemm, pinned_near
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
@@ -420,7 +525,7 @@ def main():
         cpu_group = dist.new_group(backend="gloo")
 
     peaks = measured_peaks()
-    op = ColumnParallelGemm(n, k, in_dtype=in_dtype, rank=rank, world=world, cpu_group=cpu_group)
+    op = ColumnParallelGemm(n, k, in_dtype=in_dtype, rank=rank, world=world, cpu_group=cpu_group, variant_hint=args.hint)
     nl = op.spec.n_local
     # every rank: replicated activations, its own weight shard (seeded per shard)
     a_q, sa, w_q, sb = quantised_on_gpu(m, nl, k, in_dtype, dev, seed + 17 * rank, wscale)
@@ -428,7 +533,6 @@ def main():
         dist.broadcast(a_q.view(torch.int8), src=0)
         dist.broadcast(sa, src=0)
     op.load_weight_shard(w_q, sb)
-    del w_q
     c = torch.empty(m, nl, dtype=torch.bfloat16, device=dev)
     stream = torch.cuda.current_stream()
 
@@ -436,6 +540,22 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def timed(fn, reps, warm=2):
+        """max over ranks of the device time per call of fn, CUDA events on the launching stream."""
+        for _ in range(warm):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / reps
 
     # ---- device-timed region: K steps, inputs resident ---------------------
     for _ in range(args.warmup):
@@ -464,81 +584,64 @@ def main():
     value = flops_step / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end: host buffers in, host buffer out ------------------------
-    a_host = torch.empty(a_q.shape, dtype=torch.int8).pin_memory()
+    # pinned buffers on the GPU's own NUMA node; on several GPUs each rank uploads
+    # 1/world of the activations and the ranks all-gather them over NVLink
+    a_host = pinned_near(dev, tuple(a_q.shape), torch.int8)
     a_host.copy_(a_q.view(torch.int8))
-    sa_host = sa.cpu().pin_memory()
-    c_host = torch.empty(m, nl, dtype=torch.bfloat16).pin_memory()
+    sa_host = pinned_near(dev, (m,), torch.float32)
+    sa_host.copy_(sa)
+    c_host = pinned_near(dev, (m, nl), torch.bfloat16)
     e2e_steps = max(3, min(args.steps, 10))
-
-    def e2e_step():
-        # upload, multiply and download pipelined over row blocks (ColumnParallelGemm.forward_host)
-        op.forward_host(a_host, sa_host, c_host, chunks=8)
-
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
-    s1.record(stream)
-    barrier()
-    t = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
+    e2e_ms = timed(lambda: op.forward_host(a_host, sa_host, c_host, chunks=8), e2e_steps)
     e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
-    h2d = a_host.numel() + sa_host.numel() * 4
+    h2d = int(op.last_h2d_bytes)
     d2h = c_host.numel() * 2
+    e2e_ok = bool(torch.equal(c_host, c.cpu())) if not args.no_parity else None
+    del a_host, c_host
 
     # ---- optional: with the all-gather of the shards (full output on every rank)
     gathered = None
     if world > 1:
-        for _ in range(2):
-            op.forward_full(a_q, sa, row_major=False)
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record(stream)
         reps = max(3, min(args.steps, 10))
-        for _ in range(reps):
-            op.forward_full(a_q, sa, row_major=False)
-        g1.record(stream)
-        barrier()
-        t = torch.tensor([g0.elapsed_time(g1)], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        g_ms = float(t.item()) / reps
+        g_ms = timed(lambda: op.forward_full(a_q, sa, row_major=False), reps)
         gathered = {"ms_per_step": g_ms, "tflops": flops_step / (g_ms * 1e-3) / 1e12,
                     "what": "GEMM shard + NCCL all-gather of bf16 shards (shard-major result)"}
 
     # ---- optional: the same full output from the GEMM fused with the exchange
     #      (tiles TMA-stored straight into every rank's full-width buffer)
     fused = None
+    fused_ready = False
     if world > 1 and not args.no_fused:
         try:
             op.enable_fused_gather(m_max=m)
-            for _ in range(2):
-                op.forward_full_fused(a_q, sa)
-            barrier()
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            f0.record(stream)
+            fused_ready = True
             reps = max(3, min(args.steps, 10))
-            for _ in range(reps):
-                op.forward_full_fused(a_q, sa)
-            f1.record(stream)
-            barrier()
-            t = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            f_ms = float(t.item()) / reps
+            f_ms = timed(lambda: op.forward_full_fused(a_q, sa), reps)
             fused = {"ms_per_step": f_ms, "tflops": flops_step / (f_ms * 1e-3) / 1e12,
                      "what": "one GEMM kernel per rank whose epilogue TMA-stores every tile into all ranks' "
                              "full-width buffers (peer memory), then a one-element NCCL all-reduce as barrier"}
         except Exception as e:  # symmetric memory unavailable: report, keep the main numbers
             fused = {"unavailable": repr(e)[:200]}
 
+    # ---- parity, after every timed region --------------------------------------
+    parity = None
+    if not args.no_parity:
+        local = op.forward(a_q, sa, out=c)
+        full_ag = op.forward_full(a_q, sa, row_major=True) if world > 1 else None
+        full_fused = op.forward_full_fused(a_q, sa) if fused_ready else None
+        barrier()
+        parity = parity_check(op, a_q, sa, w_q, sb, local, full_ag, full_fused, dev, world, rank)
+        parity["e2e_output_equals_device_output"] = e2e_ok
+        parity["ok"] = bool(parity["ok"] and e2e_ok)
+        del full_ag, full_fused
+    del w_q
+
     if rank != 0:
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
+        if parity is not None and not parity["ok"]:
+            sys.exit(3)
         return
 
     # ---- rank 0: roofline, extras, CPU baseline, the JSON line ----------------
@@ -546,51 +649,83 @@ def main():
     flops_launch = 2.0 * m * nl * k
     achieved = flops_launch / (med_ms * 1e-3) / 1e12
     fp8_peak = 2.0 * peaks["bf16_tflops"]
+    plan = op.launch.plan(m)
+    group_m = (args.hint >> 16) & 0xFF or 16
+    traffic = None
+    traffic_note = "no ncu capture recorded for this build"
+    if NCU_TRAFFIC_CASE:
+        tc = NCU_TRAFFIC_CASE
+        model_small = traffic_estimate(tc["m"], tc["n"], tc["k"], tc["group_m"])
+        traffic = (tc["read"] + tc["write"]) / model_small * traffic_estimate(m, nl, k, group_m)
+        traffic_note = (f"ncu dram__bytes_read+write of {tc['m']}x{tc['n']}x{tc['k']} (same tile order, group {tc['group_m']}): "
+                        f"{(tc['read'] + tc['write']) / 1e6:.0f} MB per launch = {(tc['read'] + tc['write']) / model_small:.2f} x the "
+                        "tile-order model (weights once per group of row tiles + activations + output), scaled to this "
+                        "launch by that model; profiles/gemm_rows_fp8_traffic.md")
     roofline = {
         "bound": "tensor",
-        "kernel": "gemm_rows_kernel<fp8, BN=256, 4 stages> (tcgen05 kind::f8f6f4, 128x256 tiles, persistent)",
+        "kernel": f"gemm_rows_kernel<fp8> (tcgen05 kind::f8f6f4, 128x{plan['bn']} tiles, persistent, {plan['stages']} stages)",
         "achieved": achieved,
         "peak": fp8_peak,
         "unit": "TFLOP/s",
         "frac": achieved / fp8_peak,
         "peak_source": f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no FP8 figure is measured",
         "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
-        "traffic": None,
-        "traffic_note": "DRAM counters captured on the 4096x8192x8192 case only: 214 MB per launch vs 168 MB "
-        "algorithmic (ncu launch-list summary under profiles/); the full workload re-streams the weights once per group of "
-        "16 row tiles, so its traffic does not scale in proportion",
+        "traffic": traffic,
+        "traffic_note": traffic_note,
         "algorithmic_bytes": gemm_bytes(m, nl, k),
         "launch_ms_median": med_ms,
     }
     extras = {}
     if not args.no_extras and world == 1:  # single-GPU side measurements: not repeated in the multi-GPU runs
+        del c, a_q
+        torch.cuda.empty_cache()
         PDLW = 3 << 28  # small-M kernel: dependent launch with early prefetch of the (static) weights
         cases = [
-            ("c1_fp8_128x4096x4096", 128, 4096, 4096, "fp8", 0),
-            ("c2_int8_32x8192x8192", 32, 8192, 8192, "int8", 0),
-            ("c2_int8_32x8192x8192_pdl_static_weights", 32, 8192, 8192, "int8", PDLW),
-            ("c4_fp8_1x8192x8192", 1, 8192, 8192, "fp8", 0),
-            ("c4_fp8_1x8192x8192_pdl_static_weights", 1, 8192, 8192, "fp8", PDLW),
-            ("c4_fp8_16x8192x8192", 16, 8192, 8192, "fp8", 0),
-            ("c4_fp8_16x8192x8192_pdl_static_weights", 16, 8192, 8192, "fp8", PDLW),
-            ("c4_fp8_64x8192x8192", 64, 8192, 8192, "fp8", 0),
-            ("c4_fp8_256x8192x8192", 256, 8192, 8192, "fp8", 0),
-            ("c4_fp8_1024x8192x8192", 1024, 8192, 8192, "fp8", 0),
-            ("c4_fp8_4096x8192x8192", 4096, 8192, 8192, "fp8", 0),
-            ("c4_fp8_16384x8192x8192", 16384, 8192, 8192, "fp8", 0),
-            ("c3_fp8_8192x28672x8192", 8192, 28672, 8192, "fp8", 0),
+            # name, M, N, K, dtype, weight scale, seed, bound, also time with static-weight prefetch
+            ("c1_fp8_128x4096x4096", 128, 4096, 4096, "fp8", 1.0, 1001, "hbm", True),
+            ("c2_int8_32x8192x8192", 32, 8192, 8192, "int8", 1.0, 1002, "hbm", True),
+            ("c4_fp8_1x8192x8192", 1, 8192, 8192, "fp8", 1.0, 1040, "hbm", True),
+            ("c4_fp8_16x8192x8192", 16, 8192, 8192, "fp8", 1.0, 1041, "hbm", True),
+            ("c4_fp8_64x8192x8192", 64, 8192, 8192, "fp8", 1.0, 1042, "hbm", False),
+            ("c4_fp8_256x8192x8192", 256, 8192, 8192, "fp8", 1.0, 1043, "hbm", False),
+            ("c4_fp8_1024x8192x8192", 1024, 8192, 8192, "fp8", 1.0, 1044, "tensor", False),
+            ("c4_fp8_4096x8192x8192", 4096, 8192, 8192, "fp8", 1.0, 1045, "tensor", False),
+            ("c4_fp8_16384x8192x8192", 16384, 8192, 8192, "fp8", 1.0, 1046, "tensor", False),
+            ("c3_fp8_8192x28672x8192", 8192, 28672, 8192, "fp8", 0.02, 1003, "tensor", False),
         ]
-        for name, em, en, ek, edt, hint in cases:
-            us, copies = time_config(em, en, ek, edt, dev, iters=20 if em <= 4096 and en <= 8192 else 5, hint=hint)
+        configs = {}
+        for name, em, en, ek, edt, ews, eseed, bound, static_too in cases:
+            iters = 20 if em <= 4096 and en <= 8192 else 5
+            us, copies = time_config(em, en, ek, edt, dev, iters=iters, seed=eseed, weight_scale=ews)
             by = gemm_bytes(em, en, ek)
-            extras[name] = {
-                "us": round(us, 2),
-                "tflops": round(2.0 * em * en * ek / us / 1e6, 1),
-                "hbm_gbs": round(by / us / 1e3, 1),
-                "hbm_frac_of_measured": round(by / us / 1e3 / peaks["hbm_gbs"], 3),
-                "frac_of_nominal_fp8": round(2.0 * em * en * ek / us / 1e6 / NOMINAL_FP8_TFLOPS, 3),
-                "rotating_copies": copies,
-            }
+            tf = 2.0 * em * en * ek / us / 1e6
+            row = {"us": round(us, 2), "bound": bound}
+            if bound == "hbm":
+                row["gbs"] = round(by / us / 1e3, 0)
+                row["frac"] = round(by / us / 1e3 / peaks["hbm_gbs"], 3)
+            else:
+                row["tflops"] = round(tf, 0)
+                row["frac"] = round(tf / fp8_peak, 3)
+                row["frac_nominal"] = round(tf / NOMINAL_FP8_TFLOPS, 3)
+            if static_too:
+                us2, _ = time_config(em, en, ek, edt, dev, iters=iters, hint=PDLW, seed=eseed, weight_scale=ews)
+                row["us_weights_static"] = round(us2, 2)
+                row["frac_weights_static"] = round(by / us2 / 1e3 / peaks["hbm_gbs"], 3)
+            configs[name] = row
+            torch.cuda.empty_cache()
+        roofline["configs"] = configs
+        roofline["configs_note"] = (f"hbm rows: algorithmic bytes / time over the measured copy bandwidth {peaks['hbm_gbs']} GB/s; "
+                                    f"tensor rows: over {fp8_peak:.0f} TFLOP/s (2 x measured bf16) and over nominal 4500; CUDA events "
+                                    "around a graph replay, operand copies rotated past L2, seeded N(0,1) inputs quantised per "
+                                    "token / per channel; *_weights_static = builder kwarg weights_static=True")
+        lib_fp8 = {}
+        for name, em, en, ek, ews, eseed in (("c3_8192x28672x8192", 8192, 28672, 8192, 0.02, 1003),
+                                            ("c5_16384x57344x8192", m, n, k, wscale, seed)):
+            us, mode = time_scaled_mm(em, en, ek, dev, iters=5, seed=eseed, weight_scale=ews)
+            lib_fp8[name] = ({"tflops": round(2.0 * em * en * ek / us / 1e6, 0), "us": round(us, 1), "scaling": mode}
+                             if us else {"unavailable": mode})
+            torch.cuda.empty_cache()
+        roofline["cublaslt_fp8_tflops"] = lib_fp8
         # the MXFP8 block-scaled GEMM on the prefill shape of configuration 3 (halved N to bound the run)
         extras["mxfp8_8192x14336x8192"] = time_mx(8192, 14336, 8192, dev, iters=5)
         # ... and on the reference's own MXFP8 test shapes (tests/kernels/test_preshuffle_gemm.py:590-598)
@@ -630,9 +765,12 @@ def main():
             "l2": "operands per GPU exceed L2 (126 MB); no flush needed",
             "per_gpu_tflops": value / world,
             "per_gpu_frac_of_nominal_fp8_4500": value / world / NOMINAL_FP8_TFLOPS,
+            "variant_hint": args.hint,
+            "parity_check": parity,
         },
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms, "steps": e2e_steps},
+                "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "note": "bytes per rank; on several GPUs a rank uploads 1/world of the activations and NCCL all-gathers them"},
         "gpu_launches": args.steps,
         "clocks": clocks,
         "roofline": roofline,
@@ -649,6 +787,8 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -1,7 +1,7 @@
 """Run one GEMM configuration a few times and print its device time.
 
-    python -m flydsl_b200.run_case --m 32 --n 8192 --k 8192 --dtype int8 [--iters 5] [--hint 0]
-    python -m flydsl_b200.run_case --op moe1 --m 4096 --n 2048 --k 4096 --experts 8 --topk 2 --tile-m 128
+    python bench_case.py --m 32 --n 8192 --k 8192 --dtype int8 [--iters 5] [--hint 0]
+    python bench_case.py --op moe1 --m 4096 --n 2048 --k 4096 --experts 8 --topk 2 --tile-m 128
 
 A small, self-contained driver for profilers (one kernel per iteration, random
 operands generated on the GPU, no host reference).
@@ -11,14 +11,20 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
+import sys
 
 import torch
 
-from . import _lib, compile_preshuffle_gemm, shuffle_weight
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from flydsl_b200 import _lib, compile_preshuffle_gemm, shuffle_weight  # noqa: E402
 
 
 def run_moe(a, dev):
-    from .kernels.moe.moe_gemm_2stage import compile_moe_gemm1, compile_moe_gemm2, moe_sorting
+    from flydsl_b200.kernels.moe.moe_gemm_2stage import compile_moe_gemm1, compile_moe_gemm2, moe_sorting
 
     tokens, inter, model, e, topk = a.m, a.n, a.k, a.experts, a.topk
     qd = torch.float8_e4m3fn if a.dtype == "fp8" else torch.int8
@@ -63,7 +69,7 @@ def run_moe(a, dev):
 
 
 def run_mx(a, dev):
-    from .kernels.gemm.mxfp8_preshuffle import compile_mxfp8_preshuffle_gemm, shuffle_scale
+    from flydsl_b200.kernels.gemm.mxfp8_preshuffle import compile_mxfp8_preshuffle_gemm, shuffle_scale
 
     m, n, k = a.m, a.n, a.k
     x = (torch.randn(m, k, device=dev) * 64).clamp_(-448, 448).to(torch.float8_e4m3fn)
@@ -109,7 +115,7 @@ def main():
     if a.op == "mx":
         return run_mx(a, dev)
     if a.op != "gemm":
-        from .utils import pertoken_quant_kernel
+        from flydsl_b200.utils import pertoken_quant_kernel
 
         if a.op == "quant":
             x = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16)

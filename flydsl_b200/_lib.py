@@ -108,8 +108,21 @@ def describe_plan(m: int, n: int, k: int, in_dtype: str = "fp8", variant_hint: i
     return dict(zip(PLAN_FIELDS, list(out)))
 
 
+_failure_hooks: list = []
+
+
+def on_failure_status(fn) -> None:
+    """Register a callback run whenever :func:`read_status` finds a failure recorded by a kernel."""
+    _failure_hooks.append(fn)
+
+
 def read_status() -> int:
-    """Synchronise the current device and return (and clear) its status word."""
+    """Synchronise the current device and return (and clear) its status word.
+    A non-zero status means a kernel gave up on a bounded wait; state that such
+    a kernel may have left half-updated (split-K arrival counters) is reset."""
     out = _i(0)
     check(load().flyb200_read_status(ctypes.byref(out)), "read_status")
+    if out.value != 0:
+        for fn in _failure_hooks:
+            fn()
     return out.value

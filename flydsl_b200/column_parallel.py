@@ -15,7 +15,8 @@ tests/kernels/test_allreduce.py:267,629-644.
 
 from __future__ import annotations
 
-import datetime
+import contextlib
+import os
 from dataclasses import dataclass
 
 import torch
@@ -89,11 +90,79 @@ def gather_columns(local: torch.Tensor, world: int, group=None, row_major: bool 
     return out.permute(1, 0, 2).reshape(m, world * nl)
 
 
+def _parse_cpulist(text: str) -> list[int]:
+    cpus: list[int] = []
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.extend(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def numa_cpus_of_pci_device(pci_address: str, sysfs_root: str = "/sys") -> list[int]:
+    """CPUs of the NUMA node a PCI device (``dddd:bb:dd.f``) hangs off, read from
+    sysfs; empty when the node is unknown (-1) or sysfs is not there."""
+    try:
+        with open(os.path.join(sysfs_root, "bus/pci/devices", pci_address.lower(), "numa_node")) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return []
+        with open(os.path.join(sysfs_root, "devices/system/node", f"node{node}", "cpulist")) as f:
+            return _parse_cpulist(f.read())
+    except (OSError, ValueError):
+        return []
+
+
+@contextlib.contextmanager
+def near_device(device: torch.device, sysfs_root: str = "/sys"):
+    """Run the body on the CPUs next to ``device``: pinned host buffers allocated
+    (and first touched) inside land on the GPU's own NUMA node, so the copies of
+    the eight GPUs of a two-socket machine do not all cross to one socket.  Best
+    effort: without the information, or when the process may not use those CPUs,
+    nothing changes."""
+    old = None
+    try:
+        props = torch.cuda.get_device_properties(device)
+        addr = f"{getattr(props, 'pci_domain_id', 0):04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        cpus = set(numa_cpus_of_pci_device(addr, sysfs_root)) & set(os.sched_getaffinity(0))
+        if cpus:
+            old = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, cpus)
+    except (AttributeError, OSError, RuntimeError):
+        old = None
+    try:
+        yield
+    finally:
+        if old is not None:
+            try:
+                os.sched_setaffinity(0, old)
+            except OSError:
+                pass
+
+
+def pinned_near(device: torch.device, shape, dtype) -> torch.Tensor:
+    """A pinned host tensor whose pages sit on the NUMA node of ``device``."""
+    with near_device(device):
+        t = torch.empty(shape, dtype=dtype).pin_memory()
+        t.view(torch.uint8).zero_()  # first touch
+    return t
+
+
+def row_shard(m: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [r0, r1) of an M-row matrix that rank ``rank`` uploads when the rows
+    are split evenly (M must be a multiple of ``world``)."""
+    if m % world != 0:
+        raise ValueError(f"M={m} is not a multiple of the group size {world}")
+    per = m // world
+    return rank * per, (rank + 1) * per
+
+
 class ColumnParallelGemm:
     """One rank's share of C = A . W^T split on the output channels."""
 
     def __init__(self, N: int, K: int, in_dtype: str = "fp8", out_dtype: str = "bf16", group=None, cpu_group=None,
-                 rank: int | None = None, world: int | None = None):
+                 rank: int | None = None, world: int | None = None, variant_hint: int = 0):
         from .kernels.gemm.preshuffle_gemm import compile_preshuffle_gemm
 
         self.group = group
@@ -107,7 +176,8 @@ class ColumnParallelGemm:
                 group=cpu_group if cpu_group is not None else group,
             )
         self.launch = compile_preshuffle_gemm(
-            N=self.spec.n_local, K=K, tile_m=128, tile_n=256, tile_k=128, in_dtype=in_dtype, out_dtype=out_dtype
+            N=self.spec.n_local, K=K, tile_m=128, tile_n=256, tile_k=128, in_dtype=in_dtype, out_dtype=out_dtype,
+            variant_hint=variant_hint,
         )
         self.w_shuf = None
         self.sb = None
@@ -137,12 +207,20 @@ class ColumnParallelGemm:
         return out
 
     # ---- host buffers in, host buffer out ---------------------------------------
-    def forward_host(self, a_host: torch.Tensor, sa_host: torch.Tensor, out_host: torch.Tensor, chunks: int = 8):
+    def forward_host(self, a_host: torch.Tensor, sa_host: torch.Tensor, out_host: torch.Tensor, chunks: int = 8,
+                     shard_upload: bool | None = None):
         """This rank's shard computed from pinned HOST activations into a pinned
-        HOST output, with the three legs pipelined over row blocks: while block i
-        is multiplied, block i+1 is uploaded and block i-1 downloaded (separate
-        streams; PCIe is full duplex).  Returns after enqueueing; the caller
-        synchronises ``torch.cuda.current_stream()``."""
+        HOST output, with the legs pipelined over row blocks: while block i is
+        multiplied, block i+1 is uploaded and block i-1 downloaded (separate
+        streams; PCIe is full duplex).
+
+        In a group of several GPUs every rank needs all of A.  With
+        ``shard_upload`` (default whenever the group has more than one rank and
+        the block size divides evenly) a rank uploads only ITS 1/world of each
+        row block over PCIe and the ranks exchange the pieces with an NCCL
+        all-gather over NVLink, so the host side sees A once per step instead of
+        once per GPU.  Returns after enqueueing; the caller synchronises
+        ``torch.cuda.current_stream()``."""
         m = a_host.shape[0]
         dev = self.w_shuf.device
         if getattr(self, "_host_state", None) is None or self._host_state[0] < m:
@@ -154,13 +232,28 @@ class ColumnParallelGemm:
         cur = torch.cuda.current_stream(dev)
         s_in.wait_stream(cur)
         s_out.wait_stream(cur)
+        w = self.world
         rows = max(128, ((m + chunks - 1) // chunks + 127) // 128 * 128)
+        if shard_upload is None:
+            shard_upload = w > 1 and dist.is_initialized()
+        if shard_upload and (rows % w != 0 or m % rows != 0):
+            shard_upload = False  # ragged blocks: every rank uploads everything
+        self.last_h2d_bytes = 0
         with torch.cuda.stream(s_in):
             sa_dev[:m].copy_(sa_host.view(-1)[:m], non_blocking=True)
+        self.last_h2d_bytes += m * 4
         for r0 in range(0, m, rows):
             r1 = min(m, r0 + rows)
             with torch.cuda.stream(s_in):
-                a_dev[r0:r1].copy_(a_host[r0:r1], non_blocking=True)
+                if shard_upload:
+                    p0, p1 = row_shard(r1 - r0, w, self.rank)
+                    a_dev[r0 + p0 : r0 + p1].copy_(a_host[r0 + p0 : r0 + p1], non_blocking=True)
+                    self.last_h2d_bytes += (p1 - p0) * a_host.shape[1] * a_host.element_size()
+                    # in place: rank r's piece already sits at its position in the block
+                    dist.all_gather_into_tensor(a_dev[r0:r1], a_dev[r0 + p0 : r0 + p1], group=self.group)
+                else:
+                    a_dev[r0:r1].copy_(a_host[r0:r1], non_blocking=True)
+                    self.last_h2d_bytes += (r1 - r0) * a_host.shape[1] * a_host.element_size()
                 ready = torch.cuda.Event()
                 ready.record(s_in)
             cur.wait_event(ready)
@@ -202,9 +295,13 @@ class ColumnParallelGemm:
         """Full [M, N] output on every rank from ONE GEMM kernel per rank: each
         output tile is TMA-stored into the full-width buffer of every rank
         (columns [rank*N/w, (rank+1)*N/w)), so the exchange over NVLink overlaps
-        the math; a one-element NCCL all-reduce then orders the stores against
-        the readers.  The two output buffers alternate between calls, so the
-        result of call i stays valid until call i+2 is issued."""
+        the math; a one-element NCCL all-reduce on the SAME stream then orders
+        the stores against the readers.  The returned tensor is valid for work
+        enqueued on that stream (or ordered after it) until this rank issues
+        its NEXT call: the two buffers alternate only so that a peer that is one
+        call ahead never writes into the buffer this rank is still reading
+        (a peer cannot pass the all-reduce of call i+1 before this rank has
+        issued call i+1, and call i+2 is the first that reuses call i's buffer)."""
         from . import _lib
 
         m = a_q.shape[0]
@@ -224,7 +321,9 @@ class ColumnParallelGemm:
         )  # fmt: skip
         _lib.check(rc, "gemm_a8w8_scatter")
         if self.world > 1:
-            dist.all_reduce(self._flag, group=self.group)  # all ranks' stores have landed before anyone reads
+            # all ranks' stores have landed before anyone reads; issued on the kernel's stream
+            with torch.cuda.stream(s):
+                dist.all_reduce(self._flag, group=self.group)
         return buf[:m]
 
     def forward_full(self, a_q, sa, row_major: bool = True):

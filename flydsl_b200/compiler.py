@@ -26,6 +26,7 @@ def compile(launch_fn, *args, **kwargs):  # noqa: A001 - name fixed by the refer
         if int(n) != launch_fn.N:
             raise ValueError(f"N passed to compile ({n}) differs from the N the launcher was built for ({launch_fn.N})")
         check(c, a, b, sa, sb, bias, int(m))
+        launch_fn.prepare(c.device, args[8] if len(args) > 8 else None)  # scratch allocated here, never at call time
     from .kernels.gemm.preshuffle_gemm import CompiledPreshuffleGemm
 
     return CompiledPreshuffleGemm(launch_fn)

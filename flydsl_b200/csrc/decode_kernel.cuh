@@ -242,6 +242,17 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
     // below overlap with these loads.
     const uint64_t pol_w = l2_policy_evict_first();
     const uint64_t pol_a = l2_policy_evict_last();
+    // Ask for this CTA's weights (the first p.prefetch k-blocks of its K range)
+    // to be brought into L2 right away - also before the previous kernel on the
+    // stream has completed: a prefetch reads nothing into the SM, and L2 is where
+    // all writes of the GPU meet, so the loads issued after the wait below see
+    // current data whatever that kernel still writes.  The DRAM latency is then
+    // covered by L2, not by the depth of the shared-memory ring, which can be
+    // shallow enough for two CTAs per SM: the next launch's CTAs are resident
+    // (and their weights on the way) while this launch finishes.
+    const int ahead = min(p.prefetch, num_kb);
+    for (int i = 0; i < ahead; ++i)
+      bulk_prefetch_l2(p.w + (static_cast<size_t>(kb_begin + i) * p.N + n0) * KBLOCK_BYTES, w_bytes);
     if (p.pdl == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < pre; ++i) {
       mbar_expect_tx(bar_full + 8 * i, A_STAGE + w_bytes + SF_BYTES);
@@ -287,7 +298,10 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
       int stage = pre == stages ? 0 : pre;
       uint32_t phase = pre == stages ? 1u : 0u;
       int issued = pre;
+      const int ahead = min(p.prefetch, num_kb);
       for (int kb = kb_begin + pre; kb < kb_end; ++kb) {
+        if (kb - pre + ahead < kb_end)  // the next block not yet asked for
+          bulk_prefetch_l2(p.w + (static_cast<size_t>(kb - pre + ahead) * p.N + n0) * KBLOCK_BYTES, w_bytes);
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
           report_failure(p.status, ST_TIMEOUT, abort_flag);
           ok = false;

@@ -2,10 +2,8 @@
 // checks, tensor-map encoding, kernel selection and launch.  No allocation, no
 // synchronisation and no memcpy on the launch path.
 #include "../../include/flyb200.h"
-#include "decode_kernel.cuh"
-#include "host_common.h"
+#include "launch.h"
 #include "quant_kernel.cuh"
-#include "rows2_kernel.cuh"
 
 #include <atomic>
 #include <cstdio>
@@ -14,6 +12,9 @@
 #include <mutex>
 
 using namespace flyb200;
+using flyb200::host::MAX_DEVICES;
+using flyb200::host::SMEM_LIMIT;
+using flyb200::host::ROWS2_STAGES;
 
 namespace {
 
@@ -32,7 +33,6 @@ int cuda_fail(cudaError_t e, const char* what) {
 // Device status word: kernels record the first failed bounded wait here.
 __device__ int g_status_word = 0;
 
-constexpr int MAX_DEVICES = 64;
 struct DeviceState {
   std::once_flag once;
   int sms = 0;
@@ -94,41 +94,13 @@ int make_map(CUtensorMap* m, CUtensorMapDataType dt, int elem_bytes, const void*
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int kind_of(int in_dtype) {
+  return in_dtype == FLYB200_DT_FP8 ? KIND_F8 : in_dtype == FLYB200_DT_INT8 ? KIND_I8 : in_dtype == FLYB200_DT_FP16 ? KIND_F16 : KIND_BF16;
+}
 inline int elem_bytes_of(int in_dtype) { return (in_dtype == FLYB200_DT_FP8 || in_dtype == FLYB200_DT_INT8) ? 1 : 2; }
 
-// One-time (per device) opt-in to large dynamic shared memory for a kernel.
-template <typename KernelT>
-int ensure_smem(KernelT kernel, int bytes, std::atomic<uint64_t>& done) {
-  int dev = 0;
-  CUDA_TRY(cudaGetDevice(&dev));
-  const uint64_t bit = 1ull << dev;
-  if (done.load(std::memory_order_acquire) & bit) return FLYB200_OK;
-  CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  done.fetch_or(bit, std::memory_order_release);
-  return FLYB200_OK;
-}
-
-// ---------------------------------------------------------------------------
-// kernel launch helpers
-// ---------------------------------------------------------------------------
-constexpr int ROWS_BN = 256;
-constexpr int ROWS_STAGES = 4;
 constexpr size_t TICKET_BYTES = 16384;  // 4096 channel tiles
 constexpr int MAX_SPLIT_K = 32;
-
-template <int KIND, int OUTMODE>
-int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams& p, int sms, cudaStream_t s) {
-  using L = RowsSmem<ROWS_BN, ROWS_STAGES>;
-  static std::atomic<uint64_t> done{0};
-  auto kernel = gemm_rows_kernel<KIND, ROWS_BN, ROWS_STAGES, OUTMODE>;
-  int rc = ensure_smem(kernel, L::TOTAL, done);
-  if (rc) return rc;
-  const int tiles = ((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * ((p.N + ROWS_BN - 1) / ROWS_BN);
-  const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, NUM_THREADS, L::TOTAL, s>>>(tmA, tmC, p);
-  CUDA_TRY(cudaGetLastError());
-  return FLYB200_OK;
-}
 
 // The preshuffled weights as a 3-D tensor {128 bytes, N rows, K/128 k-blocks}; boxes of
 // 128 rows x one k-block are copied verbatim (the image is already swizzled).
@@ -150,45 +122,6 @@ int make_weight_map(CUtensorMap* m, const void* base, uint64_t n_rows, uint64_t 
              static_cast<int>(r));
     return FLYB200_E_CUDA;
   }
-  return FLYB200_OK;
-}
-
-constexpr int ROWS2_STAGES = 6;
-
-template <int KIND, int OUTMODE>
-int launch_rows2(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmC, const GemmParams& p, int sms,
-                 cudaStream_t s) {
-  using L = Rows2Smem<ROWS2_STAGES>;
-  static std::atomic<uint64_t> done{0};
-  static int max_clusters[MAX_DEVICES] = {0};
-  auto kernel = gemm_rows2_kernel<KIND, ROWS2_STAGES, OUTMODE>;
-  int rc = ensure_smem(kernel, L::TOTAL, done);
-  if (rc) return rc;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = L::TOTAL;
-  cfg.stream = s;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  int dev = 0;
-  CUDA_TRY(cudaGetDevice(&dev));
-  if (max_clusters[dev] == 0) {
-    cfg.gridDim = dim3(sms & ~1, 1, 1);
-    int n = 0;
-    CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
-    if (n < 1) return FLYB200_E_UNSUPPORTED;
-    max_clusters[dev] = n;
-  }
-  const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
-  const int clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
-  cfg.gridDim = dim3(2 * clusters, 1, 1);
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmA, tmW, tmC, p));
   return FLYB200_OK;
 }
 
@@ -215,95 +148,12 @@ int make_window_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, ui
   return FLYB200_OK;
 }
 
-template <int KIND, int OUTMODE>
-int launch_rows_scatter(const CUtensorMap& tmA, const OutputMaps& outs, const GemmParams& p, int sms, cudaStream_t s) {
-  using L = RowsSmem<ROWS_BN, ROWS_STAGES>;
-  static std::atomic<uint64_t> done{0};
-  auto kernel = gemm_rows_scatter_kernel<KIND, ROWS_BN, ROWS_STAGES, OUTMODE>;
-  int rc = ensure_smem(kernel, L::TOTAL, done);
-  if (rc) return rc;
-  const int tiles = ((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * ((p.N + ROWS_BN - 1) / ROWS_BN);
-  const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, NUM_THREADS, L::TOTAL, s>>>(tmA, outs, p);
-  CUDA_TRY(cudaGetLastError());
-  return FLYB200_OK;
-}
-
-constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
-
 // Ring depth of the small-M kernel: as deep as ~200 KB of shared memory allow, at most 12.
 inline int default_decode_stages(int bn, int w_rows = BLOCK_ROWS) {
   if (w_rows == BLOCK_ROWS) return bn <= 32 ? 8 : (bn <= 128 ? 6 : 4);
   const int stage = (w_rows + bn) * KBLOCK_BYTES;
   int n = 200 * 1024 / stage;
   return n > 12 ? 12 : (n < 2 ? 2 : n);
-}
-
-template <int KIND, int BN, int OUTMODE, int WROWS = BLOCK_ROWS>
-int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
-  static std::atomic<uint64_t> done{0};
-  auto kernel = gemm_decode_kernel<KIND, BN, OUTMODE, WROWS>;
-  int rc = ensure_smem(kernel, SMEM_LIMIT, done);
-  if (rc) return rc;
-  const DecodeLayout L = decode_layout(BN, p.stages, WROWS, KIND == KIND_MXF8);
-  if (L.total > SMEM_LIMIT || BN * BLOCK_ROWS * 4 > L.off_bar) return FLYB200_E_UNSUPPORTED;
-  if (KIND == KIND_MXF8 && p.stages > 8) return FLYB200_E_UNSUPPORTED;  // scale columns in TMEM for 8 stages
-  if (WROWS != BLOCK_ROWS && p.reduce_mode != REDUCE_NONE) return FLYB200_E_UNSUPPORTED;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((p.N + WROWS - 1) / WROWS, p.split_k, p.token_blocks < 1 ? 1 : p.token_blocks);
-  cfg.blockDim = dim3(DECODE_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = L.total;
-  cfg.stream = s;
-  cudaLaunchAttribute attrs[2];
-  int na = 0;
-  if (p.reduce_mode == REDUCE_CLUSTER) {
-    attrs[na].id = cudaLaunchAttributeClusterDimension;
-    attrs[na].val.clusterDim.x = 1;
-    attrs[na].val.clusterDim.y = p.split_k;
-    attrs[na].val.clusterDim.z = 1;
-    ++na;
-  }
-  if (p.pdl) {
-    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attrs[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
-  }
-  cfg.attrs = attrs;
-  cfg.numAttrs = na;
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmA, p));
-  return FLYB200_OK;
-}
-
-template <int KIND, int OUTMODE>
-int launch_decode_bn(int bn, int w_rows, const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
-  if constexpr (KIND == KIND_MXF8) {  // block-scaled kind: 128-channel tiles, up to 128 tokens
-    if (w_rows != BLOCK_ROWS) return FLYB200_E_UNSUPPORTED;
-    switch (bn) {
-      case 16: return launch_decode<KIND, 16, OUTMODE>(tmA, p, s);
-      case 32: return launch_decode<KIND, 32, OUTMODE>(tmA, p, s);
-      case 64: return launch_decode<KIND, 64, OUTMODE>(tmA, p, s);
-      case 128: return launch_decode<KIND, 128, OUTMODE>(tmA, p, s);
-    }
-    return FLYB200_E_UNSUPPORTED;
-  } else {
-  if (w_rows == 64) {  // half-height weight tiles: built for the token counts where they pay off
-    switch (bn) {
-      case 16: return launch_decode<KIND, 16, OUTMODE, 64>(tmA, p, s);
-      case 32: return launch_decode<KIND, 32, OUTMODE, 64>(tmA, p, s);
-      case 64: return launch_decode<KIND, 64, OUTMODE, 64>(tmA, p, s);
-    }
-    return FLYB200_E_UNSUPPORTED;
-  }
-  switch (bn) {
-    case 16: return launch_decode<KIND, 16, OUTMODE>(tmA, p, s);
-    case 32: return launch_decode<KIND, 32, OUTMODE>(tmA, p, s);
-    case 64: return launch_decode<KIND, 64, OUTMODE>(tmA, p, s);
-    case 128: return launch_decode<KIND, 128, OUTMODE>(tmA, p, s);
-    case 256: return launch_decode<KIND, 256, OUTMODE>(tmA, p, s);
-  }
-  return FLYB200_E_UNSUPPORTED;
-  }
 }
 
 inline int decode_bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
@@ -338,6 +188,7 @@ struct Plan {
   int reduce_mode;
   int stages;
   int pdl;
+  int prefetch;  // k-blocks of weights requested into L2 ahead of the ring
 };
 
 // 0 = off, 1 = on, 2 = on and the weights are known to be static
@@ -392,6 +243,38 @@ bool workspace_fits(bool have_ws, size_t ws_bytes, int split, int N, int bn, int
 // automatic choice is one block and the split stays a tuning option.
 int auto_token_blocks(int /*M*/, int /*N*/, int /*sms*/) { return 1; }
 
+// Tile width of the large-M kernel when the caller does not force one.  All
+// tiles are 128 tokens high; the kernel is persistent, so a launch takes
+// ceil(tiles / SMs) rounds of one tile per SM.  Per 128-byte k-block a tile
+// costs the largest of: the tensor pipe (2 * bn cycles), the single thread
+// that issues the MMAs (ROWS_ISSUE_CYCLES), and bringing the operands into
+// shared memory ((16 KiB + bn * 128 B) / ROWS_LOAD_BYTES_PER_CYCLE).  The
+// width with the cheapest whole launch wins; ties go to the wider tile (fewer
+// operand bytes per flop).
+constexpr int ROWS_ISSUE_CYCLES = 300;
+constexpr int ROWS_LOAD_BYTES_PER_CYCLE = 96;
+constexpr int ROWS_TILE_OVERHEAD_CYCLES = 2000;  // pipeline fill and the last, exposed epilogue of a CTA
+int auto_rows_bn(int M, int N, int K_bytes, int sms) {
+  const long long num_m = (M + BLOCK_ROWS - 1) / BLOCK_ROWS;
+  const long long kb = K_bytes / KBLOCK_BYTES;
+  long long best_cost = -1;
+  int best = 256;
+  for (int bn = 256; bn >= 64; bn -= 32) {
+    const long long tiles = num_m * ((N + bn - 1) / bn);
+    const long long rounds = (tiles + sms - 1) / sms;
+    long long per_kb = 2 * bn;
+    if (per_kb < ROWS_ISSUE_CYCLES) per_kb = ROWS_ISSUE_CYCLES;
+    const long long load = (BLOCK_ROWS * KBLOCK_BYTES + bn * KBLOCK_BYTES) / ROWS_LOAD_BYTES_PER_CYCLE;
+    if (per_kb < load) per_kb = load;
+    const long long cost = rounds * (kb * per_kb + 4 * bn) + ROWS_TILE_OVERHEAD_CYCLES;
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
 int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t workspace_bytes, bool have_ws, int sms) {
   const int want_kernel = hint_kernel(variant_hint);
   const int want_split = hint_split(variant_hint);
@@ -402,8 +285,18 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   if (plan->decode && M > 256) return FLYB200_E_UNSUPPORTED;
   if (want_reduce > REDUCE_CLUSTER) return FLYB200_E_BAD_ARG;
   plan->token_blocks = 1;
-  plan->bn = ROWS_BN;
   plan->w_rows = BLOCK_ROWS;
+  if (!plan->decode) {
+    // large-M kernel: the split field carries the tile width in units of 32 channels
+    if (plan->two_sm) {
+      plan->bn = 256;
+    } else if (want_split > 0) {
+      if (want_split > 8) return FLYB200_E_BAD_ARG;
+      plan->bn = 32 * want_split;
+    } else {
+      plan->bn = auto_rows_bn(M, N, K_bytes, sms);
+    }
+  }
   if (plan->decode) {
     const int ht = hint_tokens(variant_hint);
     int t = ht == 0 ? auto_token_blocks(M, N, sms) : (ht == 1 ? 1 : ht == 2 ? 2 : 4);
@@ -432,6 +325,10 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   // one below when that does not fit into shared memory.
   if (plan->stages & 1) {
     plan->stages += decode_layout(plan->bn, plan->stages + 1, plan->w_rows).total <= SMEM_LIMIT ? 1 : -1;
+  }
+  {
+    const char* e = getenv(plan->decode ? "FLYB200_PREFETCH_DECODE" : "FLYB200_PREFETCH_ROWS");
+    plan->prefetch = e ? atoi(e) : (plan->decode ? 64 : 0);
   }
   const int hp = hint_pdl(variant_hint);
   plan->pdl = hp == 1 ? 1 : hp == 2 ? 0 : hp == 3 ? 2 : pdl_default();
@@ -462,14 +359,6 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   return FLYB200_OK;
 }
 
-template <int KIND, int OUTMODE>
-int run_kind(const Plan& plan, const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmC,
-             const GemmParams& p, int sms, cudaStream_t s) {
-  if (plan.decode) return launch_decode_bn<KIND, OUTMODE>(plan.bn, plan.w_rows, tmA, p, s);
-  if (plan.two_sm) return launch_rows2<KIND, OUTMODE>(tmA, tmW, tmC, p, sms, s);
-  return launch_rows<KIND, OUTMODE>(tmA, tmC, p, sms, s);
-}
-
 int gemm_common(void* c, const void* a, const void* w, const float* sa, const float* sb, const void* bias, int M,
                 int N, int K, int in_dtype, int outmode, int epilogue, int variant_hint, void* workspace,
                 size_t workspace_bytes, void* stream) {
@@ -497,6 +386,7 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
   if (rc) return rc;
 
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.w = static_cast<const uint8_t*>(w);
   p.sa = sa;
   p.sb = sb;
@@ -512,7 +402,10 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
   p.reduce_mode = plan.reduce_mode;
   p.stages = plan.stages;
   p.pdl = plan.pdl;
+  p.prefetch = plan.prefetch;
   p.token_blocks = plan.token_blocks;
+  p.bn = plan.bn;
+  p.rows_stages = host::rows_stages_for(plan.bn);
   p.ws_tickets = static_cast<int*>(workspace);
   p.ws_partials = workspace ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + TICKET_BYTES) : nullptr;
   p.status = st->status;
@@ -534,23 +427,9 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
   }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (in_dtype) {
-    case FLYB200_DT_FP8:
-      if (outmode == OUT_BF16) return run_kind<KIND_F8, OUT_BF16>(plan, tmA, tmW, tmC, p, st->sms, s);
-      if (outmode == OUT_FP16) return run_kind<KIND_F8, OUT_FP16>(plan, tmA, tmW, tmC, p, st->sms, s);
-      return run_kind<KIND_F8, OUT_RAW32>(plan, tmA, tmW, tmC, p, st->sms, s);
-    case FLYB200_DT_INT8:
-      if (outmode == OUT_BF16) return run_kind<KIND_I8, OUT_BF16>(plan, tmA, tmW, tmC, p, st->sms, s);
-      if (outmode == OUT_FP16) return run_kind<KIND_I8, OUT_FP16>(plan, tmA, tmW, tmC, p, st->sms, s);
-      return run_kind<KIND_I8, OUT_RAW32>(plan, tmA, tmW, tmC, p, st->sms, s);
-    case FLYB200_DT_FP16:
-      if (outmode == OUT_BF16) return run_kind<KIND_F16, OUT_BF16>(plan, tmA, tmW, tmC, p, st->sms, s);
-      return run_kind<KIND_F16, OUT_FP16>(plan, tmA, tmW, tmC, p, st->sms, s);
-    case FLYB200_DT_BF16:
-      if (outmode == OUT_BF16) return run_kind<KIND_BF16, OUT_BF16>(plan, tmA, tmW, tmC, p, st->sms, s);
-      return run_kind<KIND_BF16, OUT_FP16>(plan, tmA, tmW, tmC, p, st->sms, s);
-  }
-  return FLYB200_E_BAD_ARG;
+  const int kind = kind_of(in_dtype);
+  if (plan.decode) return host::launch_decode_kind(kind, outmode, plan.bn, plan.w_rows, tmA, p, s);
+  return host::launch_rows_kind(kind, outmode, plan.two_sm, tmA, tmW, tmC, p, st->sms, s);
 }
 
 // ---------------------------------------------------------------------------
@@ -708,6 +587,7 @@ int gemm_mx_small(void* c, const void* a, const void* w, const void* sf_a, const
   p.reduce_mode = plan.reduce_mode;
   p.stages = plan.stages > 8 ? 8 : plan.stages;
   p.pdl = plan.pdl;
+  p.prefetch = plan.prefetch;
   p.token_blocks = 1;
   p.sf_w = static_cast<const uint8_t*>(sf_w);
   p.sf_a = static_cast<const uint8_t*>(sf_a);
@@ -718,8 +598,7 @@ int gemm_mx_small(void* c, const void* a, const void* w, const void* sf_a, const
                 plan.bn);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (outmode == OUT_FP16) return launch_decode_bn<KIND_MXF8, OUT_FP16>(plan.bn, plan.w_rows, tmA, p, s);
-  return launch_decode_bn<KIND_MXF8, OUT_BF16>(plan.bn, plan.w_rows, tmA, p, s);
+  return host::launch_decode_kind(KIND_MXF8, outmode == OUT_FP16 ? OUT_FP16 : OUT_BF16, plan.bn, plan.w_rows, tmA, p, s);
 }
 int byte_matrix_map(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
   return make_map(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, row_bytes, rows, KBLOCK_BYTES, box_rows);
@@ -767,6 +646,11 @@ int flyb200_gemm_a8w8_static_scratch(void* c, const void* a, const void* w_shuf,
   if (M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
   if (M > 256) return FLYB200_E_UNSUPPORTED;  // only the small-M kernel has a split-K scratch
   if (!flyb200_layout_kind(N, K, eb)) return FLYB200_E_UNSUPPORTED;
+  // every check that can fail comes before the first write to the shared array
+  if (!c || !a || !w_shuf) return FLYB200_E_BAD_ARG;
+  if (epilogue < FLYB200_EPI_NONE || epilogue > FLYB200_EPI_BIAS_GELU) return FLYB200_E_BAD_ARG;
+  if (epilogue != FLYB200_EPI_NONE && !bias) return FLYB200_E_BAD_ARG;
+  if (!aligned16(c) || !aligned16(a) || !aligned16(w_shuf)) return FLYB200_E_BAD_ALIGN;
   if (M == 0) return FLYB200_OK;
 
   const int bn = decode_bn_for(M);
@@ -845,6 +729,8 @@ int flyb200_gemm_a8w8_scatter(void* const* c_bufs, int n_bufs, int first_buf, lo
   p.group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : 16;
   p.split_k = 1;
   p.kb_per_split = K_bytes / KBLOCK_BYTES;
+  p.bn = 256;
+  p.rows_stages = host::rows_stages_for(256);
   p.n_dst = n_bufs;
   p.dst_first = first_buf;
   p.status = st->status;
@@ -864,22 +750,8 @@ int flyb200_gemm_a8w8_scatter(void* const* c_bufs, int n_bufs, int first_buf, lo
     if (rc) return rc;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool f16out = out_dtype == FLYB200_OUT_FP16;
-  switch (in_dtype) {
-    case FLYB200_DT_FP8:
-      return f16out ? launch_rows_scatter<KIND_F8, OUT_FP16>(tmA, outs, p, st->sms, s)
-                    : launch_rows_scatter<KIND_F8, OUT_BF16>(tmA, outs, p, st->sms, s);
-    case FLYB200_DT_INT8:
-      return f16out ? launch_rows_scatter<KIND_I8, OUT_FP16>(tmA, outs, p, st->sms, s)
-                    : launch_rows_scatter<KIND_I8, OUT_BF16>(tmA, outs, p, st->sms, s);
-    case FLYB200_DT_FP16:
-      return f16out ? launch_rows_scatter<KIND_F16, OUT_FP16>(tmA, outs, p, st->sms, s)
-                    : launch_rows_scatter<KIND_F16, OUT_BF16>(tmA, outs, p, st->sms, s);
-    case FLYB200_DT_BF16:
-      return f16out ? launch_rows_scatter<KIND_BF16, OUT_FP16>(tmA, outs, p, st->sms, s)
-                    : launch_rows_scatter<KIND_BF16, OUT_BF16>(tmA, outs, p, st->sms, s);
-  }
-  return FLYB200_E_BAD_ARG;
+  return host::launch_rows_scatter_kind(kind_of(in_dtype), out_dtype == FLYB200_OUT_FP16 ? OUT_FP16 : OUT_BF16, tmA, outs, p,
+                                        st->sms, s);
 }
 
 int flyb200_shuffle_weight(void* dst, const void* src, int N, int K, int elem_bytes, int src_layout, void* stream) {
@@ -951,7 +823,7 @@ int flyb200_describe_plan(int M, int N, int K, int in_dtype, int variant_hint, i
   out8[2] = plan.split_k;
   out8[3] = plan.kb_per_split;
   out8[4] = plan.reduce_mode;
-  out8[5] = plan.decode ? plan.stages : (plan.two_sm ? ROWS2_STAGES : ROWS_STAGES);
+  out8[5] = plan.decode ? plan.stages : (plan.two_sm ? ROWS2_STAGES : host::rows_stages_for(plan.bn));
   out8[6] = plan.decode ? plan.pdl : 0;
   out8[7] = plan.token_blocks;
   return FLYB200_OK;

@@ -47,12 +47,15 @@ struct GemmParams {
   int reduce_mode;       // decode kernel: how the K splits are combined (REDUCE_*)
   int stages;            // decode kernel: depth of the shared-memory ring
   int pdl;               // decode kernel: launched with programmatic stream serialisation
+  int prefetch;          // k-blocks of weights requested into L2 ahead of the shared-memory ring (0 = none)
   float* ws_partials;    // decode kernel, REDUCE_WORKSPACE
   int* ws_tickets;       // decode kernel, REDUCE_WORKSPACE (zero before first use; self-resetting)
   int token_blocks;      // decode kernel: grid.z, blocks of BN tokens
   const uint8_t* sf_w;   // decode kernel, MX kind: scale image of the weights [K/128][N/128][512]
   const uint8_t* sf_a;   // decode kernel, MX kind: scale image of the activations [K/128][sf_a_tiles][512]
   int sf_a_tiles;        // ceil(M / 128)
+  int bn;                // large-M kernel: output channels per tile (multiple of 32, 32..256)
+  int rows_stages;       // large-M kernel: depth of the shared-memory ring
   int n_dst;             // scatter kernel: number of output buffers
   int dst_first;         // scatter kernel: buffer stored to first
   int* status;           // device status word (first failure wins)
@@ -153,10 +156,10 @@ __device__ __forceinline__ float load_bias(const void* bias, int col) {
 // of them (the caller's own output, or the same window of the output buffers of
 // several GPUs), starting with map `dst_first` so that ranks do not all hit the
 // same peer at the same time.
-template <int KIND, int BN, int OUTMODE, typename ReleaseFn>
+template <int KIND, int OUTMODE, typename ReleaseFn>
 __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* tmC, int n_dst, int dst_first,
-                                                   uint32_t t_row, int m0, int n0, int lane, uint32_t stage_c, int& cbuf,
-                                                   ReleaseFn release_tmem) {
+                                                   uint32_t t_row, int m0, int n0, int BN, int lane, uint32_t stage_c,
+                                                   int& cbuf, ReleaseFn release_tmem) {
   using KT = KindTraits<KIND>;
   constexpr int C_BUF = 32 * 128;
   const bool scaled = (p.sa != nullptr) && (p.sb != nullptr);
@@ -187,6 +190,36 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CU
   } else {
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 64) {
+      if (c0 + 64 > BN) {
+        // Last 32 columns of a tile whose width is not a multiple of 64: a
+        // 64-column TMA box would reach into the neighbouring tile, so these
+        // leave the registers directly (64 contiguous bytes per row).
+        uint32_t r[32];
+        tmem_ld_x32(t_row + c0, r);
+        tmem_ld_wait();
+        release_tmem();
+        if (row < p.M) {
+          uint16_t* out_row = reinterpret_cast<uint16_t*>(p.c) + static_cast<size_t>(row) * p.N;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            const int col = n0 + c0 + j;
+            if (col < p.N) {  // N is a multiple of 16: eight columns are in or out together
+              uint32_t pk[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int ce = col + 2 * e;
+                const float s0 = scaled ? __ldg(p.sb + ce) : 0.0f, s1 = scaled ? __ldg(p.sb + ce + 1) : 0.0f;
+                const float b0 = p.epilogue != EPI_NONE ? load_bias<OUTMODE>(p.bias, ce) : 0.0f;
+                const float b1 = p.epilogue != EPI_NONE ? load_bias<OUTMODE>(p.bias, ce + 1) : 0.0f;
+                pk[e] = pack2<OUTMODE>(epilogue_value<KT::is_int>(r[j + 2 * e], sa_v, s0, b0, p.epilogue, scaled),
+                                       epilogue_value<KT::is_int>(r[j + 2 * e + 1], sa_v, s1, b1, p.epilogue, scaled));
+              }
+              *reinterpret_cast<uint4*>(out_row + col) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
+        }
+        break;
+      }
       uint32_t r0[32], r1[32];
       tmem_ld_x32(t_row + c0, r0);
       tmem_ld_x32(t_row + c0 + 32, r1);
@@ -244,18 +277,24 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CU
 // ===========================================================================
 // Large-M kernel
 // ===========================================================================
-template <int BN, int STAGES>
-struct RowsSmem {
-  static constexpr int A_STAGE = BLOCK_ROWS * KBLOCK_BYTES;
-  static constexpr int B_STAGE = BN * KBLOCK_BYTES;
-  static constexpr int C_BUF = 32 * 128;                       // 32 rows x 64 two-byte columns
-  static constexpr int OFF_A = 0;
-  static constexpr int OFF_B = OFF_A + STAGES * A_STAGE;
-  static constexpr int OFF_C = OFF_B + STAGES * B_STAGE;       // 4 warps x 2 buffers
-  static constexpr int OFF_BAR = OFF_C + 4 * 2 * C_BUF;        // full[S], empty[S], tfull[2], tempty[2]
-  static constexpr int OFF_MISC = OFF_BAR + 8 * (2 * STAGES + 4);
-  static constexpr int TOTAL = OFF_MISC + 16;
+// Shared-memory carve-up of the large-M kernel for a tile width `bn` and a ring
+// depth `stages` (computed identically on host and device).
+struct RowsLayout {
+  int a_stage, b_stage, off_b, off_c, off_bar, off_misc, total;
 };
+constexpr int ROWS_C_BUF = 32 * 128;  // staging buffer: 32 rows x 64 two-byte columns
+constexpr int ROWS_ACC_COLS = 256;    // TMEM columns between the two accumulator buffers
+__host__ __device__ inline RowsLayout rows_layout(int bn, int stages) {
+  RowsLayout l;
+  l.a_stage = BLOCK_ROWS * KBLOCK_BYTES;
+  l.b_stage = bn * KBLOCK_BYTES;
+  l.off_b = stages * l.a_stage;
+  l.off_c = l.off_b + stages * l.b_stage;       // 4 warps x 2 buffers
+  l.off_bar = l.off_c + 4 * 2 * ROWS_C_BUF;     // full[S], empty[S], tfull[2], tempty[2]
+  l.off_misc = l.off_bar + 8 * (2 * stages + 4);
+  l.total = l.off_misc + 16;
+  return l;
+}
 
 constexpr int MAX_DESTINATIONS = 8;
 struct OutputMaps {
@@ -263,8 +302,10 @@ struct OutputMaps {
 };
 
 // Body shared by the two entry kernels below: `tmC` points to `n_dst` output
-// tensor maps (kernel parameters of the caller).
-template <int KIND, int BN, int STAGES, int OUTMODE>
+// tensor maps (kernel parameters of the caller).  The tile width (p.bn, a
+// multiple of 32 up to 256) and the ring depth (p.rows_stages) are run-time
+// values: the host picks the width that fills the SMs in whole waves.
+template <int KIND, int OUTMODE>
 __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUtensorMap* tmC_ptr, int n_dst,
                                                int dst_first, const GemmParams& p) {
   const CUtensorMap& tmC = *tmC_ptr;
@@ -272,16 +313,18 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
   long long prof_wait[4] = {0, 0, 0, 0};  // producer:empty, mma:tempty, mma:full, epilogue:tfull
   const long long prof_begin = clock64();
 #endif
-  using L = RowsSmem<BN, STAGES>;
   using KT = KindTraits<KIND>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = smem_u32(smem_raw);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L::OFF_MISC + 4);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L::OFF_MISC);
+  const int BN = p.bn;
+  const int STAGES = p.rows_stages;
+  const RowsLayout L = rows_layout(BN, STAGES);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L.off_misc + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L.off_misc);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint32_t bar_full = smem_base + L::OFF_BAR;
+  const uint32_t bar_full = smem_base + L.off_bar;
   const uint32_t bar_empty = bar_full + 8 * STAGES;
   const uint32_t bar_tfull = bar_empty + 8 * STAGES;
   const uint32_t bar_tempty = bar_tfull + 16;
@@ -308,8 +351,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
     prefetch_tensormap(&tmA);
     if (OUTMODE != OUT_RAW32) prefetch_tensormap(&tmC);
   }
-  constexpr uint32_t TMEM_COLS = 512;
-  static_assert(2 * BN <= 512, "two accumulator buffers must fit TMEM");
+  constexpr uint32_t TMEM_COLS = 512;  // two accumulator buffers of up to 256 columns
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
@@ -325,6 +367,11 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
   const int num_kb = p.K_bytes / KBLOCK_BYTES;
   const int gm_full = p.group_m;
 
+  // Tile order: groups of `group_m` row tiles; inside a group the row tile
+  // changes fastest and the channel tiles are walked once, so the group's
+  // activations stay in L2 while the weights stream through.  Odd groups walk
+  // the channels backwards: the weight tiles that the previous group touched
+  // last are the first ones the next group asks for.
   auto tile_coords = [&](int t, int& m_blk, int& n_blk) {
     const int per_group = gm_full * num_n;
     const int g = t / per_group;
@@ -333,6 +380,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
     const int r = t - g * per_group;
     m_blk = first_m + r % gm;
     n_blk = r / gm;
+    if (g & 1) n_blk = num_n - 1 - n_blk;
   };
 
   if (warp == 0) {
@@ -350,17 +398,24 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
         const int n0 = n_blk * BN;
         const uint32_t w_rows = static_cast<uint32_t>(min(BN, p.N - n0));
         const uint32_t w_bytes = w_rows * KBLOCK_BYTES;
+        // The ring holds a few k-blocks; the weights of the next `prefetch`
+        // k-blocks are already on their way from DRAM into L2, so the depth
+        // of the ring only has to cover the L2 latency.
+        const int ahead = min(p.prefetch, num_kb);
+        for (int kb = 0; kb < ahead; ++kb)
+          bulk_prefetch_l2(p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES, w_bytes);
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (kb + ahead < num_kb)
+            bulk_prefetch_l2(p.w + (static_cast<size_t>(kb + ahead) * p.N + n0) * KBLOCK_BYTES, w_bytes);
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag FLYB200_PROF_ARG(&prof_wait[0]))) {
             report_failure(p.status, ST_TIMEOUT, abort_flag);
             ok = false;
             break;
           }
           const uint32_t fb = bar_full + 8 * stage;
-          mbar_expect_tx(fb, L::A_STAGE + w_bytes);
-          tma_load_2d(smem_base + L::OFF_A + stage * L::A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, m_blk * BLOCK_ROWS,
-                      pol_a);
-          bulk_load_1d(smem_base + L::OFF_B + stage * L::B_STAGE,
+          mbar_expect_tx(fb, L.a_stage + w_bytes);
+          tma_load_2d(smem_base + stage * L.a_stage, &tmA, fb, kb * KBLOCK_BYTES, m_blk * BLOCK_ROWS, pol_a);
+          bulk_load_1d(smem_base + L.off_b + stage * L.b_stage,
                        p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES, w_bytes, fb, pol_w);
           ++issued;
           if (++stage == STAGES) {
@@ -387,7 +442,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
   } else if (warp == 1) {
     // ------------------------------ MMA issue -----------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, BLOCK_ROWS, BN);
+      const uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, BLOCK_ROWS, static_cast<uint32_t>(BN));
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -399,7 +454,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ROWS_ACC_COLS);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag FLYB200_PROF_ARG(&prof_wait[2]))) {
             report_failure(p.status, ST_TIMEOUT, abort_flag);
@@ -407,8 +462,8 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
             break;
           }
           tc_fence_after();
-          const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L::OFF_A + stage * L::A_STAGE);
-          const uint64_t bdesc = umma_desc_sw128_kmajor(smem_base + L::OFF_B + stage * L::B_STAGE);
+          const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + stage * L.a_stage);
+          const uint64_t bdesc = umma_desc_sw128_kmajor(smem_base + L.off_b + stage * L.b_stage);
 #pragma unroll
           for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
             umma_ss<KIND>(d_tmem, adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
@@ -430,7 +485,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int ew = warp - 2; // staging buffer owner
-    const uint32_t stage_c = smem_base + L::OFF_C + ew * 2 * L::C_BUF;
+    const uint32_t stage_c = smem_base + L.off_c + ew * 2 * ROWS_C_BUF;
     int acc = 0;
     uint32_t acc_phase = 0;
     int cbuf = 0;
@@ -446,8 +501,9 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
         break;
       }
       tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      epilogue_warp_tile<KIND, BN, OUTMODE>(p, tmC_ptr, n_dst, dst_first, t_row, m0, n0, lane, stage_c, cbuf, [&]() {
+      const uint32_t t_row =
+          tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * ROWS_ACC_COLS);
+      epilogue_warp_tile<KIND, OUTMODE>(p, tmC_ptr, n_dst, dst_first, t_row, m0, n0, BN, lane, stage_c, cbuf, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
@@ -483,22 +539,22 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
 }
 
 // One output buffer (the regular GEMM).
-template <int KIND, int BN, int STAGES, int OUTMODE>
+template <int KIND, int OUTMODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_rows_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC,
                  const GemmParams p) {
-  gemm_rows_body<KIND, BN, STAGES, OUTMODE>(tmA, &tmC, 1, 0, p);
+  gemm_rows_body<KIND, OUTMODE>(tmA, &tmC, 1, 0, p);
 }
 
 // Every output tile is stored into the same window of up to eight buffers, e.g.
 // the full-width output of each GPU of a column-parallel group (peer-mapped
 // memory; plain TMA stores, per CTA, no multicast): the all-gather of the
 // shards happens tile by tile inside the GEMM.
-template <int KIND, int BN, int STAGES, int OUTMODE>
+template <int KIND, int OUTMODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_rows_scatter_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ OutputMaps outs,
                          const GemmParams p) {
-  gemm_rows_body<KIND, BN, STAGES, OUTMODE>(tmA, outs.m, p.n_dst, p.dst_first, p);
+  gemm_rows_body<KIND, OUTMODE>(tmA, outs.m, p.n_dst, p.dst_first, p);
 }
 
 }  // namespace flyb200

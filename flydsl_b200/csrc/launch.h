@@ -1,0 +1,54 @@
+// Kernel launchers of libflyb200, one translation unit per kernel family so
+// that the families compile in parallel (not part of the C ABI).
+#pragma once
+#include "decode_kernel.cuh"
+#include "host_common.h"
+
+#include <atomic>
+
+namespace flyb200 {
+namespace host {
+
+constexpr int SMEM_LIMIT = 232448;  // 227 KiB of dynamic shared memory per CTA
+constexpr int MAX_DEVICES = 64;
+constexpr int ROWS_MAX_STAGES = 8;
+constexpr int ROWS2_STAGES = 6;
+
+#define FLYB200_CUDA_TRY(expr)                                                          \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess) return ::flyb200::host::record_cuda_error(_e, #expr);        \
+  } while (0)
+
+// One-time (per device) opt-in to large dynamic shared memory for a kernel.
+template <typename KernelT>
+int ensure_smem(KernelT kernel, int bytes, std::atomic<uint64_t>& done) {
+  int dev = 0;
+  FLYB200_CUDA_TRY(cudaGetDevice(&dev));
+  const uint64_t bit = 1ull << dev;
+  if (done.load(std::memory_order_acquire) & bit) return 0;
+  FLYB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  done.fetch_or(bit, std::memory_order_release);
+  return 0;
+}
+
+// Deepest ring (at most ROWS_MAX_STAGES) of the large-M kernel that fits shared memory for a tile width.
+inline int rows_stages_for(int bn) {
+  int s = ROWS_MAX_STAGES;
+  while (s > 2 && rows_layout(bn, s).total > SMEM_LIMIT) --s;
+  return s;
+}
+
+// Large-M kernel (p.bn, p.rows_stages set): one CTA per tile, or CTA pairs (`two_sm`, 256 x 256 tiles).
+// `kind` is KIND_*, `outmode` OUT_*.
+int launch_rows_kind(int kind, int outmode, bool two_sm, const CUtensorMap& tmA, const CUtensorMap& tmW,
+                     const CUtensorMap& tmC, const GemmParams& p, int sms, cudaStream_t s);
+// Large-M kernel storing every tile through p.n_dst output maps.
+int launch_rows_scatter_kind(int kind, int outmode, const CUtensorMap& tmA, const OutputMaps& outs, const GemmParams& p,
+                             int sms, cudaStream_t s);
+// Small-M kernel for a token block of `bn` and weight tiles of `w_rows` channels.
+int launch_decode_kind(int kind, int outmode, int bn, int w_rows, const CUtensorMap& tmA, const GemmParams& p,
+                       cudaStream_t s);
+
+}  // namespace host
+}  // namespace flyb200

@@ -172,6 +172,13 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
       "l"(src), "r"(bytes), "r"(bar), "l"(policy)
       : "memory");
 }
+// Ask for a contiguous, 16-byte aligned run of global memory to be brought into
+// L2 (no destination in the SM).  A hint: it reads nothing into the SM, so it
+// cannot observe stale data - L2 is the point of coherence for every SM of the
+// GPU, and a later load sees whatever was written last.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 // 2-D tiled store: shared memory -> global (clipped at the tensor bounds).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src),

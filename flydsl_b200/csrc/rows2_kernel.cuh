@@ -282,7 +282,7 @@ gemm_rows2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
       const uint32_t tempty_leader = mapa_u32(bar_tempty + 8 * acc, 0);
-      epilogue_warp_tile<KIND, BN, OUTMODE>(p, &tmC, 1, 0, t_row, m0, n0, lane, stage_c, cbuf, [&]() {
+      epilogue_warp_tile<KIND, OUTMODE>(p, &tmC, 1, 0, t_row, m0, n0, BN, lane, stage_c, cbuf, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(tempty_leader);

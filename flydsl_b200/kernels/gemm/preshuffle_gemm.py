@@ -26,9 +26,15 @@ _IN_DTYPES = ("fp8", "int8", "fp16", "bf16")
 _EPILOGUES = ("none", "bias", "bias_relu", "bias_silu", "bias_gelu")
 _TORCH_OUT = {"bf16": torch.bfloat16, "fp16": torch.float16}
 
-# scratch for split-K partial sums, one per (device, stream); its ticket area
-# must start zeroed and is left zeroed by every completed launch
+# Scratch for split-K partial sums, one buffer per (device, stream).  The first
+# 16 KiB are per-tile arrival counters that must start at zero; every completed
+# launch leaves them at zero.  Buffers are never freed or replaced while the
+# process lives: a kernel still running on another stream, or a captured CUDA
+# graph, may hold the address.
 _workspaces: dict = {}
+_retired: list = []
+_TICKET_BYTES = 16384
+_WORST_CASE_M = (16, 32, 64, 128, 256)  # one M per token-block width of the small-M kernel
 
 
 def _stream_handle(stream) -> int:
@@ -44,15 +50,46 @@ def _stream_handle(stream) -> int:
     return int(handle)
 
 
+def _on_stream(device: torch.device, stream: int):
+    """Context that makes the caller's stream (raw handle; 0 = default) torch's current stream."""
+    if stream == 0:
+        return torch.cuda.stream(torch.cuda.default_stream(device))
+    return torch.cuda.stream(torch.cuda.ExternalStream(stream, device=device))
+
+
 def _workspace(device: torch.device, stream: int, nbytes: int):
+    """Pointer and size of the scratch for launches on ``stream``; allocates
+    (zeroed on that stream) only when no buffer exists yet or a larger one is
+    needed.  Callers pass the worst case of their launcher, so this happens on
+    the first call only."""
     if nbytes == 0:
         return 0, 0
     key = (device.index, stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                "preshuffle_gemm: this shape needs a split-K workspace that does not exist yet; call the launcher once "
+                "(or flyc.compile it) on this stream before capturing a CUDA graph"
+            )
+        if ws is not None:
+            _retired.append(ws)  # may still be in use by running kernels or captured graphs
+        with _on_stream(device, stream):
+            ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws.data_ptr(), ws.numel()
+
+
+def _rezero_tickets() -> None:
+    """After a kernel reported a failed wait its arrival counters may be left
+    non-zero: clear them (the device is idle: the status read synchronised it)."""
+    for ws in list(_workspaces.values()) + _retired:
+        ws[:_TICKET_BYTES].zero_()
+    if _workspaces:
+        torch.cuda.synchronize()
+
+
+_lib.on_failure_status(_rezero_tickets)
 
 
 class PreshuffleGemm:
@@ -76,6 +113,24 @@ class PreshuffleGemm:
         ``sm_count`` SMs (kernel, tile width, split-K, reduction, ring depth, ...):
         a pure host function of the library, no CUDA call."""
         return _lib.describe_plan(max(int(M), 1), self.N, self.K, self.in_dtype, self.variant_hint, sm_count)
+
+    def workspace_bytes(self, device: torch.device) -> int:
+        """Scratch this launcher can need on ``device`` for any M: the largest
+        request over the token-block widths of the small-M kernel (0 when no
+        shape of this launcher reduces through global memory)."""
+        n = self._ws_bytes.get(device.index)
+        if n is None:
+            lib = _lib.load()
+            with torch.cuda.device(device):
+                n = max(int(lib.flyb200_workspace_bytes(m, self.N, self.K, self._dt, self.variant_hint))
+                        for m in _WORST_CASE_M)
+            self._ws_bytes[device.index] = n
+        return n
+
+    def prepare(self, device: torch.device, stream=None) -> None:
+        """Allocate whatever the launcher needs on ``device`` for launches on
+        ``stream`` so that no later call allocates (``flyc.compile`` calls this)."""
+        _workspace(device, _stream_handle(stream), self.workspace_bytes(device))
 
     def _check_tensors(self, c, a, b, sa, sb, bias, M):
         N, K = self.N, self.K
@@ -128,11 +183,7 @@ class PreshuffleGemm:
         bias = arg_bias.data_ptr() if self.epilogue != "none" else None
 
         def run():
-            nbytes = self._ws_bytes.get((dev.index, M))
-            if nbytes is None:
-                nbytes = int(lib.flyb200_workspace_bytes(M, self.N, self.K, self._dt, self.variant_hint))
-                self._ws_bytes[(dev.index, M)] = nbytes
-            ws_ptr, ws_len = _workspace(dev, s, nbytes)
+            ws_ptr, ws_len = _workspace(dev, s, self.workspace_bytes(dev))
             rc = lib.flyb200_gemm_a8w8(
                 arg_c.data_ptr(), arg_a.data_ptr(), arg_b.data_ptr(), sa, sb, bias,
                 M, self.N, self.K, self._dt, self._out, self._epi, self.variant_hint,
@@ -155,12 +206,11 @@ class CompiledPreshuffleGemm:
     no checking either (python/flydsl/compiler/jit_executor.py:185-214).
     Passing buffers smaller than M, N, K imply is then the caller's error."""
 
-    __slots__ = ("op", "_fn", "_ws")
+    __slots__ = ("op", "_fn")
 
     def __init__(self, op: "PreshuffleGemm"):
         self.op = op
         self._fn = _lib.load().flyb200_gemm_a8w8
-        self._ws = {}
 
     def __call__(self, arg_c, arg_a, arg_b, arg_scale_a, arg_scale_b, arg_bias, i32_m, i32_n, stream=None):
         op = self.op
@@ -173,13 +223,10 @@ class CompiledPreshuffleGemm:
             raise ValueError(f"N passed at call time ({i32_n}) differs from the N the launcher was built for ({op.N})")
         s = 0 if stream is None else (stream if isinstance(stream, int) else stream.cuda_stream)
         dev = arg_c.device
-        key = (dev.index, M)
-        nbytes = self._ws.get(key)
+        nbytes = op._ws_bytes.get(dev.index)
         if nbytes is None:
-            with torch.cuda.device(dev):
-                nbytes = int(_lib.load().flyb200_workspace_bytes(M, op.N, op.K, op._dt, op.variant_hint))
-            self._ws[key] = nbytes
-        ws = _workspace(dev, s, nbytes) if nbytes else (0, 0)  # looked up per call: the buffer may have grown
+            nbytes = op.workspace_bytes(dev)
+        ws = _workspace(dev, s, nbytes) if nbytes else (0, 0)
         eight = op._is_8bit
         if torch.cuda.current_device() != dev.index:
             with torch.cuda.device(dev):
@@ -212,6 +259,7 @@ def compile_preshuffle_gemm(
     lds_stage: int = 2,
     preload: Optional[tuple] = None,
     variant_hint: int = 0,
+    weights_static: bool = False,
 ):
     """Build the GEMM launcher ``fn(C, A, B, scale_a, scale_b, bias, M, N, stream)``.
 
@@ -226,6 +274,16 @@ def compile_preshuffle_gemm(
     ``preload`` steer AMD code generation in the reference; here they are
     validated and otherwise ignored.  ``variant_hint`` (not in the reference)
     forwards a tuning override to the library; 0 = automatic.
+
+    ``weights_static`` (not in the reference): promise that no kernel on the
+    launch stream writes the weights ``B`` - true for inference, where they
+    are model state loaded once.  The small-M kernel (M <= 256) then starts
+    streaming weights while the previous kernel on the stream is still
+    finishing (programmatic dependent launch), which hides its ramp-up: about
+    0.8 us of a 14 us decode GEMM.  Leave it False when the weights are
+    produced on the same stream shortly before the call (a freshly
+    dequantised, updated or re-shuffled weight): the early loads could then
+    read the old bytes.  Activations, scales and bias are never read early.
     """
     if in_dtype not in _IN_DTYPES:
         raise ValueError(f"in_dtype must be fp8/int8/fp16/bf16, got {in_dtype!r}")
@@ -256,4 +314,6 @@ def compile_preshuffle_gemm(
             f"the B200 weight image needs N % 16 == 0 and K*elem_bytes % 128 == 0; got N={N}, K={K}, "
             f"elem_bytes={elem_bytes}"
         )
+    if weights_static and ((int(variant_hint) >> 28) & 0x3) == 0:
+        variant_hint = int(variant_hint) | (3 << 28)
     return PreshuffleGemm(N, K, in_dtype, out_dtype, epilogue, (tile_m, tile_n, tile_k), variant_hint)

@@ -54,9 +54,12 @@ extern "C" {
 
 /* variant_hint: 0 = choose automatically.  Otherwise a bit field used for
  * tuning sweeps (each field: 0 = automatic):
- *   bits 0-7   split-K factor of the small-M kernel
+ *   bits 0-7   small-M kernel: split-K factor; large-M kernel (one CTA per
+ *              tile): tile width in units of 32 output channels (1..8, i.e.
+ *              128 x 32 ... 128 x 256 tiles).  Automatic for the large-M kernel:
+ *              the width whose tiles fill the SMs in the fewest, fullest rounds.
  *   bits 8-11  kernel: 1 = small-M weight-stationary kernel (M <= 256),
- *              2 = large-M persistent kernel, one CTA per 128x256 tile,
+ *              2 = large-M persistent kernel, one CTA per 128 x (32..256) tile,
  *              3 = large-M persistent kernel, CTA pairs on 256x256 tiles
  *              4 = small-M kernel with 64-channel weight tiles and no K split
  *              (M <= 64 per token block; twice the CTAs, no reduction step)
@@ -98,7 +101,9 @@ extern "C" {
  *            first 16 KiB must be zero before the first use and are left zero by
  *            every completed call; may be NULL (the automatic choice then keeps
  *            partial sums on chip).  Two calls that overlap on the GPU must not
- *            share a workspace.
+ *            share a workspace.  A call whose kernel gave up on a bounded wait
+ *            (flyb200_read_status() != 0) may leave counters non-zero: zero the
+ *            first 16 KiB again before the workspace is reused.
  * Requirements: N % 16 == 0, K * elem_bytes % 128 == 0, pointers 16-byte aligned. */
 int flyb200_gemm_a8w8(void* c, const void* a, const void* w_shuf, const float* scale_a, const float* scale_b,
                       const void* bias, int M, int N, int K, int in_dtype, int out_dtype, int epilogue,
@@ -147,7 +152,7 @@ size_t flyb200_static_scratch_bytes(void);
  * the operator fused with the all-gather of its output shards: rank r of a group
  * of n_bufs GPUs passes the (peer-mapped) full-width output buffers of all ranks
  * and c_col_offset = r * N, and every 128 x 256 tile leaves the kernel through
- * one TMA store per buffer, so the transfer over NVLink overlaps the math tile
+ * TMA stores to each buffer, so the transfer over NVLink overlaps the math tile
  * by tile.  Plain per-CTA stores; no multicast, no loads from peer memory.  The
  * reference has no multi-GPU form of this operator (its only matching
  * collective is the all_gather_into_tensor fallback of

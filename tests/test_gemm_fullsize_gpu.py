@@ -30,6 +30,8 @@ def gpu_inputs(m, n, k, dev, seed, weight_scale=1.0):
         (5120, 2048, 8320, 1.0),  # reference large shape, narrow N
         (9728, 8192, 8320, 1.0),  # reference large shape (its int8 benchmark shape, here fp8)
         (16384, 8192, 8192, 1.0),  # top of the M sweep
+        (4096, 8192, 8192, 1.0),  # M sweep
+        (16384, 57344, 8192, 1.0),  # benchmark config 5 on one GPU (the multi-GPU workload, unsplit)
     ],
 )
 def test_large_fp8_sampled_rows_and_properties(m, n, k, wscale):
@@ -65,6 +67,48 @@ def test_large_fp8_sampled_rows_and_properties(m, n, k, wscale):
     fn(c3.view(-1), as_i8(a_q).view(-1), as_i8(b_shuf).view(-1), sa, sb, bias, m, n, torch.cuda.current_stream())
     torch.cuda.synchronize()
     assert torch.equal(c3[:m], c[:m])
+
+
+@pytest.mark.parametrize("m", [1, 16, 64, 256, 1024])
+def test_m_sweep_fp8_every_row_against_the_oracle(m):
+    """Benchmark config 4 (N = K = 8192) below the sampled sizes: every output element
+    against the fp32 dequantise-and-matmul reference, inputs quantised per token /
+    per channel from seeded N(0,1) as the configuration states."""
+    dev = torch.device("cuda:0")
+    n = k = 8192
+    a_q, b_q, sa, sb = gpu_inputs(m, n, k, dev, seed=1040 + m)
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=128, tile_n=256, tile_k=128, in_dtype="fp8")
+    rows = ((m + 127) // 128) * 128
+    c = torch.full((rows, n), -8192.0, dtype=torch.bfloat16, device=dev)
+    bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    fn(c.view(-1), as_i8(a_q).view(-1), as_i8(shuffle_weight(b_q)).view(-1), sa, sb, bias, m, n, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert int((c[m:] != -8192.0).sum().item()) == 0
+    ref = oracle.run_torch(a_q.cpu(), b_q.cpu(), sa.cpu(), sb.cpu())
+    got = c[:m].float().cpu()
+    bad = oracle.strict_mismatches(got, ref, RTOL, ATOL)
+    assert bad == 0, f"M={m}: {bad} mismatches; max abs diff {(got - ref).abs().max()}"
+
+
+def test_int8_decode_config_scaled_bf16_output():
+    """Benchmark config 2 (INT8 32 x 8192 x 8192, round-to-nearest quantisation) through the
+    scaled bf16 path, next to the accumulator check of the parity file."""
+    dev = torch.device("cuda:0")
+    m, n, k = 32, 8192, 8192
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "int8", seed=1002, rne_int8=True)
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=32, tile_n=128, tile_k=128, in_dtype="int8")
+    c = torch.full((m + 8, n), -8192.0, dtype=torch.bfloat16, device=dev)
+    bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    fn(c.view(-1), a_q.to(dev).view(-1), shuffle_weight(b_q.to(dev)).view(-1), sa.to(dev).view(-1), sb.to(dev).view(-1), bias, m, n,
+       torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert int((c[m:] != -8192.0).sum().item()) == 0
+    # exact int32 sums scaled in fp32 and rounded once: the kernel's arithmetic, so the bf16 results are equal
+    want = oracle.epilogue(oracle.int32_acc(a_q, b_q), sa, sb, None, "none", out_dtype=torch.bfloat16)
+    assert torch.equal(c[:m].cpu(), want)
+    assert oracle.strict_mismatches(c[:m].float().cpu(), oracle.run_torch(a_q, b_q, sa, sb), RTOL, ATOL) == 0
 
 
 def test_int8_large_accumulators_exact_on_sample():

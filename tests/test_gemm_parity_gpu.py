@@ -357,6 +357,49 @@ def test_fp16_output(dev, in_dtype, m):
     assert oracle.strict_mismatches(got, ref, RTOL, ATOL) == 0
 
 
+# --- large-M kernel: every tile width (the split field of the hint, in units of 32 channels)
+
+
+@pytest.mark.parametrize("width", [1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("m,n,k", [(300, 1040, 2048), (129, 2064, 1152)])
+def test_large_m_kernel_every_tile_width(dev, width, m, n, k):
+    """128 x (32 * width) tiles: N is no multiple of any width, so the last tile of every row is
+    clipped, and widths that are not a multiple of 64 end in the 32-column tail of the epilogue."""
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "fp8", seed=500 + width + m)
+    c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, "fp8", hint=ROWS | width)
+    check_scaled(c, a_q, b_q, sa, sb, m)
+    a_i, b_i, _, _ = oracle.make_inputs(m, n, k, "int8", seed=600 + width, rne_int8=True)
+    acc = gpu_acc(a_i.to(dev), shuffle_weight(b_i.to(dev)), m, n, k, "int8", variant_hint=ROWS | width)
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert torch.equal(acc.cpu(), oracle.int32_acc(a_i, b_i))
+
+
+@pytest.mark.parametrize("width", [3, 7])
+@pytest.mark.parametrize("in_dtype", ["fp8", "bf16"])
+def test_large_m_kernel_tile_tail_with_fused_epilogue(dev, width, in_dtype):
+    m, n, k = 200, 1040, 1024
+    g = torch.Generator().manual_seed(width)
+    bias = torch.randn(n, generator=g).to(torch.bfloat16)
+    if in_dtype == "bf16":
+        a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        b = torch.randn(n, k, generator=g).to(torch.bfloat16)
+        sa = sb = None
+    else:
+        a, b, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=width)
+    got = run_gemm_generic(dev, a, b, sa, sb, bias, m, n, k, in_dtype, epilogue="bias_silu", hint=ROWS | width)
+    ref = oracle.epilogue(a.float() @ b.float().T, sa, sb, bias, "bias_silu", out_dtype=torch.float32)
+    assert oracle.strict_mismatches(got, ref, RTOL, ATOL) == 0
+
+
+def test_automatic_tile_width_fills_whole_rounds():
+    """The planner picks the width whose tiles cover the 148 SMs in full rounds: 1024 x 8192 gives
+    8 x 37 = 296 tiles of 224 channels (two rounds) instead of 256 tiles of 256 (1.73 rounds)."""
+    plan = _lib.describe_plan(1024, 8192, 8192, "fp8", 0, 148)
+    assert plan["kernel"] == 2 and plan["bn"] == 224
+    assert _lib.describe_plan(16384, 57344, 8192, "fp8", 0, 148)["bn"] == 256
+
+
 # --- failure path: a bounded device-side wait that cannot succeed
 
 
