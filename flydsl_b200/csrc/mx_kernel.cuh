@@ -44,29 +44,39 @@ struct MxParams {
   int* status;
 };
 
-template <int BN>
+// FP4: the codes are E2M1, two per byte.  A 128-byte k-block then holds 256
+// elements = eight scale blocks per row: two scale atoms per 128 rows instead of
+// one (atom h covers elements [128 h, 128 h + 128) of the k-block), everything
+// else - operand tiles, ring, swizzle - is the same bytes as for 8-bit codes.
+template <int BN, bool FP4 = false>
 struct MxSmem {
   static constexpr int STAGES = BN == 128 ? 6 : 4;
   static constexpr int NACC = BN == 128 ? 2 : 1;          // TMEM accumulators
+  static constexpr int HALVES = FP4 ? 2 : 1;              // scale atoms per 128 rows and k-block
   static constexpr int SFB_ATOMS = BN / 128;
   static constexpr int A_STAGE = BLOCK_ROWS * KBLOCK_BYTES;
   static constexpr int B_STAGE = BN * KBLOCK_BYTES;
-  static constexpr int SFB_STAGE = SFB_ATOMS * MX_SF_ATOM;
+  static constexpr int SFA_STAGE = HALVES * MX_SF_ATOM;
+  static constexpr int SFB_HALF = SFB_ATOMS * MX_SF_ATOM;
+  static constexpr int SFB_STAGE = HALVES * SFB_HALF;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_STAGE;
   static constexpr int OFF_SFA = OFF_B + STAGES * B_STAGE;
-  static constexpr int OFF_SFB = OFF_SFA + STAGES * MX_SF_ATOM;
+  static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_STAGE;
   static constexpr int OFF_BAR = OFF_SFB + STAGES * SFB_STAGE;  // full[S], empty[S], tfull[2], tempty[2]
   static constexpr int OFF_MISC = OFF_BAR + 8 * (2 * STAGES + 4);
   static constexpr int TOTAL = OFF_MISC + 16;
 };
 
-template <int OUTMODE, int BN>
+template <int OUTMODE, int BN, bool FP4 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const MxParams p) {
-  using L = MxSmem<BN>;
+  using L = MxSmem<BN, FP4>;
   constexpr int STAGES = L::STAGES;
   constexpr int NACC = L::NACC;
-  constexpr int SF_COLS = 4 + 4 * L::SFB_ATOMS;  // TMEM columns of the scale atoms of one stage
+  constexpr int HALVES = L::HALVES;
+  // TMEM columns of the scale atoms of one stage: per half, 4 for A then 4 per 128 channels for W
+  constexpr int SFA_COLS = 4 * HALVES;
+  constexpr int SF_COLS = SFA_COLS + 4 * L::SFB_ATOMS * HALVES;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = smem_u32(smem_raw);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L::OFF_MISC + 4);
@@ -142,15 +152,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
             break;
           }
           const uint32_t fb = bar_full + 8 * stage;
-          mbar_expect_tx(fb, L::A_STAGE + L::B_STAGE + MX_SF_ATOM + L::SFB_STAGE);
+          mbar_expect_tx(fb, L::A_STAGE + L::B_STAGE + L::SFA_STAGE + L::SFB_STAGE);
           tma_load_2d(smem_base + L::OFF_A + stage * L::A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, m_blk * BLOCK_ROWS, pol);
           bulk_load_1d(smem_base + L::OFF_B + stage * L::B_STAGE,
                        p.w + (static_cast<size_t>(kb) * p.N + n_blk * BN) * KBLOCK_BYTES, L::B_STAGE, fb, pol);
-          bulk_load_1d(smem_base + L::OFF_SFA + stage * MX_SF_ATOM,
-                       p.sfa + (static_cast<size_t>(kb) * num_m + m_blk) * MX_SF_ATOM, MX_SF_ATOM, fb, pol);
-          bulk_load_1d(smem_base + L::OFF_SFB + stage * L::SFB_STAGE,
-                       p.sfw + (static_cast<size_t>(kb) * (p.N / 128) + n_blk * L::SFB_ATOMS) * MX_SF_ATOM, L::SFB_STAGE,
-                       fb, pol);
+          // the scale images are indexed by 128-ELEMENT k-blocks: HALVES of them per 128-byte k-block
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h) {
+            const size_t ekb = static_cast<size_t>(kb) * HALVES + h;
+            bulk_load_1d(smem_base + L::OFF_SFA + stage * L::SFA_STAGE + h * MX_SF_ATOM,
+                         p.sfa + (ekb * num_m + m_blk) * MX_SF_ATOM, MX_SF_ATOM, fb, pol);
+            bulk_load_1d(smem_base + L::OFF_SFB + stage * L::SFB_STAGE + h * L::SFB_HALF,
+                         p.sfw + (ekb * (p.N / 128) + n_blk * L::SFB_ATOMS) * MX_SF_ATOM, L::SFB_HALF, fb, pol);
+          }
           ++issued;
           if (++stage == STAGES) {
             stage = 0;
@@ -174,7 +188,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
   } else if (warp == 1) {
     // ------------------------------ MMA issue -----------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_mxf8(BLOCK_ROWS, BN);
+      constexpr uint32_t idesc = FP4 ? umma_idesc_mxf4(BLOCK_ROWS, BN) : umma_idesc_mxf8(BLOCK_ROWS, BN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -196,19 +210,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
           tc_fence_after();
           // scale atoms of this stage: shared memory -> their TMEM columns
           const uint32_t sfa_t = tmem_base + SF_COL0 + static_cast<uint32_t>(stage * SF_COLS);
-          const uint32_t sfb_t = sfa_t + 4;
-          tmem_cp_sf(sfa_t, sf_smem_desc(smem_base + L::OFF_SFA + stage * MX_SF_ATOM));
+          const uint32_t sfb_t = sfa_t + SFA_COLS;
 #pragma unroll
-          for (int at = 0; at < L::SFB_ATOMS; ++at)
-            tmem_cp_sf(sfb_t + 4 * at, sf_smem_desc(smem_base + L::OFF_SFB + stage * L::SFB_STAGE + at * MX_SF_ATOM));
+          for (int h = 0; h < HALVES; ++h) {
+            tmem_cp_sf(sfa_t + 4 * h, sf_smem_desc(smem_base + L::OFF_SFA + stage * L::SFA_STAGE + h * MX_SF_ATOM));
+#pragma unroll
+            for (int at = 0; at < L::SFB_ATOMS; ++at)
+              tmem_cp_sf(sfb_t + 4 * (h * L::SFB_ATOMS + at),
+                         sf_smem_desc(smem_base + L::OFF_SFB + stage * L::SFB_STAGE + h * L::SFB_HALF + at * MX_SF_ATOM));
+          }
           const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L::OFF_A + stage * L::A_STAGE);
           const uint64_t bdesc = umma_desc_sw128_kmajor(smem_base + L::OFF_B + stage * L::B_STAGE);
 #pragma unroll
           for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
-            // the k-th 32-element block uses byte k of the scale columns: scale-factor id k for both operands
-            const uint32_t id = idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
-            umma_mxf8(d_tmem, adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
-                      bdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), id, sfa_t, sfb_t, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (FP4) {
+              // 32 bytes = 64 elements = scale blocks 2k and 2k+1 of the k-block: atom k/2, bytes 2(k%2) and 2(k%2)+1
+              const uint32_t sf_id = static_cast<uint32_t>((k & 1) * 2);
+              const uint32_t id = idesc | (sf_id << 4) | (sf_id << 29);
+              umma_mxf4(d_tmem, adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                        bdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), id, sfa_t + 4 * (k >> 1),
+                        sfb_t + 4 * L::SFB_ATOMS * (k >> 1), (kb | k) != 0 ? 1u : 0u);
+            } else {
+              // the k-th 32-element block uses byte k of the scale columns: scale-factor id k for both operands
+              const uint32_t id = idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
+              umma_mxf8(d_tmem, adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                        bdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), id, sfa_t, sfb_t, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(bar_empty + 8 * stage);
           if (++stage == STAGES) {

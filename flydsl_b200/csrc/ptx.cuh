@@ -309,6 +309,26 @@ __device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t adesc, uint6
       : "memory");
 }
 
+// MXFP4: E2M1 codes, two per byte (128 bytes of a swizzled row = 256 elements of K).
+// kind::mxf4 consumes 64 elements (32 bytes) of K per instruction, i.e. two
+// 32-element scale blocks: with scale_vec::2X the instruction takes two scale
+// bytes per row from a TMEM column, bytes {0,1} or {2,3} as the scale-factor id
+// (0 or 2) says.  Operand format code of E2M1 in this kind: 1.
+__host__ __device__ constexpr uint32_t umma_idesc_mxf4(uint32_t m, uint32_t n) {
+  return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa_tmem,
+                                          uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }

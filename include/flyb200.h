@@ -317,6 +317,27 @@ int flyb200_moe_reduce(void* y, const void* x, int tokens, int topk, int dim, in
  * Requirements: K % 128 == 0, N % 128 == 0, pointers 16-byte aligned. */
 int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
                        int M, int N, int K, int out_dtype, void* stream);
+
+/* ---- MXFP4: E2M1 codes (two per byte) with one E8M0 scale per 32 elements of K on both operands ----
+ * Replaces the MXFP4 x MXFP4 configuration of the same reference kernel
+ * (kernels/gemm/mxfp4_preshuffle.py launch_gemm with a_dtype = b_dtype = "fp4",
+ * :72-74,99-133; call convention and data recipe pinned by
+ * tests/kernels/test_preshuffle_gemm.py:343-466 test_mfma_w4_flyc_preshuffle):
+ *   c[M, N] = sum_k fp4(a[m,k]) * 2^(sa[m, k/32] - 127) * fp4(w[n,k]) * 2^(sw[n, k/32] - 127)
+ * computed with tcgen05.mma kind::mxf4.block_scale.scale_vec::2X (64 elements of
+ * K and two scale blocks per instruction), scale factors in TMEM.
+ *   a              [M, K/2] bytes, row-major; element 2i of a row in the low nibble of byte i
+ *   w_shuf         the [N, K/2] byte matrix of weight codes in the image of
+ *                  flyb200_shuffle_weight (elem_bytes = 1, K/2 bytes per row); takes the
+ *                  place of shuffle_weight_w4 (tests/kernels/utils/gemm_common_utils.py:607-642)
+ *   scale_a_image, scale_w_image   as for flyb200_gemm_mxfp8: flyb200_mx_scale_image of the
+ *                  [rows, K/32] scales with K counted in ELEMENTS
+ * K is the number of elements.  Requirements: K % 256 == 0, N % 128 == 0, pointers
+ * 16-byte aligned.  The reference's mixed configurations (fp8 or fp6 activations
+ * with fp4 weights) are not built: kind::mxf8f6f4 wants 4- and 6-bit operands
+ * padded to 8 bits in shared memory, which forfeits the smaller weight stream. */
+int flyb200_gemm_mxfp4(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
+                       int M, int N, int K, int out_dtype, void* stream);
 int flyb200_mx_scale_image(void* dst, const void* src, int rows, int K, void* stream);
 size_t flyb200_mx_scale_image_bytes(int rows, int K);
 

@@ -80,3 +80,72 @@ def make_inputs(m, n, k, seed):
     a_q, sa = per_1x32_f8_quant(a)
     b_q, sb = per_1x32_f8_quant(b)
     return a_q, sa, b_q, sb
+
+
+# ---------------------------------------------------------------------------
+# MXFP4: E2M1 codes, two per byte, one E8M0 scale per 32 elements
+# (tests/kernels/utils/gemm_common_utils.py:14-50, 162-276, 675-705)
+# Parity status: PINNED by tests/golden/mx_fp4.npz (tests/golden/make_golden_mx4.py
+# ran the reference's per_1x32_f4_quant / mxfp4_to_f32 / e8m0_to_f32 and the
+# reference formula of tests/kernels/test_preshuffle_gemm.py:404-411 on CPU).
+# ---------------------------------------------------------------------------
+FP4_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)  # magnitudes of codes 0..7; bit 3 is the sign
+_FP4_MIDPOINTS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)  # between code c and c + 1
+
+
+def f32_to_fp4_codes(x):
+    """E2M1 code (uint8, 0..15) of every element: round to nearest, ties to the code
+    with an even mantissa bit, magnitudes of 6 and above saturate to 6, the sign bit
+    (also of -0.0) is kept (gemm_common_utils.py:162-276 with ebits=2, mbits=1)."""
+    a = x.float().abs()
+    code = torch.zeros_like(a, dtype=torch.int32)
+    for c, mid in enumerate(_FP4_MIDPOINTS):
+        up = (a > mid) | ((a == mid) & bool(c & 1))  # at a tie the odd code moves up to its even neighbour
+        code = code + up.to(torch.int32)
+    code = code | (torch.signbit(x.float()).to(torch.int32) << 3)
+    return code.to(torch.uint8)
+
+
+def pack_fp4(codes):
+    """Two codes per byte, the even element in the low nibble (gemm_common_utils.py:142-149)."""
+    assert codes.shape[-1] % 2 == 0
+    return (codes[..., 1::2] << 4 | codes[..., 0::2]).contiguous()
+
+
+def mxfp4_to_f32(packed):
+    """fp32 value of every E2M1 code of a packed tensor [..., K/2] -> [..., K] (gemm_common_utils.py:23-50)."""
+    b = packed.view(torch.uint8)
+    codes = torch.stack([b & 0xF, b >> 4], dim=-1).flatten(-2)
+    table = torch.tensor(FP4_VALUES + tuple(-v for v in FP4_VALUES), dtype=torch.float32)
+    return table[codes.long()]
+
+
+def per_1x32_f4_quant(x):
+    """(packed codes uint8 [..., K/2], scales uint8 E8M0 [..., K/32]): scale = E8M0 of
+    blockmax / 4 (4 = the largest power of two E2M1 holds), codes = x / scale rounded
+    to E2M1 (gemm_common_utils.py:675-705)."""
+    shape = x.shape
+    flat = x.contiguous().view(-1, BLOCK).float()
+    max_abs = torch.amax(torch.abs(flat), dim=-1)
+    scale = f32_to_e8m0(max_abs / 4.0)
+    y = flat / e8m0_to_f32(scale).view(-1, 1)
+    codes = f32_to_fp4_codes(y).view(*shape)
+    return pack_fp4(codes), scale.view(*shape[:-1], shape[-1] // BLOCK).contiguous()
+
+
+def dequant_fp4(packed, scale):
+    return mxfp4_to_f32(packed) * e8m0_to_f32(scale).repeat_interleave(BLOCK, dim=-1)
+
+
+def mx4_gemm(a_packed, scale_a, b_packed, scale_b):
+    """fp32 [M, N]: dequantise both operands, torch.mm (tests/kernels/test_preshuffle_gemm.py:404-411)."""
+    return torch.mm(dequant_fp4(a_packed, scale_a), dequant_fp4(b_packed, scale_b).T).to(torch.float32)
+
+
+def make_inputs_fp4(m, n, k, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = torch.randn(m, k, generator=g, dtype=torch.float32)
+    b = torch.randn(n, k, generator=g, dtype=torch.float32)
+    a_q, sa = per_1x32_f4_quant(a)
+    b_q, sb = per_1x32_f4_quant(b)
+    return a_q, sa, b_q, sb

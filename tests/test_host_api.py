@@ -150,6 +150,18 @@ def test_reference_import_paths():
     assert callable(flyc.compile)
 
 
+def test_reference_import_lines_resolve_after_compat_install():
+    import flydsl_b200.compat
+
+    names = flydsl_b200.compat.install()
+    assert "flydsl.compiler" in names and "kernels.gemm.preshuffle_gemm" in names
+    import flydsl.compiler as ref_flyc  # the reference's line (tests/kernels/test_preshuffle_gemm.py:21)
+    from kernels.gemm.preshuffle_gemm import compile_preshuffle_gemm as ref_cpg  # (:35)
+    from kernels.moe.moe_gemm_2stage import compile_moe_gemm1  # noqa: F401
+
+    assert ref_flyc.compile is flyc.compile and ref_cpg is compile_preshuffle_gemm
+
+
 def test_variant_selection_is_a_pure_host_function():
     """The M-bucket dispatch (the counterpart of the reference's per-tile tuning
     table) can be inspected without a GPU."""

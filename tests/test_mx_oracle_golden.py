@@ -42,3 +42,43 @@ def test_scale_image_layout():
         off = (k_block * 2 + tile) * 512 + (rr % 32) * 16 + (rr // 32) * 4 + j
         assert int(img[off]) == int(s[r, kb])
     assert int(img[(0 * 2 + 1) * 512 + (5 % 32) * 16 + 0 + 0]) == 0  # padding row 128 + 5
+
+
+# --- MXFP4 (E2M1 codes, two per byte): fixture from the reference's per_1x32_f4_quant / mxfp4_to_f32
+
+Z4 = np.load(os.path.join(os.path.dirname(__file__), "golden", "mx_fp4.npz"))
+
+
+def t4(name):
+    return torch.from_numpy(Z4[name])
+
+
+def test_fp4_rounding_at_every_boundary():
+    got = mx_oracle.f32_to_fp4_codes(t4("probe"))
+    assert torch.equal(got, t4("probe_codes"))
+
+
+def test_fp4_decode_table():
+    all_bytes = torch.arange(256, dtype=torch.uint8).view(1, 256)
+    assert torch.equal(mx_oracle.mxfp4_to_f32(all_bytes), t4("table"))
+
+
+def test_fp4_quantiser_matches_reference():
+    for x, q, s in (("a", "a_q", "sa"), ("b", "b_q", "sb")):
+        codes, scale = mx_oracle.per_1x32_f4_quant(t4(x))
+        assert torch.equal(codes, t4(q))
+        assert torch.equal(scale, t4(s))
+
+
+def test_fp4_gemm_reference_matches():
+    c = mx_oracle.mx4_gemm(t4("a_q"), t4("sa"), t4("b_q"), t4("sb"))
+    assert torch.equal(c, t4("c"))
+
+
+def test_shipped_fp4_quantiser_matches_reference_fixture():
+    from flydsl_b200.kernels.gemm.mxfp4_preshuffle import mxfp4_to_f32, per_1x32_f4_quant
+
+    for x, q, s in (("a", "a_q", "sa"), ("b", "b_q", "sb")):
+        codes, scale = per_1x32_f4_quant(t4(x))
+        assert torch.equal(codes, t4(q)) and torch.equal(scale, t4(s))
+    assert torch.equal(mxfp4_to_f32(torch.arange(256, dtype=torch.uint8).view(1, 256)), t4("table"))
