@@ -82,7 +82,7 @@ class ClockSampler:
         0x80: "hw_power_brake_slowdown",
     }
 
-    def __init__(self, device_index: int, period_s: float = 0.02):
+    def __init__(self, device_index: int, period_s: float = 0.005):
         self.samples, self.reasons, self.power = [], set(), []
         self.max_mhz = None
         self._stop = threading.Event()
@@ -115,10 +115,20 @@ class ClockSampler:
                 for bit, name in self.REASONS.items():
                     if mask & bit:
                         self.reasons.add(name)
-                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                self.power.append(self._power_w())
             except Exception:
                 pass
             self._stop.wait(self.period)
+
+    def _power_w(self):
+        nv = self.nv
+        try:  # instantaneous board power where the driver offers it (the default reading is a running average)
+            fv = nv.nvmlDeviceGetFieldValues(self.h, [nv.NVML_FI_DEV_POWER_INSTANT])[0]
+            if fv.nvmlReturn == 0 and fv.value.uiVal > 0:
+                return fv.value.uiVal / 1000.0
+        except Exception:
+            pass
+        return nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
 
     def start(self):
         if self.h is not None:
@@ -470,7 +480,7 @@ def parity_check(op, a_q, sa, w_q_local, sb_local, local, full_ag, full_fused, d
 # there, and that case's algorithmic bytes.  The weights stream once per group of row
 # tiles and the activations once, so the full workload's traffic is estimated group by
 # group (see traffic_estimate), not by plain proportion.
-NCU_TRAFFIC_CASE = None  # filled in from the capture: {"m":..,"n":..,"k":..,"group_m":..,"read":..,"write":..}
+NCU_TRAFFIC_CASE = {"m": 4096, "n": 14336, "k": 8192, "group_m": 32, "read": 176.1e6, "write": 95.7e6}
 
 
 def traffic_estimate(m, n, k, group_m):
@@ -561,6 +571,17 @@ def main():
     for _ in range(args.warmup):
         op.forward(a_q, sa, out=c)
     barrier()
+    # More untimed steps right up to the timed region (about half a second of them): the
+    # board's power and clock telemetry lags by tens of milliseconds, and the timed steps
+    # should run - and be sampled - at the clocks a long job sees, not at a cold burst.
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0.record(stream)
+    op.forward(a_q, sa, out=c)
+    w1.record(stream)
+    torch.cuda.synchronize()
+    preroll = max(0, min(400, int(0.5 / max(w0.elapsed_time(w1) * 1e-3, 1e-5))))
+    for _ in range(preroll):
+        op.forward(a_q, sa, out=c)
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
@@ -650,7 +671,7 @@ def main():
     achieved = flops_launch / (med_ms * 1e-3) / 1e12
     fp8_peak = 2.0 * peaks["bf16_tflops"]
     plan = op.launch.plan(m)
-    group_m = (args.hint >> 16) & 0xFF or 16
+    group_m = (args.hint >> 16) & 0xFF or 32
     traffic = None
     traffic_note = "no ncu capture recorded for this build"
     if NCU_TRAFFIC_CASE:
@@ -772,6 +793,7 @@ def main():
                 "ms_per_step": e2e_ms, "steps": e2e_steps,
                 "note": "bytes per rank; on several GPUs a rank uploads 1/world of the activations and NCCL all-gathers them"},
         "gpu_launches": args.steps,
+        "untimed_steps_before": args.warmup + 1 + preroll,
         "clocks": clocks,
         "roofline": roofline,
         "cpu_baseline": cpu,

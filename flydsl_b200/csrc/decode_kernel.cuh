@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
       int issued = pre;
       const int ahead = min(p.prefetch, num_kb);
       for (int kb = kb_begin + pre; kb < kb_end; ++kb) {
-        if (kb - pre + ahead < kb_end)  // the next block not yet asked for
+        if (ahead > 0 && kb - pre + ahead < kb_end)  // the next block not yet asked for
           bulk_prefetch_l2(p.w + (static_cast<size_t>(kb - pre + ahead) * p.N + n0) * KBLOCK_BYTES, w_bytes);
         if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
           report_failure(p.status, ST_TIMEOUT, abort_flag);

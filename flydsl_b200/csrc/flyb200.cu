@@ -158,10 +158,10 @@ inline int default_decode_stages(int bn, int w_rows = BLOCK_ROWS) {
 
 inline int decode_bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
-// Split-K factor of the small-M kernel when the caller does not force one:
-// enough CTAs to cover the SMs, at least four k-blocks per CTA.
+// Split-K factor that simply covers the SMs, with at least four k-blocks per
+// CTA (the built-in-scratch entry point sizes its split with this).
 // `token_blocks`: CTAs per channel tile that the token split already provides.
-int auto_split_k(int N, int K_bytes, int sms, int token_blocks = 1) {
+int fill_sms_split_k(int N, int K_bytes, int sms, int token_blocks = 1) {
   const int n_tiles = ((N + BLOCK_ROWS - 1) / BLOCK_ROWS) * token_blocks;
   const int kb = K_bytes / KBLOCK_BYTES;
   if (n_tiles >= sms || n_tiles > static_cast<int>(TICKET_BYTES / sizeof(int))) return 1;
@@ -169,6 +169,65 @@ int auto_split_k(int N, int K_bytes, int sms, int token_blocks = 1) {
   if (split > kb / 4) split = kb / 4;
   if (split > MAX_SPLIT_K) split = MAX_SPLIT_K;
   return split < 1 ? 1 : split;
+}
+
+// Estimated time (ns) of the small-M kernel for a split-K factor, from rates
+// measured on B200 (N = K = 8192 and 4096, 1..256 tokens):
+//   fixed      ~3 us: launch, first bytes from DRAM, exit.
+//   stream     a CTA takes in ~71 B/ns (its 16 KiB weight block from DRAM plus the
+//              token tile from L2 share the SM's input port); all CTAs together
+//              cannot beat a read-only stream over the GPU (~7 TB/s).  CTAs
+//              beyond one per SM run in a second round.
+//   reduction  cluster: two cluster barriers and a remote round trip (~1.5 us)
+//              plus the (split-1)/split of a partial tile (bn x 512 B) every CTA
+//              reads from its peers at ~15 B/ns; clusters of more than four CTAs
+//              measured ~10 us slower than the model (scheduling of large clusters
+//              that each need a whole SM's shared memory).  Workspace: ~3 us
+//              (ticket, fences) plus the last CTA reading `split` partial tiles
+//              from L2 at ~100 B/ns.
+// Reproduces the measured ranking: split 2 at 64 channel tiles (14.5 us against
+// 21 us unsplit and 15 us for split 4), split 4 at 32 tiles of 128 tokens (9.8 us
+// against 12.1 / 19.0 / 21.4 us for 2 / 1 / 8).
+double split_cost_ns(int split, int n_tiles, int kb, int bn, int sms, bool cluster) {
+  const double stage_bytes = static_cast<double>(BLOCK_ROWS * KBLOCK_BYTES + bn * KBLOCK_BYTES);
+  const int rounds = (n_tiles * split + sms - 1) / sms;
+  const int kbs = (kb + split - 1) / split;
+  double stream = rounds * kbs * stage_bytes / 71.0;
+  const double hbm = static_cast<double>(n_tiles) * kb * (BLOCK_ROWS * KBLOCK_BYTES) / 7000.0;
+  if (stream < hbm) stream = hbm;
+  double reduce = 0.0;
+  if (split > 1) {
+    const double partial = bn * 512.0;
+    reduce = cluster ? 1500.0 + (split - 1.0) / split * partial / 15.0 + (split > 4 ? 10000.0 : 0.0)
+                     : 3000.0 + split * partial / 100.0;
+  }
+  return 3000.0 + stream + reduce;
+}
+
+// Split-K factor of the small-M kernel when the caller does not force one: the
+// cheapest by split_cost_ns over cluster splits 1..8 and, where a workspace of
+// the needed size was passed, workspace splits 9..32.  Every split keeps at
+// least two k-blocks per CTA.
+int auto_split_k(int N, int K_bytes, int sms, int bn, int token_blocks, size_t workspace_bytes, bool have_ws) {
+  const int n_tiles = ((N + BLOCK_ROWS - 1) / BLOCK_ROWS) * token_blocks;
+  const int kb = K_bytes / KBLOCK_BYTES;
+  if (n_tiles >= sms) return 1;
+  int best = 1;
+  double best_cost = split_cost_ns(1, n_tiles, kb, bn, sms, true);
+  for (int s = 2; s <= MAX_SPLIT_K && 2 * s <= kb; ++s) {
+    const bool cluster = s <= MAX_CLUSTER_SPLIT;
+    if (!cluster) {
+      if (!have_ws || n_tiles > static_cast<int>(TICKET_BYTES / sizeof(int))) break;
+      const size_t need = TICKET_BYTES + static_cast<size_t>(s) * n_tiles * bn * BLOCK_ROWS * sizeof(uint32_t);
+      if (workspace_bytes < need) break;
+    }
+    const double c = split_cost_ns(s, n_tiles, kb, bn, sms, cluster);
+    if (c < best_cost) {
+      best_cost = c;
+      best = s;
+    }
+  }
+  return best;
 }
 
 size_t partial_bytes(int split, int N, int bn, int token_blocks = 1) {
@@ -199,6 +258,17 @@ int pdl_default() {
     return e[0] == '1' ? 1 : e[0] == '2' ? 2 : 0;
   }();
   return mode;
+}
+
+// FLYB200_PREFETCH_DECODE: tuning override of the small-M kernel's prefetch distance (k-blocks); -1 = not set
+int decode_prefetch_override() {
+  static const int n = []() {
+    const char* e = getenv("FLYB200_PREFETCH_DECODE");
+    if (!e) return -1;
+    const int v = atoi(e);
+    return v < 0 ? 0 : v;
+  }();
+  return n;
 }
 
 bool w64_default() {
@@ -303,7 +373,9 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     plan->bn = decode_bn_for((M + t - 1) / t);
     plan->token_blocks = (M + plan->bn - 1) / plan->bn;  // no empty block
   }
-  plan->group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : (plan->two_sm ? 8 : 16);
+  // 32 row tiles (32 MiB of 8-bit activations at K = 8192) stay in L2 while a group walks the channels:
+  // measured DRAM reads 1.17 x the operands against 1.67 x with groups of 16, at equal time
+  plan->group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : (plan->two_sm ? 8 : 32);
   plan->split_k = 1;
   plan->reduce_mode = REDUCE_NONE;
   if (plan->decode) {
@@ -326,16 +398,21 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   if (plan->stages & 1) {
     plan->stages += decode_layout(plan->bn, plan->stages + 1, plan->w_rows).total <= SMEM_LIMIT ? 1 : -1;
   }
-  {
-    const char* e = getenv(plan->decode ? "FLYB200_PREFETCH_DECODE" : "FLYB200_PREFETCH_ROWS");
-    plan->prefetch = e ? atoi(e) : (plan->decode ? 64 : 0);
-  }
+  // Weights requested into L2 ahead of the ring.  Small-M kernel: four k-blocks
+  // beyond the depth of the ring measured best (INT8 32 x 8192 x 8192 on one GPU:
+  // 13.9 us with 12 blocks ahead of an 8-deep ring, 14.4 us with 8, 14.7 us with
+  // none, 15.3 us with the whole K range requested at once).  Large-M kernel:
+  // none; there the weights of a tile are shared by the CTAs of a group and
+  // mostly hit L2 already, and the extra requests cost 1-30 %.
+  plan->prefetch = 0;  // small-M kernel: set below, once the ring depth is known
+  if (plan->decode) plan->prefetch = decode_prefetch_override() >= 0 ? decode_prefetch_override() : plan->stages + 4;
   const int hp = hint_pdl(variant_hint);
   plan->pdl = hp == 1 ? 1 : hp == 2 ? 0 : hp == 3 ? 2 : pdl_default();
   const int kb = K_bytes / KBLOCK_BYTES;
   plan->kb_per_split = kb;
   if (plan->decode) {
-    int split = want_split > 0 ? want_split : auto_split_k(N, K_bytes, sms, plan->token_blocks);
+    int split = want_split > 0 ? want_split
+                               : auto_split_k(N, K_bytes, sms, plan->bn, plan->token_blocks, workspace_bytes, have_ws);
     if (plan->w_rows == 64) split = 1;
     if (split > kb) split = kb;
     int mode = REDUCE_NONE;
@@ -661,7 +738,7 @@ int flyb200_gemm_a8w8_static_scratch(void* c, const void* a, const void* w_shuf,
     DeviceState* st = nullptr;
     int rc = device_state(&st);
     if (rc) return rc;
-    split = auto_split_k(N, K * eb, st->sms);
+    split = fill_sms_split_k(N, K * eb, st->sms);
     while (split > 1 && TICKET_BYTES + partial_bytes(split, N, bn) > STATIC_SCRATCH_BYTES) --split;
   }
   if (split > kb) split = kb;
@@ -726,7 +803,7 @@ int flyb200_gemm_a8w8_scatter(void* const* c_bufs, int n_bufs, int first_buf, lo
   p.N = N;
   p.K_bytes = K_bytes;
   p.epilogue = epilogue;
-  p.group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : 16;
+  p.group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : 32;
   p.split_k = 1;
   p.kb_per_split = K_bytes / KBLOCK_BYTES;
   p.bn = 256;

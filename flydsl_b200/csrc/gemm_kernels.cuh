@@ -154,8 +154,9 @@ __device__ __forceinline__ float load_bias(const void* bias, int col) {
 // `release_tmem()` is called once, as soon as the accumulator has been read.
 // `tmC` points to `n_dst` tensor maps: the staged chunk is stored through each
 // of them (the caller's own output, or the same window of the output buffers of
-// several GPUs), starting with map `dst_first` so that ranks do not all hit the
-// same peer at the same time.
+// several GPUs), starting with map `dst_first` (+ a per-tile, per-warp rotation)
+// so that neither the ranks nor the tiles of one rank all hit the same peer at
+// the same time.
 template <int KIND, int OUTMODE, typename ReleaseFn>
 __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* tmC, int n_dst, int dst_first,
                                                    uint32_t t_row, int m0, int n0, int BN, int lane, uint32_t stage_c,
@@ -262,8 +263,7 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CU
       if (lane == 0) {
         if (m0 < p.M && (n0 + c0) < p.N) {
           for (int d = 0; d < n_dst; ++d) {
-            int which = dst_first + d;
-            if (which >= n_dst) which -= n_dst;
+            int which = (dst_first + d) % n_dst;
             tma_store_2d(tmC + which, stage_c + cbuf * C_BUF, n0 + c0, m0);
           }
         }
@@ -405,7 +405,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
         for (int kb = 0; kb < ahead; ++kb)
           bulk_prefetch_l2(p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES, w_bytes);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (kb + ahead < num_kb)
+          if (ahead > 0 && kb + ahead < num_kb)
             bulk_prefetch_l2(p.w + (static_cast<size_t>(kb + ahead) * p.N + n0) * KBLOCK_BYTES, w_bytes);
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag FLYB200_PROF_ARG(&prof_wait[0]))) {
             report_failure(p.status, ST_TIMEOUT, abort_flag);
@@ -503,7 +503,9 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
       tc_fence_after();
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * ROWS_ACC_COLS);
-      epilogue_warp_tile<KIND, OUTMODE>(p, tmC_ptr, n_dst, dst_first, t_row, m0, n0, BN, lane, stage_c, cbuf, [&]() {
+      // own buffer first for the first tile; every further tile and warp starts one destination later
+      const int first = n_dst > 1 ? (dst_first + (t / static_cast<int>(gridDim.x)) + ew) % n_dst : 0;
+      epilogue_warp_tile<KIND, OUTMODE>(p, tmC_ptr, n_dst, first, t_row, m0, n0, BN, lane, stage_c, cbuf, [&]() {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);

@@ -50,6 +50,32 @@ def _worker(rank, world, port, q):
             torch.cuda.synchronize()
             if not torch.equal(unfused, full):
                 ok, msg = False, f"{in_dtype}: fused and unfused results differ on rank {rank}"
+            # back-to-back calls without any host synchronisation: result i is read (a clone enqueued on
+            # the stream) before call i+1 is issued, which is all the contract promises; inputs differ
+            # per call (token scales times 2^i, exact in bf16) so that a stale or torn buffer shows
+            base = full.clone()  # `full` is a view of a buffer that the calls below overwrite
+            clones = []
+            for it in range(4):
+                clones.append(op.forward_full_fused(a_d, sa_d * float(2 ** it)).clone())
+            torch.cuda.synchronize()
+            for it, got in enumerate(clones):
+                if not torch.equal(got, (base.float() * float(2 ** it)).to(base.dtype)):
+                    ok, msg = False, f"{in_dtype}: unsynchronised call {it} returned a stale or torn buffer on rank {rank}"
+            # host buffers in and out, each rank uploading only its half of the rows of every block
+            from flydsl_b200.column_parallel import pinned_near
+            a_host = pinned_near(dev, tuple(a_q.shape), torch.int8)
+            a_host.copy_(a_q.view(torch.int8))
+            sa_host = sa.clone().pin_memory()
+            c_host = pinned_near(dev, (m, op.spec.n_local), torch.bfloat16)
+            m_even = m // 256 * 256  # forward_host shards whole 128-row blocks evenly over the ranks
+            if m_even:
+                op.forward_host(a_host[:m_even], sa_host[:m_even], c_host[:m_even], chunks=max(1, m_even // 256))
+                torch.cuda.synchronize()
+                if op.last_h2d_bytes >= m_even * k:
+                    ok, msg = False, f"{in_dtype}: rank {rank} uploaded all of A ({op.last_h2d_bytes} bytes) instead of its share"
+                # (a few hundred rows may run on the small-M kernel, whose summation order differs: compare with the oracle)
+                if oracle.strict_mismatches(c_host[:m_even].float(), ref[:m_even, sl], 1e-2, 1e-2):
+                    ok, msg = False, f"{in_dtype}: host-buffer path differs from the oracle on rank {rank}"
             if _lib.read_status() != 0:
                 ok, msg = False, "device status set"
         dist.barrier()
