@@ -244,6 +244,13 @@ def quantised_on_gpu(m, n, k, in_dtype, dev, seed, weight_scale):
     return a_q, sa.view(-1), w_q, sb.view(-1)
 
 
+def settle(seconds=0.3):
+    """Let the board leave the power-capped state of the preceding tensor-bound runs
+    before a short memory-bound case is timed (idle host time, outside every timed region)."""
+    torch.cuda.synchronize()
+    time.sleep(seconds)
+
+
 def time_config(m, n, k, in_dtype, dev, iters=40, hint=0, seed=0, weight_scale=1.0):
     """Device time of one single-GPU configuration: CUDA events around a graph
     replay of `iters` launches whose operand copies rotate, so that consecutive
@@ -322,29 +329,38 @@ def time_scaled_mm(m, n, k, dev, iters=5, seed=0, weight_scale=1.0):
     return None, last
 
 
-def time_mx(m, n, k, dev, iters=10):
-    """Device time of the MXFP8 block-scaled GEMM (operands larger than L2, back-to-back launches);
-    algorithmic bytes as in the reference's test (tests/kernels/test_preshuffle_gemm.py:695)."""
+def time_mx(m, n, k, dev, iters=10, fp4=False):
+    """Device time of the block-scaled GEMM, MXFP8 or (fp4=True) MXFP4 codes (operands larger than L2,
+    back-to-back launches); algorithmic bytes as in the reference's tests
+    (tests/kernels/test_preshuffle_gemm.py:695 and :455-459)."""
     from flydsl_b200 import shuffle_weight
+    from flydsl_b200.kernels.gemm.mxfp4_preshuffle import compile_mxfp4_preshuffle_gemm
     from flydsl_b200.kernels.gemm.mxfp8_preshuffle import compile_mxfp8_preshuffle_gemm, shuffle_scale
 
     g = torch.Generator(device=dev).manual_seed(78)
-    a = (torch.randn(m, k, generator=g, device=dev) * 64).clamp_(-448, 448).to(FP8)
-    byts = m * k + n * k + 2 * m * n + (m + n) * (k // 32)
+    code_bytes = k // 2 if fp4 else k  # bytes per row of codes
+
+    def codes(rows):
+        if fp4:  # random E2M1 pairs
+            return torch.randint(0, 256, (rows, code_bytes), generator=g, dtype=torch.uint8, device=dev)
+        return (torch.randn(rows, k, generator=g, device=dev) * 64).clamp_(-448, 448).to(FP8).view(torch.uint8)
+
+    a = codes(m)
+    byts = (m + n) * code_bytes + 2 * m * n + (m + n) * (k // 32)
     # weights (and their scales) rotate over enough copies that no launch finds them in L2
     copies = max(1, min(6, int(400e6 // byts) + 1))
     ws, sws = [], []
     for _ in range(copies):
-        ws.append(shuffle_weight((torch.randn(n, k, generator=g, device=dev) * 64).clamp_(-448, 448).to(FP8)))
+        ws.append(shuffle_weight(codes(n)))
         sws.append(shuffle_scale(torch.randint(120, 130, (n, k // 32), generator=g, dtype=torch.uint8, device=dev)))
     sa = shuffle_scale(torch.randint(120, 130, (m, k // 32), generator=g, dtype=torch.uint8, device=dev))
     c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-    fn = compile_mxfp8_preshuffle_gemm(N=n, K=k)
+    fn = compile_mxfp4_preshuffle_gemm(N=n, K=k) if fp4 else compile_mxfp8_preshuffle_gemm(N=n, K=k)
     st = torch.cuda.Stream()
 
     def launch(i):
         j = i % copies
-        fn(c.view(-1), a.view(torch.uint8).view(-1), ws[j].view(torch.uint8).view(-1), sa, sws[j], None, m, n, st)
+        fn(c.view(-1), a.view(-1), ws[j].view(torch.uint8).view(-1), sa, sws[j], None, m, n, st)
 
     with torch.cuda.stream(st):
         for i in range(3):
@@ -362,9 +378,10 @@ def time_mx(m, n, k, dev, iters=10):
         e1.record(st)
         st.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / iters
+    nominal = 2 * NOMINAL_FP8_TFLOPS if fp4 else NOMINAL_FP8_TFLOPS
     return {"us": round(us, 2), "tflops": round(2.0 * m * n * k / us / 1e6, 1), "hbm_gbs": round(byts / us / 1e3, 1),
-            "frac_of_nominal_fp8": round(2.0 * m * n * k / us / 1e6 / NOMINAL_FP8_TFLOPS, 3), "algorithmic_bytes": int(byts),
-            "rotating_copies": copies}
+            ("frac_of_nominal_fp4_9000" if fp4 else "frac_of_nominal_fp8"): round(2.0 * m * n * k / us / 1e6 / nominal, 3),
+            "algorithmic_bytes": int(byts), "rotating_copies": copies}
 
 
 def time_moe(tokens, model_dim, inter_dim, experts, topk, tile_m, dev, iters=20):
@@ -717,6 +734,8 @@ def main():
         configs = {}
         for name, em, en, ek, edt, ews, eseed, bound, static_too in cases:
             iters = 20 if em <= 4096 and en <= 8192 else 5
+            if bound == "hbm":
+                settle()
             us, copies = time_config(em, en, ek, edt, dev, iters=iters, seed=eseed, weight_scale=ews)
             by = gemm_bytes(em, en, ek)
             tf = 2.0 * em * en * ek / us / 1e6
@@ -751,11 +770,20 @@ def main():
         extras["mxfp8_8192x14336x8192"] = time_mx(8192, 14336, 8192, dev, iters=5)
         # ... and on the reference's own MXFP8 test shapes (tests/kernels/test_preshuffle_gemm.py:590-598)
         for mm in (32, 64, 128, 1024):
+            settle()
             r = time_mx(mm, 8192, 8192, dev, iters=20)
             r["hbm_frac_of_measured"] = round(r["hbm_gbs"] / peaks["hbm_gbs"], 3)
             extras[f"mxfp8_{mm}x8192x8192"] = r
+        # the MXFP4 block-scaled GEMM (two codes per byte): prefill shape and two of the reference's test shapes
+        extras["mxfp4_8192x14336x8192"] = time_mx(8192, 14336, 8192, dev, iters=5, fp4=True)
+        for mm in (64, 1024):
+            settle()
+            r = time_mx(mm, 8192, 8192, dev, iters=20, fp4=True)
+            r["hbm_frac_of_measured"] = round(r["hbm_gbs"] / peaks["hbm_gbs"], 3)
+            extras[f"mxfp4_{mm}x8192x8192"] = r
         # the grouped (mixture-of-experts) stages: a decode-sized and a prefill-sized batch
         for name, mt, mtile in (("moe_fp8_decode_32tok", 32, 16), ("moe_fp8_prefill_4096tok", 4096, 128)):
+            settle()
             r = time_moe(mt, 4096, 2048, 8, 2, mtile, dev)
             for stage in ("stage1", "stage2"):
                 r[stage]["hbm_frac_of_measured"] = round(r[stage]["hbm_gbs"] / peaks["hbm_gbs"], 3)

@@ -69,15 +69,21 @@ def run_moe(a, dev):
 
 
 def run_mx(a, dev):
+    from flydsl_b200.kernels.gemm.mxfp4_preshuffle import compile_mxfp4_preshuffle_gemm
     from flydsl_b200.kernels.gemm.mxfp8_preshuffle import compile_mxfp8_preshuffle_gemm, shuffle_scale
 
     m, n, k = a.m, a.n, a.k
-    x = (torch.randn(m, k, device=dev) * 64).clamp_(-448, 448).to(torch.float8_e4m3fn)
-    w = shuffle_weight((torch.randn(n, k, device=dev) * 64).clamp_(-448, 448).to(torch.float8_e4m3fn))
+    fp4 = a.op == "mx4"
+    if fp4:  # random E2M1 pairs, two codes per byte
+        x = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device=dev)
+        w = shuffle_weight(torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev))
+    else:
+        x = (torch.randn(m, k, device=dev) * 64).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        w = shuffle_weight((torch.randn(n, k, device=dev) * 64).clamp_(-448, 448).to(torch.float8_e4m3fn))
     sa = shuffle_scale(torch.randint(120, 130, (m, k // 32), dtype=torch.uint8, device=dev))
     sw = shuffle_scale(torch.randint(120, 130, (n, k // 32), dtype=torch.uint8, device=dev))
     c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-    fn = compile_mxfp8_preshuffle_gemm(N=n, K=k)
+    fn = compile_mxfp4_preshuffle_gemm(N=n, K=k) if fp4 else compile_mxfp8_preshuffle_gemm(N=n, K=k)
     args = (c.view(-1), x.view(torch.uint8).view(-1), w.view(torch.uint8).view(-1), sa, sw, None, m, n, torch.cuda.current_stream())
     fn(*args)
     torch.cuda.synchronize()
@@ -88,8 +94,8 @@ def run_mx(a, dev):
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / a.iters
-    byts = m * k + n * k + 2 * m * n + (m + n) * (k // 32)
-    print(json.dumps({"op": "mx", "M": m, "N": n, "K": k, "us": round(us, 2), "tflops": round(2.0 * m * n * k / us / 1e6, 1),
+    byts = (m + n) * (k // 2 if fp4 else k) + 2 * m * n + (m + n) * (k // 32)
+    print(json.dumps({"op": a.op, "M": m, "N": n, "K": k, "us": round(us, 2), "tflops": round(2.0 * m * n * k / us / 1e6, 1),
                       "gbs": round(byts / us / 1e3, 1), "status": _lib.read_status()}))
 
 
@@ -101,10 +107,10 @@ def main():
     ap.add_argument("--dtype", default="fp8", choices=["fp8", "int8"])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--hint", type=lambda s: int(s, 0), default=0)
-    ap.add_argument("--op", default="gemm", choices=["gemm", "quant", "shuffle", "moe1", "moe2", "mx"],
+    ap.add_argument("--op", default="gemm", choices=["gemm", "quant", "shuffle", "moe1", "moe2", "mx", "mx4"],
                     help="gemm (default), quant: per-token quantiser on [m, k] bf16, shuffle: weight preshuffle of [n, k], "
                     "moe1 / moe2: mixture-of-experts stage 1 / 2 with m tokens, inter_dim n and model_dim k, "
-                    "mx: MXFP8 block-scaled GEMM")
+                    "mx / mx4: MXFP8 / MXFP4 block-scaled GEMM")
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--topk", type=int, default=2)
     ap.add_argument("--tile-m", type=int, default=128)
@@ -112,7 +118,7 @@ def main():
     dev = torch.device("cuda:0")
     if a.op in ("moe1", "moe2"):
         return run_moe(a, dev)
-    if a.op == "mx":
+    if a.op in ("mx", "mx4"):
         return run_mx(a, dev)
     if a.op != "gemm":
         from flydsl_b200.utils import pertoken_quant_kernel

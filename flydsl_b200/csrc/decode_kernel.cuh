@@ -29,8 +29,9 @@ constexpr int MAX_CLUSTER_SPLIT = 8;
 struct DecodeLayout {
   int off_w, off_a, off_bar, off_misc, off_sa, off_sf, total;
 };
-// `mx`: reserve per stage the scale atoms of the block-scaled kind (weights, tokens).
-__host__ __device__ inline DecodeLayout decode_layout(int bn, int stages, int w_rows = BLOCK_ROWS, bool mx = false) {
+// `sf_atoms`: 512-byte scale atoms that ride along with every stage in the block-scaled
+// kinds (weights then tokens): 2 for 8-bit codes, 4 for packed 4-bit codes, else 0.
+__host__ __device__ inline DecodeLayout decode_layout(int bn, int stages, int w_rows = BLOCK_ROWS, int sf_atoms = 0) {
   DecodeLayout l;
   l.off_w = 0;
   l.off_a = stages * w_rows * KBLOCK_BYTES;
@@ -40,9 +41,9 @@ __host__ __device__ inline DecodeLayout decode_layout(int bn, int stages, int w_
   l.off_sa = l.off_misc + 32;
   l.total = l.off_sa + bn * 4;
   l.off_sf = 0;
-  if (mx) {
+  if (sf_atoms > 0) {
     l.off_sf = (l.total + 15) & ~15;
-    l.total = l.off_sf + stages * 2 * MX_SF_ATOM;
+    l.total = l.off_sf + stages * sf_atoms * MX_SF_ATOM;
   }
   return l;
 }
@@ -170,10 +171,28 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = smem_u32(smem_raw);
   const int stages = p.stages;
-  constexpr bool MX = KIND == KIND_MXF8;  // block-scaled: two 512-byte scale atoms ride along with every stage
+  // block-scaled kinds: scale atoms ride along with every stage - per operand one atom per 128
+  // elements of K, i.e. one for 8-bit codes and two (HALVES) for packed 4-bit codes
+  constexpr bool MX = KIND == KIND_MXF8 || KIND == KIND_MXF4;
+  constexpr int HALVES = KIND == KIND_MXF4 ? 2 : 1;
+  constexpr int SF_ATOMS = MX ? 2 * HALVES : 0;
   static_assert(!MX || (WROWS == BLOCK_ROWS && BN <= 128), "MX kind: 128-channel tiles, at most 128 tokens");
-  const DecodeLayout L = decode_layout(BN, stages, WROWS, MX);
-  constexpr uint32_t SF_BYTES = MX ? 2 * MX_SF_ATOM : 0;
+  const DecodeLayout L = decode_layout(BN, stages, WROWS, SF_ATOMS);
+  constexpr uint32_t SF_BYTES = SF_ATOMS * MX_SF_ATOM;
+  // scale atoms of k-block kb of this CTA -> shared memory at `sf`: [weights h = 0..HALVES-1][tokens h = 0..HALVES-1]
+  auto load_scale_atoms = [&](uint32_t sf, int kb, uint32_t bar, uint64_t pol_w_, uint64_t pol_a_, bool weights, bool tokens) {
+    if constexpr (MX) {
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        const size_t ekb = static_cast<size_t>(kb) * HALVES + h;  // 128-ELEMENT k-block of the scale images
+        if (weights)
+          bulk_load_1d(sf + h * MX_SF_ATOM, p.sf_w + (ekb * (p.N / BLOCK_ROWS) + blockIdx.x) * MX_SF_ATOM, MX_SF_ATOM, bar,
+                       pol_w_);
+        if (tokens)
+          bulk_load_1d(sf + (HALVES + h) * MX_SF_ATOM, p.sf_a + ekb * p.sf_a_tiles * MX_SF_ATOM, MX_SF_ATOM, bar, pol_a_);
+      }
+    }
+  };
   constexpr int W_STAGE = WROWS * KBLOCK_BYTES;
   constexpr int A_STAGE = BN * KBLOCK_BYTES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L.off_misc);
@@ -258,27 +277,23 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
       mbar_expect_tx(bar_full + 8 * i, A_STAGE + w_bytes + SF_BYTES);
       bulk_load_1d(smem_base + L.off_w + i * W_STAGE,
                    p.w + (static_cast<size_t>(kb_begin + i) * p.N + n0) * KBLOCK_BYTES, w_bytes, bar_full + 8 * i, pol_w);
-      if constexpr (MX)
-        bulk_load_1d(smem_base + L.off_sf + i * 2 * MX_SF_ATOM,
-                     p.sf_w + (static_cast<size_t>(kb_begin + i) * (p.N / BLOCK_ROWS) + blockIdx.x) * MX_SF_ATOM, MX_SF_ATOM,
-                     bar_full + 8 * i, pol_w);
+      load_scale_atoms(smem_base + L.off_sf + i * SF_BYTES, kb_begin + i, bar_full + 8 * i, pol_w, pol_a, true, false);
     }
     if (p.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < pre; ++i) {
       tma_load_2d(smem_base + L.off_a + i * A_STAGE, &tmA, bar_full + 8 * i, (kb_begin + i) * KBLOCK_BYTES, m_base, pol_a);
-      if constexpr (MX)
-        bulk_load_1d(smem_base + L.off_sf + i * 2 * MX_SF_ATOM + MX_SF_ATOM,
-                     p.sf_a + static_cast<size_t>(kb_begin + i) * p.sf_a_tiles * MX_SF_ATOM, MX_SF_ATOM, bar_full + 8 * i, pol_a);
+      load_scale_atoms(smem_base + L.off_sf + i * SF_BYTES, kb_begin + i, bar_full + 8 * i, pol_w, pol_a, false, true);
     }
   }
   // Two accumulators (columns [0, BN) and [BN, 2 BN)): even k-blocks are issued by
   // warp 1 into the first, odd k-blocks by warp 6 into the second, so that the
   // ~290 cycles one thread needs to issue a k-block's MMAs are spent by two
   // threads in parallel; the epilogue adds the two.
-  // MX kind: 8 more columns per ring stage (at most 8 stages) for the scale atoms in flight
+  // MX kinds: 4 more columns per scale atom and ring stage (at most 8 stages) for the atoms in flight
   constexpr int MX_MAX_STAGES = 8;
   constexpr uint32_t SF_COL0 = 2 * BN;
-  constexpr uint32_t TMEM_NEED = 2 * BN + (MX ? 8 * MX_MAX_STAGES : 0);
+  constexpr uint32_t SF_COLS = 4 * SF_ATOMS;  // TMEM columns of one stage's scale atoms
+  constexpr uint32_t TMEM_NEED = 2 * BN + SF_COLS * MX_MAX_STAGES;
   constexpr uint32_t TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -312,12 +327,7 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
         bulk_load_1d(smem_base + L.off_w + stage * W_STAGE, p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES,
                      w_bytes, fb, pol_w);
         tma_load_2d(smem_base + L.off_a + stage * A_STAGE, &tmA, fb, kb * KBLOCK_BYTES, m_base, pol_a);
-        if constexpr (MX) {
-          const uint32_t sf = smem_base + L.off_sf + stage * 2 * MX_SF_ATOM;
-          bulk_load_1d(sf, p.sf_w + (static_cast<size_t>(kb) * (p.N / BLOCK_ROWS) + blockIdx.x) * MX_SF_ATOM, MX_SF_ATOM, fb,
-                       pol_w);
-          bulk_load_1d(sf + MX_SF_ATOM, p.sf_a + static_cast<size_t>(kb) * p.sf_a_tiles * MX_SF_ATOM, MX_SF_ATOM, fb, pol_a);
-        }
+        load_scale_atoms(smem_base + L.off_sf + stage * SF_BYTES, kb, fb, pol_w, pol_a, true, true);
         ++issued;
         if (++stage == stages) {
           stage = 0;
@@ -359,17 +369,33 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
         const uint64_t adesc = umma_desc_sw128_kmajor(smem_base + L.off_a + stage * A_STAGE);
         if constexpr (MX) {
           // scale atoms of this stage -> their TMEM columns; the weights are the M-side operand here
-          const uint32_t sfw_t = tmem_base + SF_COL0 + static_cast<uint32_t>(stage * 8);
-          const uint32_t sfa_t = sfw_t + 4;
-          const uint32_t sf = smem_base + L.off_sf + stage * 2 * MX_SF_ATOM;
-          tmem_cp_sf(sfw_t, sf_smem_desc(sf));
-          tmem_cp_sf(sfa_t, sf_smem_desc(sf + MX_SF_ATOM));
-          constexpr uint32_t mx_idesc = umma_idesc_mxf8(WROWS, BN);
+          const uint32_t sfw_t = tmem_base + SF_COL0 + static_cast<uint32_t>(stage) * SF_COLS;
+          const uint32_t sfa_t = sfw_t + 4 * HALVES;
+          const uint32_t sf = smem_base + L.off_sf + stage * SF_BYTES;
 #pragma unroll
-          for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
-            const uint32_t id = mx_idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
-            umma_mxf8(d_tmem, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
-                      adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), id, sfw_t, sfa_t, (kb >= 2 || k != 0) ? 1u : 0u);
+          for (int h = 0; h < HALVES; ++h) {
+            tmem_cp_sf(sfw_t + 4 * h, sf_smem_desc(sf + h * MX_SF_ATOM));
+            tmem_cp_sf(sfa_t + 4 * h, sf_smem_desc(sf + (HALVES + h) * MX_SF_ATOM));
+          }
+          if constexpr (KIND == KIND_MXF4) {
+            constexpr uint32_t mx_idesc = umma_idesc_mxf4(WROWS, BN);
+#pragma unroll
+            for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
+              // 32 bytes = 64 elements = scale blocks 2k, 2k+1: atom k/2, bytes 2(k%2) and 2(k%2)+1 of its columns
+              const uint32_t sf_id = static_cast<uint32_t>((k & 1) * 2);
+              const uint32_t id = mx_idesc | (sf_id << 4) | (sf_id << 29);
+              umma_mxf4(d_tmem, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                        adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), id, sfw_t + 4 * (k >> 1), sfa_t + 4 * (k >> 1),
+                        (kb >= 2 || k != 0) ? 1u : 0u);
+            }
+          } else {
+            constexpr uint32_t mx_idesc = umma_idesc_mxf8(WROWS, BN);
+#pragma unroll
+            for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
+              const uint32_t id = mx_idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29);
+              umma_mxf8(d_tmem, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
+                        adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), id, sfw_t, sfa_t, (kb >= 2 || k != 0) ? 1u : 0u);
+            }
           }
         } else {
 #pragma unroll

@@ -640,9 +640,10 @@ int static_scratch_address(void** out) {
 
 namespace flyb200 {
 namespace host {
-// MXFP8 GEMM for up to 128 tokens on the small-M (weight-streaming) kernel.
+// Block-scaled GEMM (MXFP8, or MXFP4 with `fp4`) for up to 128 tokens on the small-M (weight-streaming)
+// kernel; K = bytes of codes per row.
 int gemm_mx_small(void* c, const void* a, const void* w, const void* sf_a, const void* sf_w, int M, int N, int K,
-                  int outmode, void* stream) {
+                  int outmode, bool fp4, void* stream) {
   DeviceState* st = nullptr;
   int rc = device_state(&st);
   if (rc) return rc;
@@ -675,7 +676,8 @@ int gemm_mx_small(void* c, const void* a, const void* w, const void* sf_a, const
                 plan.bn);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return host::launch_decode_kind(KIND_MXF8, outmode == OUT_FP16 ? OUT_FP16 : OUT_BF16, plan.bn, plan.w_rows, tmA, p, s);
+  return host::launch_decode_kind(fp4 ? KIND_MXF4 : KIND_MXF8, outmode == OUT_FP16 ? OUT_FP16 : OUT_BF16, plan.bn, plan.w_rows, tmA,
+                                  p, s);
 }
 int byte_matrix_map(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
   return make_map(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, row_bytes, rows, KBLOCK_BYTES, box_rows);

@@ -14,9 +14,10 @@ int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
   auto kernel = gemm_decode_kernel<KIND, BN, OUTMODE, WROWS>;
   int rc = ensure_smem(kernel, SMEM_LIMIT, done);
   if (rc) return rc;
-  const DecodeLayout L = decode_layout(BN, p.stages, WROWS, KIND == KIND_MXF8);
+  constexpr int SF_ATOMS = KIND == KIND_MXF8 ? 2 : KIND == KIND_MXF4 ? 4 : 0;
+  const DecodeLayout L = decode_layout(BN, p.stages, WROWS, SF_ATOMS);
   if (L.total > SMEM_LIMIT || BN * BLOCK_ROWS * 4 > L.off_bar) return FLYB200_E_UNSUPPORTED;
-  if (KIND == KIND_MXF8 && p.stages > 8) return FLYB200_E_UNSUPPORTED;  // scale columns in TMEM for 8 stages
+  if (SF_ATOMS > 0 && p.stages > 8) return FLYB200_E_UNSUPPORTED;  // scale columns in TMEM for 8 stages
   if (WROWS != BLOCK_ROWS && p.reduce_mode != REDUCE_NONE) return FLYB200_E_UNSUPPORTED;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -46,7 +47,7 @@ int launch_decode(const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
 
 template <int KIND, int OUTMODE>
 int launch_decode_bn(int bn, int w_rows, const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s) {
-  if constexpr (KIND == KIND_MXF8) {  // block-scaled kind: 128-channel tiles, up to 128 tokens
+  if constexpr (KIND == KIND_MXF8 || KIND == KIND_MXF4) {  // block-scaled kinds: 128-channel tiles, up to 128 tokens
     if (w_rows != BLOCK_ROWS) return FLYB200_E_UNSUPPORTED;
     switch (bn) {
       case 16: return launch_decode<KIND, 16, OUTMODE>(tmA, p, s);
@@ -99,6 +100,10 @@ int launch_decode_kind(int kind, int outmode, int bn, int w_rows, const CUtensor
     case KIND_MXF8:
       if (outmode == OUT_BF16) return launch_decode_bn<KIND_MXF8, OUT_BF16>(bn, w_rows, tmA, p, s);
       if (outmode == OUT_FP16) return launch_decode_bn<KIND_MXF8, OUT_FP16>(bn, w_rows, tmA, p, s);
+      break;
+    case KIND_MXF4:
+      if (outmode == OUT_BF16) return launch_decode_bn<KIND_MXF4, OUT_BF16>(bn, w_rows, tmA, p, s);
+      if (outmode == OUT_FP16) return launch_decode_bn<KIND_MXF4, OUT_FP16>(bn, w_rows, tmA, p, s);
       break;
   }
   return FLYB200_E_UNSUPPORTED;

@@ -76,7 +76,7 @@ int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* s
     const char* e = getenv("FLYB200_MX_SMALL");
     if (M <= 128 && !(e && e[0] == '0'))
       return host::gemm_mx_small(c, a, w_shuf, scale_a_image, scale_w_image, M, N, K,
-                                 out_dtype == FLYB200_OUT_FP16 ? 1 : 0, stream);
+                                 out_dtype == FLYB200_OUT_FP16 ? 1 : 0, false, stream);
   }
   MxParams p;
   memset(&p, 0, sizeof(p));
@@ -119,6 +119,13 @@ int flyb200_gemm_mxfp4(void* c, const void* a, const void* w_shuf, const void* s
   if (!aligned16(c) || !aligned16(a) || !aligned16(w_shuf) || !aligned16(scale_a_image) || !aligned16(scale_w_image))
     return FLYB200_E_BAD_ALIGN;
   if (M == 0) return FLYB200_OK;
+  // up to 128 tokens: a weight stream (half the bytes of 8-bit codes), run by the small-M kernel
+  {
+    const char* e = getenv("FLYB200_MX_SMALL");
+    if (M <= 128 && !(e && e[0] == '0'))
+      return host::gemm_mx_small(c, a, w_shuf, scale_a_image, scale_w_image, M, N, K / 2,
+                                 out_dtype == FLYB200_OUT_FP16 ? 1 : 0, true, stream);
+  }
   MxParams p;
   memset(&p, 0, sizeof(p));
   p.w = static_cast<const uint8_t*>(w_shuf);

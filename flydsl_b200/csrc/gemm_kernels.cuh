@@ -82,6 +82,11 @@ struct KindTraits<KIND_MXF8> {  // E4M3 codes with E8M0 block scales: fp32 accum
   static constexpr bool is_int = false;
 };
 template <>
+struct KindTraits<KIND_MXF4> {  // packed E2M1 codes with E8M0 block scales
+  static constexpr uint32_t dfmt = 1, abfmt = 1;
+  static constexpr bool is_int = false;
+};
+template <>
 struct KindTraits<KIND_F16> {
   static constexpr uint32_t dfmt = 1, abfmt = 0;
   static constexpr bool is_int = false;

@@ -235,7 +235,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t dfmt, uint32_t abfmt,
   return (dfmt << 4) | (abfmt << 7) | (abfmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-enum : int { KIND_F8 = 0, KIND_I8 = 1, KIND_F16 = 2, KIND_BF16 = 3, KIND_MXF8 = 4 };
+enum : int { KIND_F8 = 0, KIND_I8 = 1, KIND_F16 = 2, KIND_BF16 = 3, KIND_MXF8 = 4, KIND_MXF4 = 5 };
 
 template <int KIND>
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,

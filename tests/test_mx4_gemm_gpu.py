@@ -117,3 +117,31 @@ def test_both_tile_shapes(dev, monkeypatch, shape, m, n, k):
     monkeypatch.setenv("FLYB200_MX_BN", shape)
     a_q, sa, b_q, sb = mx_oracle.make_inputs_fp4(m, n, k, seed=m + k)
     check(run(dev, a_q, sa, b_q, sb), mx_oracle.mx4_gemm(a_q, sa, b_q, sb))
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 1024, 2048), (128, 512, 1024), (5, 256, 256), (64, 8192, 8192), (100, 384, 4096)])
+def test_small_m_kernel_and_large_m_kernel_agree(dev, monkeypatch, m, n, k):
+    """Up to 128 tokens run the weight-streaming kernel (FLYB200_MX_SMALL=0 forces the other one)."""
+    a_q, sa, b_q, sb = mx_oracle.make_inputs_fp4(m, n, k, seed=3 * m + k)
+    small = run(dev, a_q, sa, b_q, sb)
+    monkeypatch.setenv("FLYB200_MX_SMALL", "0")
+    large = run(dev, a_q, sa, b_q, sb)
+    ref = mx_oracle.mx4_gemm(a_q, sa, b_q, sb)
+    check(small, ref)
+    check(large, ref)
+
+
+def test_small_m_kernel_scale_probe(dev):
+    """The which-scale-meets-which-block probe on the weight-streaming kernel (16 tokens)."""
+    m, n, k = 16, 256, 1024
+    blocks = k // 32
+    ones_a = torch.full((m, k // 2), 0x22, dtype=torch.uint8)
+    ones_w = torch.full((n, k // 2), 0x22, dtype=torch.uint8)
+    sa = torch.full((m, blocks), 127 - 20, dtype=torch.uint8)
+    sa[torch.arange(m), (torch.arange(m) * 5) % blocks] = (127 + torch.arange(m) % 8).to(torch.uint8)
+    sw = torch.full((n, blocks), 127 - 20, dtype=torch.uint8)
+    sw[torch.arange(n), (torch.arange(n) * 3) % blocks] = (127 + torch.arange(n) % 6).to(torch.uint8)
+    flat_a = torch.full((m, blocks), 127, dtype=torch.uint8)
+    flat_w = torch.full((n, blocks), 127, dtype=torch.uint8)
+    check(run(dev, ones_a, sa, ones_w, flat_w), mx_oracle.mx4_gemm(ones_a, sa, ones_w, flat_w))
+    check(run(dev, ones_a, flat_a, ones_w, sw), mx_oracle.mx4_gemm(ones_a, flat_a, ones_w, sw))
