@@ -128,15 +128,26 @@ class _MoeStage:
         self._slot_major = stage == 1 and in_dtype == "int8smooth"
         self._gather_mode = (2 if self._slot_major else 0) if stage == 1 else 1  # how a sorted row finds its activation row
         self._scratch: dict = {}
+        self._retired: list = []
 
-    def _sorted_buffers(self, device, rows):
-        buf = self._scratch.get(device.index)
+    def _sorted_buffers(self, device, rows, stream=0):
+        """Gathered activation rows and their scales, one pair per (device, stream): two launches
+        on different streams must not share them.  A buffer that has to grow is replaced but
+        never freed (a kernel still running or a captured graph may hold its address), and
+        growing inside a stream capture is refused: run the shape once before capturing."""
+        key = (device.index, stream or 0)
+        buf = self._scratch.get(key)
         if buf is None or buf[0].shape[0] < rows:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("moe_gemm: the gather scratch for this shape does not exist yet; call the launcher "
+                                   "once on this stream before capturing a CUDA graph")
+            if buf is not None:
+                self._retired.append(buf)
             buf = (
                 torch.empty((rows, self._k), dtype=torch.uint8, device=device),
                 torch.empty((rows,), dtype=torch.float32, device=device),
             )
-            self._scratch[device.index] = buf
+            self._scratch[key] = buf
         return buf
 
     def __call__(
@@ -208,7 +219,7 @@ class _MoeStage:
         lib = _lib.load()
         s = _stream_handle(stream) or None
         rows = blocks * self.tile_m
-        a_sorted, sa_sorted = self._sorted_buffers(dev, rows)
+        a_sorted, sa_sorted = self._sorted_buffers(dev, rows, s)
         a_ptr, sa_ptr, ids_ptr, nv_ptr = a_sorted.data_ptr(), sa_sorted.data_ptr(), sorted_token_ids.data_ptr(), num_valid_ids.data_ptr()
         rc = lib.flyb200_moe_gather_rows(a_ptr, sa_ptr, x.data_ptr(), scale_x.data_ptr(), ids_ptr, nv_ptr, tokens, self.topk,
                                          self._gather_mode, self._k, rows, s)

@@ -116,6 +116,43 @@ def test_cta_pair_kernel_scaled_output(dev, in_dtype, m, n, k):
     check_scaled(c, a_q, b_q, sa, sb, m)
 
 
+def test_first_captured_call_allocates_nothing_when_compiled(dev):
+    """A narrow-N shape reduces its K splits through a global workspace.  flyc.compile allocates
+    that workspace for the stream it is given, so the launcher's very first call may be a captured
+    one; without compile a first call inside a capture is refused with a clear message instead of
+    allocating behind the capture."""
+    m, n, k = 16, 1024, 8192
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "fp8", seed=77)
+    s = torch.cuda.Stream()
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype="fp8")
+    assert fn.plan(m)["reduce"] == 1 and fn.workspace_bytes(dev) > 16384  # the workspace path
+    c = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+    args = (c.view(-1), as_i8(a_q.to(dev)).view(-1), as_i8(shuffle_weight(b_q.to(dev))).view(-1), sa.to(dev), sb.to(dev),
+            torch.empty(0, dtype=torch.bfloat16, device=dev), m, n, s)
+    torch.cuda.synchronize()
+    # (1) not compiled, first call under capture: refused
+    g0 = torch.cuda.CUDAGraph()
+    with pytest.raises(RuntimeError, match="before capturing"):
+        with torch.cuda.graph(g0, stream=s):
+            fn(*args)
+    torch.cuda.synchronize()
+    # (2) compiled on the capture stream: the first call is the captured one and allocates nothing
+    fn2 = compile_preshuffle_gemm(N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype="fp8")
+    cf = flyc.compile(fn2, *args)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated(dev)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        cf(*args)
+    assert torch.cuda.memory_allocated(dev) == before
+    c.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    ref = oracle.run_torch(a_q, b_q, sa, sb)
+    assert oracle.strict_mismatches(c.float().cpu(), ref, RTOL, ATOL) == 0
+
+
 # --- INT8: accumulators bit-exact before scaling
 
 
