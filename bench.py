@@ -734,8 +734,7 @@ def main():
         configs = {}
         for name, em, en, ek, edt, ews, eseed, bound, static_too in cases:
             iters = 20 if em <= 4096 and en <= 8192 else 5
-            if bound == "hbm":
-                settle()
+            settle()  # every case starts from the same idle state, not from the throttled end of the previous one
             us, copies = time_config(em, en, ek, edt, dev, iters=iters, seed=eseed, weight_scale=ews)
             by = gemm_bytes(em, en, ek)
             tf = 2.0 * em * en * ek / us / 1e6
