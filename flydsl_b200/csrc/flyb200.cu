@@ -150,7 +150,7 @@ int make_window_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, ui
 
 // Ring depth of the small-M kernel: as deep as ~200 KB of shared memory allow, at most 12.
 inline int default_decode_stages(int bn, int w_rows = BLOCK_ROWS) {
-  if (w_rows == BLOCK_ROWS) return bn <= 32 ? 8 : (bn <= 128 ? 6 : 4);
+  if (w_rows == BLOCK_ROWS) return bn <= 64 ? 8 : (bn <= 128 ? 6 : 4);
   const int stage = (w_rows + bn) * KBLOCK_BYTES;
   int n = 200 * 1024 / stage;
   return n > 12 ? 12 : (n < 2 ? 2 : n);
