@@ -148,3 +148,35 @@ def test_cta_pair_kernel_matches_single_cta_kernel_at_full_size():
     torch.cuda.synchronize()
     assert device_status() == 0
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize(
+    "m,n,k",
+    [
+        (65536, 1024, 1024),  # the largest M the reference's launcher can address (its views use M_max = 65536)
+        (40, 16, 128),  # the smallest weight image: 16 channels, one k-block
+        (300, 16, 128),  # the same through the large-M kernel
+        (7, 256, 65536),  # a very long K: 512 k-blocks per channel tile
+        (1000, 57344, 256),  # many channel tiles, short K (int32 tile counters, ragged last row tile)
+    ],
+)
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+def test_extreme_shapes(m, n, k, in_dtype):
+    dev = torch.device("cuda:0")
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=m + n + k)
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=128, tile_n=256, tile_k=128, in_dtype=in_dtype)
+    c = torch.full((m + 8, n), -8192.0, dtype=torch.bfloat16, device=dev)
+    bias = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    fn(c.view(-1), as_i8(a_q.to(dev)).view(-1), as_i8(shuffle_weight(b_q.to(dev))).view(-1), sa.to(dev).view(-1),
+       sb.to(dev).view(-1), bias, m, n, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert device_status() == 0
+    assert int((c[m:] != -8192.0).sum().item()) == 0
+    gen = torch.Generator().manual_seed(1)
+    pick = torch.cat([torch.tensor([0, m // 2, m - 1]), torch.randint(0, m, (61,), generator=gen)]).unique() if m > 64 else torch.arange(m)
+    ref = oracle.run_torch(a_q[pick], b_q, sa[pick], sb)
+    got = c[pick.to(dev)].float().cpu()
+    # a K of 65536 sums 64 times more terms than the benchmark shapes: the absolute floor scales with the result's size
+    atol = max(ATOL, 1e-2 * float(ref.abs().max()) / 16) if k > 8192 else ATOL
+    bad = oracle.strict_mismatches(got, ref, RTOL, atol)
+    assert bad == 0, f"{bad} mismatches; max abs diff {(got - ref).abs().max()}"
