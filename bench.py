@@ -686,7 +686,9 @@ def main():
     med_ms = statistics.median(kernel_ms)
     flops_launch = 2.0 * m * nl * k
     achieved = flops_launch / (med_ms * 1e-3) / 1e12
-    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    fp8_peak = 2.0 * peaks["bf16_tflops"]  # burst: the denominator of the short cases in roofline.configs
+    # the timed steps run after half a second at the power cap: the matching measured figure is the sustained one
+    fp8_peak_sustained = 2.0 * (peaks["bf16_sustained"] or peaks["bf16_tflops"])
     plan = op.launch.plan(m)
     group_m = (args.hint >> 16) & 0xFF or 32
     traffic = None
@@ -703,10 +705,13 @@ def main():
         "bound": "tensor",
         "kernel": f"gemm_rows_kernel<fp8> (tcgen05 kind::f8f6f4, 128x{plan['bn']} tiles, persistent, {plan['stages']} stages)",
         "achieved": achieved,
-        "peak": fp8_peak,
+        "peak": fp8_peak_sustained,
         "unit": "TFLOP/s",
-        "frac": achieved / fp8_peak,
-        "peak_source": f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no FP8 figure is measured",
+        "frac": achieved / fp8_peak_sustained,
+        "peak_source": f"2 x {peaks['source']} dense bf16 SUSTAINED ({peaks['bf16_sustained']} TFLOP/s; the kernel is timed after "
+                       f"~0.5 s at the power cap): no FP8 figure is measured.  Against 2 x the bf16 burst figure "
+                       f"({peaks['bf16_tflops']}): frac_of_2x_bf16_burst",
+        "frac_of_2x_bf16_burst": achieved / fp8_peak,
         "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
         "traffic": traffic,
         "traffic_note": traffic_note,

@@ -437,6 +437,15 @@ def test_automatic_tile_width_fills_whole_rounds():
     assert _lib.describe_plan(16384, 57344, 8192, "fp8", 0, 148)["bn"] == 256
 
 
+def test_reference_example_fp16_4096_cubed():
+    """The reference's own example (examples/04-preshuffle_gemm.py): fp16 4096^3 with its tolerance."""
+    from flydsl_b200.examples.preshuffle_gemm import run
+
+    ok, violation, _ = run(4096, 4096, 4096)
+    assert ok, f"max violation of 1e-3 + 1e-3*|expected|: {violation}"
+    assert device_status() == 0
+
+
 # --- failure path: a bounded device-side wait that cannot succeed
 
 
