@@ -419,6 +419,39 @@ def time_mx(m, n, k, dev, iters=10, fp4=False):
             "algorithmic_bytes": int(byts), "rotating_copies": copies}
 
 
+def time_mx_mixed(m, n, k, dev, iters=10):
+    """Device time of the MXFP6-activation x MXFP4-weight GEMM through its launcher (the call includes the
+    launcher's per-call conversion of the activations from the reference's layout to byte containers);
+    algorithmic bytes as in the reference's test (tests/kernels/test_preshuffle_gemm.py:582-583)."""
+    from flydsl_b200.kernels.gemm.mxfp4_preshuffle import compile_mxfp4_preshuffle_gemm, shuffle_scale_w4, shuffle_weight_w4
+
+    g = torch.Generator(device=dev).manual_seed(79)
+    a_pad = torch.randint(0, 256, (m, k // 32, 32), generator=g, dtype=torch.uint8, device=dev)
+    a_pad[:, :, 24:] = 0  # per 32 elements: 24 bytes of packed 6-bit codes + 8 zero bytes
+    a_pad = a_pad.view(m, k)
+    w = shuffle_weight_w4(torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8, device=dev), 16, False, False,
+                          for_a_dtype="fp6")
+    sa = shuffle_scale_w4(torch.randint(120, 130, (m, k // 32), generator=g, dtype=torch.uint8, device=dev), 1, False)
+    sw = shuffle_scale_w4(torch.randint(120, 130, (n, k // 32), generator=g, dtype=torch.uint8, device=dev), 1, False)
+    c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    fn = compile_mxfp4_preshuffle_gemm(N=n, K=k, a_dtype="fp6", b_dtype="fp4")
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            fn(c.view(-1), a_pad.view(-1), w.view(-1), sa, sw, None, m, n, st)
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(iters):
+            fn(c.view(-1), a_pad.view(-1), w.view(-1), sa, sw, None, m, n, st)
+        e1.record(st)
+        st.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    byts = m * k + n * k // 2 + 2 * m * n + (m + n) * (k // 32)
+    return {"us": round(us, 2), "tflops": round(2.0 * m * n * k / us / 1e6, 1), "algorithmic_bytes": int(byts),
+            "note": "eager launches incl. the activation layout conversion; weights travel in byte containers (N*K bytes)"}
+
+
 def time_moe(tokens, model_dim, inter_dim, experts, topk, tile_m, dev, iters=20):
     """Device time of the two mixture-of-experts GEMM stages (activation gather
     included) on seeded synthetic routing, with the algorithmic bytes of the
@@ -827,6 +860,7 @@ def main():
             r = time_mx(mm, 8192, 8192, dev, iters=20, fp4=True)
             r["hbm_frac_of_measured"] = round(r["hbm_gbs"] / peaks["hbm_gbs"], 3)
             extras[f"mxfp4_{mm}x8192x8192"] = r
+        extras["mxfp6_x_mxfp4_4096x8192x8192"] = time_mx_mixed(4096, 8192, 8192, dev)
         # the grouped (mixture-of-experts) stages: a decode-sized and a prefill-sized batch
         for name, mt, mtile in (("moe_fp8_decode_32tok", 32, 16), ("moe_fp8_prefill_4096tok", 4096, 128)):
             settle()

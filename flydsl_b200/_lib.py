@@ -54,6 +54,7 @@ SIGNATURES = {
     "flyb200_moe_reduce": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp]),
     "flyb200_moe_sorting": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flyb200_gemm_mxfp8": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "flyb200_gemm_mx_mixed": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "flyb200_gemm_mxfp4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "flyb200_mx_scale_image": (_i, [_vp, _vp, _i, _i, _vp]),
     "flyb200_mx_scale_image_bytes": (_sz, [_i, _i]),

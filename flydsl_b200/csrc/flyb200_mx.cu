@@ -111,6 +111,43 @@ int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* s
   return launch_mx<MOE_OUT_FP16, 128>(tmA, p, s);
 }
 
+int flyb200_gemm_mx_mixed(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
+                          int M, int N, int K, int a_format, int w_format, int out_dtype, void* stream) {
+  if (!c || !a || !w_shuf || !scale_a_image || !scale_w_image || M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
+  if (out_dtype != FLYB200_OUT_BF16 && out_dtype != FLYB200_OUT_FP16) return FLYB200_E_BAD_ARG;
+  auto known = [](int f) { return f == FLYB200_MXFMT_E4M3 || f == FLYB200_MXFMT_E5M2 || f == FLYB200_MXFMT_E2M3 ||
+                                  f == FLYB200_MXFMT_E3M2 || f == FLYB200_MXFMT_E2M1; };
+  if (!known(a_format) || !known(w_format)) return FLYB200_E_BAD_ARG;
+  if (K % KBLOCK_BYTES != 0 || N % 128 != 0) return FLYB200_E_UNSUPPORTED;
+  if (!aligned16(c) || !aligned16(a) || !aligned16(w_shuf) || !aligned16(scale_a_image) || !aligned16(scale_w_image))
+    return FLYB200_E_BAD_ALIGN;
+  if (M == 0) return FLYB200_OK;
+  MxParams p;
+  memset(&p, 0, sizeof(p));
+  p.w = static_cast<const uint8_t*>(w_shuf);
+  p.sfa = static_cast<const uint8_t*>(scale_a_image);
+  p.sfw = static_cast<const uint8_t*>(scale_w_image);
+  p.c = c;
+  p.M = M;
+  p.N = N;
+  p.K_bytes = K;  // one byte per code: sub-byte codes travel in byte containers
+  p.group_m = 16;
+  p.fmt_bits = (static_cast<uint32_t>(a_format) << 7) | (static_cast<uint32_t>(w_format) << 10);
+  int rc = host::status_word(&p.status);
+  if (rc) return rc;
+  CUtensorMap tmA;
+  rc = host::byte_matrix_map(&tmA, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M), BLOCK_ROWS);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool wide = N % 256 == 0 && K >= 2048;
+  if (wide) {
+    if (out_dtype == FLYB200_OUT_BF16) return launch_mx<MOE_OUT_BF16, 256>(tmA, p, s);
+    return launch_mx<MOE_OUT_FP16, 256>(tmA, p, s);
+  }
+  if (out_dtype == FLYB200_OUT_BF16) return launch_mx<MOE_OUT_BF16, 128>(tmA, p, s);
+  return launch_mx<MOE_OUT_FP16, 128>(tmA, p, s);
+}
+
 int flyb200_gemm_mxfp4(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
                        int M, int N, int K, int out_dtype, void* stream) {
   if (!c || !a || !w_shuf || !scale_a_image || !scale_w_image || M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;

@@ -41,6 +41,7 @@ struct MxParams {
   void* c;
   int M, N, K_bytes;
   int group_m;
+  uint32_t fmt_bits;   // operand formats of kind::mxf8f6f4 as instruction-descriptor bits: (A format << 7) | (B format << 10)
   int* status;
 };
 
@@ -188,7 +189,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
   } else if (warp == 1) {
     // ------------------------------ MMA issue -----------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = FP4 ? umma_idesc_mxf4(BLOCK_ROWS, BN) : umma_idesc_mxf8(BLOCK_ROWS, BN);
+      // 8-bit containers: E4M3 unless the caller names other formats (E2M3 / E2M1 codes padded to a byte)
+      const uint32_t idesc = FP4 ? umma_idesc_mxf4(BLOCK_ROWS, BN) : (umma_idesc_mxf8(BLOCK_ROWS, BN) | p.fmt_bits);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;

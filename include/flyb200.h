@@ -338,6 +338,34 @@ int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* s
  * padded to 8 bits in shared memory, which forfeits the smaller weight stream. */
 int flyb200_gemm_mxfp4(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
                        int M, int N, int K, int out_dtype, void* stream);
+
+/* ---- mixed block-scaled kinds: 8-, 6- and 4-bit codes in byte containers ----
+ * Replaces the configurations of the same reference kernel whose operands
+ * differ in width: MXFP6 (E2M3) activations x MXFP4 (E2M1) weights
+ * (kernels/gemm/mxfp4_preshuffle.py a_dtype = "fp6", b_dtype = "fp4"; pinned by
+ * tests/kernels/test_preshuffle_gemm.py:472-587 test_mfma_a6w4_preshuffle) and
+ * MXFP8 activations x MXFP4 weights (a_dtype = "fp8"; the reference's test
+ * skips it).  Computed with tcgen05.mma kind::mxf8f6f4.block_scale, which takes
+ * sub-byte codes only in byte-sized containers: every 16 consecutive codes of a
+ * row occupy 16 bytes - 16 E4M3 bytes, or 12 bytes of 6-bit codes (code i in
+ * bits [6i, 6i+6) of the little-endian bit stream) followed by 4 bytes of
+ * padding, or 8 bytes of 4-bit codes (code i in nibble i, low nibble first)
+ * followed by 8 bytes of padding.  Both operands are passed in that form, so
+ * the weight stream has the size of FP8's: the memory saving of 4-bit weights
+ * is realised by flyb200_gemm_mxfp4 (both operands 4-bit), not here.
+ *   a              [M, K] bytes, row-major, codes in containers as above
+ *   w_shuf         the [N, K] byte matrix of weight containers in the image of
+ *                  flyb200_shuffle_weight (elem_bytes = 1)
+ *   scale images   as for flyb200_gemm_mxfp8 (K counted in elements)
+ *   a_format, w_format   FLYB200_MXFMT_* below
+ * Requirements: K % 128 == 0, N % 128 == 0, pointers 16-byte aligned. */
+#define FLYB200_MXFMT_E4M3 0
+#define FLYB200_MXFMT_E5M2 1
+#define FLYB200_MXFMT_E2M3 3
+#define FLYB200_MXFMT_E3M2 4
+#define FLYB200_MXFMT_E2M1 5
+int flyb200_gemm_mx_mixed(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
+                          int M, int N, int K, int a_format, int w_format, int out_dtype, void* stream);
 int flyb200_mx_scale_image(void* dst, const void* src, int rows, int K, void* stream);
 size_t flyb200_mx_scale_image_bytes(int rows, int K);
 

@@ -149,3 +149,81 @@ def make_inputs_fp4(m, n, k, seed):
     a_q, sa = per_1x32_f4_quant(a)
     b_q, sb = per_1x32_f4_quant(b)
     return a_q, sa, b_q, sb
+
+
+# ---------------------------------------------------------------------------
+# MXFP6 (E2M3) activations, and the byte containers of the mixed kinds
+# (tests/kernels/utils/gemm_common_utils.py:708-770; reference formula of
+# tests/kernels/test_preshuffle_gemm.py:530-538)
+# Parity status: PINNED by tests/golden/mx_fp6.npz (tests/golden/make_golden_mx6.py ran the
+# reference's per_1x32_f6_quant / pack_fp6_e2m3 / fp6_e2m3_to_f32 and the A6W4 formula on CPU).
+# ---------------------------------------------------------------------------
+def _fp6_magnitudes():
+    v = []
+    for c in range(32):
+        e, m = (c >> 3) & 3, c & 7
+        v.append(m / 8.0 if e == 0 else (2.0 ** (e - 1)) * (1.0 + m / 8.0))
+    return v
+
+
+FP6_VALUES = tuple(_fp6_magnitudes())  # magnitudes of codes 0..31; bit 5 is the sign
+
+
+def f32_to_fp6_codes(x):
+    """E2M3 code (uint8, low 6 bits) of every element: round to nearest, ties to the code with an
+    even mantissa bit, magnitudes of 7.5 and above saturate, sign kept (gemm_common_utils.py:162-276
+    with ebits=2, mbits=3)."""
+    a = x.float().abs()
+    code = torch.zeros_like(a, dtype=torch.int32)
+    for c in range(31):
+        mid = (FP6_VALUES[c] + FP6_VALUES[c + 1]) / 2.0
+        code = code + ((a > mid) | ((a == mid) & bool(c & 1))).to(torch.int32)
+    code = code | (torch.signbit(x.float()).to(torch.int32) << 5)
+    return code.to(torch.uint8)
+
+
+def fp6_to_f32(codes):
+    table = torch.tensor(FP6_VALUES + tuple(-v for v in FP6_VALUES), dtype=torch.float32)
+    return table[(codes & 0x3F).long()]
+
+
+def pack_fp6(codes):
+    """Four 6-bit codes -> three bytes, little-endian bit stream (gemm_common_utils.py:708-721)."""
+    g = codes.to(torch.int32).unflatten(-1, (-1, 4)) & 0x3F
+    e0, e1, e2, e3 = g.unbind(dim=-1)
+    out = torch.stack([((e1 & 3) << 6) | e0, ((e2 & 15) << 4) | (e1 >> 2), (e3 << 2) | (e2 >> 4)], dim=-1).to(torch.uint8)
+    return out.reshape(*codes.shape[:-1], codes.shape[-1] // 4 * 3).contiguous()
+
+
+def per_1x32_f6_quant(x):
+    """(a_pad uint8 [M, K]: per 32 elements 24 bytes of packed codes + 8 zero bytes, scales uint8
+    [M, K/32], codes uint8 [M, K]) (gemm_common_utils.py:744-770)."""
+    m, k = x.shape
+    flat = x.contiguous().view(-1, BLOCK).float()
+    scale = f32_to_e8m0(torch.amax(torch.abs(flat), dim=-1) / 4.0)  # 4 = the largest power of two below 7.5
+    codes = f32_to_fp6_codes(flat / e8m0_to_f32(scale).view(-1, 1)).view(m, k)
+    a_pad = torch.zeros(m, k // BLOCK, BLOCK, dtype=torch.uint8)
+    a_pad[:, :, :24] = pack_fp6(codes).view(m, k // BLOCK, 24)
+    return a_pad.view(m, k), scale.view(m, k // BLOCK), codes
+
+
+def fp6_containers(codes):
+    """6-bit codes [.., K] -> byte containers [.., K]: every 16 codes become 12 packed bytes + 4 zero bytes."""
+    g = pack_fp6(codes).unflatten(-1, (-1, 12))
+    return torch.cat([g, torch.zeros(*g.shape[:-1], 4, dtype=torch.uint8)], dim=-1).flatten(-2).contiguous()
+
+
+def fp4_containers(packed):
+    """packed 4-bit codes [.., K/2] -> byte containers [.., K]: every 16 codes (8 bytes) + 8 zero bytes."""
+    g = packed.view(torch.uint8).unflatten(-1, (-1, 8))
+    return torch.cat([g, torch.zeros_like(g)], dim=-1).flatten(-2).contiguous()
+
+
+def a6w4_gemm(a_codes, scale_a, b_packed, scale_b):
+    """fp32 [M, N] of MXFP6 activations x MXFP4 weights (tests/kernels/test_preshuffle_gemm.py:530-538)."""
+    a = fp6_to_f32(a_codes) * e8m0_to_f32(scale_a).repeat_interleave(BLOCK, dim=-1)
+    return torch.mm(a, dequant_fp4(b_packed, scale_b).T).to(torch.float32)
+
+
+def a8w4_gemm(a_fp8, scale_a, b_packed, scale_b):
+    return torch.mm(dequant(a_fp8, scale_a), dequant_fp4(b_packed, scale_b).T).to(torch.float32)

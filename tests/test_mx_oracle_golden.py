@@ -82,3 +82,33 @@ def test_shipped_fp4_quantiser_matches_reference_fixture():
         codes, scale = per_1x32_f4_quant(t4(x))
         assert torch.equal(codes, t4(q)) and torch.equal(scale, t4(s))
     assert torch.equal(mxfp4_to_f32(torch.arange(256, dtype=torch.uint8).view(1, 256)), t4("table"))
+
+
+# --- MXFP6 activations (E2M3): fixture from the reference's per_1x32_f6_quant / fp6_e2m3_to_f32
+
+Z6 = np.load(os.path.join(os.path.dirname(__file__), "golden", "mx_fp6.npz"))
+
+
+def t6(name):
+    return torch.from_numpy(Z6[name])
+
+
+def test_fp6_rounding_table_quantiser_and_gemm_match_reference():
+    assert torch.equal(mx_oracle.f32_to_fp6_codes(t6("probe")), t6("probe_codes"))
+    assert torch.equal(mx_oracle.fp6_to_f32(torch.arange(64, dtype=torch.uint8)), t6("table"))
+    a_pad, sa, codes = mx_oracle.per_1x32_f6_quant(t6("a"))
+    assert torch.equal(a_pad, t6("a_pad")) and torch.equal(sa, t6("sa")) and torch.equal(codes, t6("a_codes"))
+    assert torch.equal(mx_oracle.a6w4_gemm(t6("a_codes"), t6("sa"), t6("b_q"), t6("sb")), t6("c"))
+
+
+def test_shipped_fp6_helpers_match_reference_fixture():
+    from flydsl_b200.kernels.gemm import mxfp4_preshuffle as mp
+
+    a_pad, sa, codes = mp.per_1x32_f6_quant(t6("a"))
+    assert torch.equal(a_pad, t6("a_pad")) and torch.equal(sa, t6("sa")) and torch.equal(codes, t6("a_codes"))
+    assert torch.equal(mp.fp6_e2m3_to_f32(torch.arange(64, dtype=torch.uint8)), t6("table"))
+    # container forms: what the kernel reads
+    assert torch.equal(mp.fp6_containers_from_padded(t6("a_pad")), mx_oracle.fp6_containers(t6("a_codes")))
+    assert torch.equal(mp.fp4_containers(t6("b_q")), mx_oracle.fp4_containers(t6("b_q")))
+    row = mx_oracle.fp6_containers(t6("a_codes"))[0]
+    assert int(row[12:16].sum()) == 0 and row.numel() == t6("a_codes").shape[1]  # 12 data bytes + 4 padding per 16 codes
