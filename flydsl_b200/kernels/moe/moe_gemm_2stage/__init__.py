@@ -14,8 +14,14 @@ The positional arguments are the reference's
 per expert.  ``tile_m`` is the routing block size the sorted ids were padded
 to; ``tile_n`` / ``tile_k`` are validated as the reference does and are
 otherwise hints (a CTA always takes two 128-channel weight tiles and 128-byte
-k-blocks).  ``in_dtype`` "fp8", "int8" and "int8smooth" are built; "int4"
-(packed W4A8 weights) raises ``ValueError``.
+k-blocks).  ``in_dtype`` "fp8", "int8", "int8smooth" and "int4" are built.  "int4"
+is W4A8 (tests/kernels/test_moe_gemm_2stage.py:64-79,212-220): int8 activations and
+weights quantised to [-8, 7], passed as the preshuffled int8 image packed two
+values per byte (``pack_shuffled_int8_to_packed_int4``).  The tensor core has no
+4-bit integer kind, so the launcher expands a packed weight tensor back to its
+int8 image the first time it sees it (cached by address; ``forget_weights``
+drops an entry) and runs the int8 kernels: same results as the reference, the
+weight stream of int8.
 
 ``moe_sorting`` builds the routing table the kernels consume (layout:
 tests/kernels/test_moe_gemm_2stage.py:99-137): on CUDA tensors with the
@@ -47,7 +53,24 @@ _IN = {
     # int8 with per-route ("smooth-quantised") activations: stage 1 reads x and scale_x
     # slot-major, [topk * tokens, ...] with row = slot * tokens + token; stage 2 is plain int8
     "int8smooth": (_lib.DT_INT8, torch.int8),
+    # W4A8: int8 activations, weights in [-8, 7] passed packed two per byte and expanded once to the int8 image
+    "int4": (_lib.DT_INT8, torch.int8),
 }
+
+
+def pack_shuffled_int8_to_packed_int4(x_shuf_i8: torch.Tensor) -> torch.Tensor:
+    """Pack a preshuffled int8 weight image with values in [-8, 7] two per byte, as the reference's
+    helper does (tests/kernels/test_moe_gemm_2stage.py:64-79): every 8 consecutive values v0..v7
+    become 4 bytes, byte j = (v_j & 15) | (v_{j+4} << 4)."""
+    u = (x_shuf_i8.contiguous().view(-1).to(torch.int16) & 0xF).to(torch.uint8).view(-1, 8)
+    return (u[:, :4] | (u[:, 4:] << 4)).contiguous().view(-1).view(torch.int8)
+
+
+def unpack_packed_int4_to_shuffled_int8(packed: torch.Tensor) -> torch.Tensor:
+    """Inverse of :func:`pack_shuffled_int8_to_packed_int4`: 4 bytes -> 8 sign-extended int8 values."""
+    b = packed.contiguous().view(-1).view(torch.uint8).view(-1, 4)
+    nib = torch.cat([b & 0xF, b >> 4], dim=1).to(torch.int16)  # v0..v3 from the low nibbles, v4..v7 from the high ones
+    return ((nib ^ 8) - 8).to(torch.int8).view(-1)
 _REFERENCE_IN_DTYPES = ("fp8", "int8", "int8smooth", "int4")
 
 
@@ -129,6 +152,25 @@ class _MoeStage:
         self._gather_mode = (2 if self._slot_major else 0) if stage == 1 else 1  # how a sorted row finds its activation row
         self._scratch: dict = {}
         self._retired: list = []
+        self._w4_expanded: dict = {}  # (data_ptr, numel) of a packed int4 weight tensor -> its int8 image
+
+    def _weights_for_kernel(self, w: torch.Tensor, w_elems: int) -> torch.Tensor:
+        """W4A8: a tensor of w_elems / 2 bytes is the packed form; expand it once.  Anything else passes through."""
+        if self.in_dtype != "int4" or w.numel() != w_elems // 2:
+            return w
+        key = (w.data_ptr(), w.numel())
+        img = self._w4_expanded.get(key)
+        if img is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("moe_gemm: packed int4 weights are expanded on first use; call the launcher once "
+                                   "before capturing a CUDA graph")
+            img = unpack_packed_int4_to_shuffled_int8(w)
+            self._w4_expanded[key] = img
+        return img
+
+    def forget_weights(self, w: torch.Tensor) -> None:
+        """Drop the cached int8 image of a packed int4 weight tensor (its contents changed in place)."""
+        self._w4_expanded.pop((w.data_ptr(), w.numel()), None)
 
     def _sorted_buffers(self, device, rows, stream=0):
         """Gathered activation rows and their scales, one pair per (device, stream): two launches
@@ -188,8 +230,12 @@ class _MoeStage:
         x_rows = tokens if (self.stage == 1 and not self._slot_major) else tokens * self.topk
         out_rows = tokens if (self.stage == 2 and self.accumulate) else tokens * self.topk
         w_rows = self.experts * (2 * self.inter_dim if self.stage == 1 else self.model_dim)
+        if self.in_dtype == "int4" and w.numel() == w_rows * k // 2:
+            w_need = w_rows * k // 2  # packed two values per byte
+        else:
+            w_need = w_rows * k
         need = (
-            ("out", out, out_rows * n_out), ("x", x, x_rows * k), ("w", w, w_rows * k),
+            ("out", out, out_rows * n_out), ("x", x, x_rows * k), ("w", w, w_need),
             ("scale_x", scale_x, x_rows), ("scale_w", scale_w, w_rows),
             # the sorted ids are read up to num_valid_ids[0] only, which may end inside the last block
             ("sorted_token_ids", sorted_token_ids, (blocks - 1) * self.tile_m + 1), ("sorted_expert_ids", sorted_expert_ids, blocks),
@@ -219,6 +265,8 @@ class _MoeStage:
         lib = _lib.load()
         s = _stream_handle(stream) or None
         rows = blocks * self.tile_m
+        if self.in_dtype == "int4":
+            w = self._weights_for_kernel(w, self.experts * (2 * self.inter_dim if self.stage == 1 else self.model_dim) * self._k)
         a_sorted, sa_sorted = self._sorted_buffers(dev, rows, s)
         a_ptr, sa_ptr, ids_ptr, nv_ptr = a_sorted.data_ptr(), sa_sorted.data_ptr(), sorted_token_ids.data_ptr(), num_valid_ids.data_ptr()
         rc = lib.flyb200_moe_gather_rows(a_ptr, sa_ptr, x.data_ptr(), scale_x.data_ptr(), ids_ptr, nv_ptr, tokens, self.topk,
@@ -240,7 +288,7 @@ def _check_common(model_dim, inter_dim, experts, topk, tile_m, tile_n, tile_k, i
     if in_dtype not in _REFERENCE_IN_DTYPES:
         raise ValueError(f"in_dtype must be 'fp8', 'int8', 'int8smooth', or 'int4', got {in_dtype!r}")
     if in_dtype not in _IN:
-        raise ValueError(f"in_dtype={in_dtype!r} is not built for B200 (fp8, int8 and int8smooth are)")
+        raise ValueError(f"in_dtype={in_dtype!r} is not built for B200")
     if min(int(model_dim), int(inter_dim), int(experts), int(topk)) <= 0:
         raise ValueError("model_dim, inter_dim, experts and topk must be positive")
     if not (16 <= int(tile_m) <= 256 and int(tile_m) % 16 == 0):
@@ -318,4 +366,5 @@ def compile_moe_reduction(*, topk, model_dim, dtype_str="f16", use_mask=False, n
     return launch
 
 
-__all__ = ["compile_moe_gemm1", "compile_moe_gemm2", "compile_moe_reduction", "moe_sorting"]
+__all__ = ["compile_moe_gemm1", "compile_moe_gemm2", "compile_moe_reduction", "moe_sorting",
+           "pack_shuffled_int8_to_packed_int4", "unpack_packed_int4_to_shuffled_int8"]

@@ -17,7 +17,7 @@ import math
 import torch
 import torch.nn.functional as F
 
-QUANT_DTYPES = {"fp8": torch.float8_e4m3fn, "int8": torch.int8}
+QUANT_DTYPES = {"fp8": torch.float8_e4m3fn, "int8": torch.int8, "int4": torch.int8}  # int4 = W4A8: int8 activations
 
 
 def moe_sorting(topk_ids, topk_weights, num_experts, block_size):
@@ -119,9 +119,11 @@ def cosine_sim(a, b):
     return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-12))
 
 
-def pertoken_quant(x, quant_dtype):
-    """tests/utils.py:29-73 for finite inputs (the general restatement is in a8w8_oracle)."""
-    qmax = 448.0 if quant_dtype == torch.float8_e4m3fn else 127.0
+def pertoken_quant(x, quant_dtype, dtype_max=None):
+    """tests/utils.py:29-73 for finite inputs (the general restatement is in a8w8_oracle).  ``dtype_max=7``
+    quantises to the signed 4-bit range held in int8, as the reference's W4A8 tests do
+    (tests/kernels/test_moe_gemm_2stage.py:214-215)."""
+    qmax = float(dtype_max) if dtype_max is not None else (448.0 if quant_dtype == torch.float8_e4m3fn else 127.0)
     amax = x.abs().amax(dim=-1, keepdim=True).to(torch.float32)
     scale = amax / qmax
     scale = torch.where(scale == 0, torch.ones_like(scale), scale)
@@ -168,8 +170,9 @@ def make_inputs(tokens, model_dim, inter_dim, experts, topk, in_dtype, seed):
     w1 = torch.randn((experts, 2 * inter_dim, model_dim), generator=g, dtype=torch.float32) / math.sqrt(model_dim)
     w2 = torch.randn((experts, model_dim, inter_dim), generator=g, dtype=torch.float32) / math.sqrt(inter_dim)
     x_q, scale_x = pertoken_quant(x, qd)
-    w1_q, scale_w1 = pertoken_quant(w1, qd)
-    w2_q, scale_w2 = pertoken_quant(w2, qd)
+    wmax = 7 if in_dtype == "int4" else None  # W4A8: weights in [-8, 7]
+    w1_q, scale_w1 = pertoken_quant(w1, qd, wmax)
+    w2_q, scale_w2 = pertoken_quant(w2, qd, wmax)
     out1 = moe_gemm1(
         x_q, w1_q.view(experts * 2 * inter_dim, model_dim), scale_x, scale_w1.view(-1, 1), topk_ids.long(), topk_weights,
         inter_dim, False,

@@ -514,3 +514,69 @@ def test_topk_reduction_with_expert_mask(dev, dtype_str):
     torch.cuda.synchronize()
     want = (x.float() * keep.unsqueeze(-1)).sum(dim=1).to(OUT_T[dtype_str])
     assert torch.equal(y.cpu(), want)
+
+
+# --- W4A8: int8 activations, weights in [-8, 7] passed packed two per byte (in_dtype="int4")
+
+
+@pytest.mark.parametrize("tile_m,tokens", [(16, 5), (32, 64), (64, 300), (128, 600)])
+def test_int4_weights_both_stages(dev, tile_m, tokens):
+    """The reference's W4A8 flow (tests/kernels/test_moe_gemm_2stage.py:212-220, 302-325): quantise the
+    weights to [-8, 7], preshuffle the int8 values, pack two per byte, launch with in_dtype="int4"."""
+    from flydsl_b200.kernels.moe.moe_gemm_2stage import pack_shuffled_int8_to_packed_int4
+
+    d = moe_oracle.make_inputs(tokens, seed=31 + tokens, in_dtype="int4", **SHAPE)
+    assert int(d["w1_q"].min()) >= -8 and int(d["w1_q"].max()) <= 7
+    experts, topk, model_dim, inter_dim = SHAPE["experts"], SHAPE["topk"], SHAPE["model_dim"], SHAPE["inter_dim"]
+    ids, w, e_ids, n_valid, blocks = routing_on(dev, d, experts, tile_m)
+    st = torch.cuda.current_stream()
+    # stage 1
+    w1_packed = pack_shuffled_int8_to_packed_int4(shuffle_weight(d["w1_q"].to(dev)))
+    assert w1_packed.numel() == experts * 2 * inter_dim * model_dim // 2
+    out1 = torch.full((tokens * topk, inter_dim), 7.0, dtype=torch.bfloat16, device=dev)
+    exe1 = compile_moe_gemm1(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, tile_n=64,
+                             tile_k=128, doweight_stage1=False, out_dtype="bf16", in_dtype="int4")
+    for _ in range(2):  # the second call takes the cached expansion
+        exe1(out1, d["x_q"].to(dev).view(-1), w1_packed, d["scale_x"].to(dev).view(-1), d["scale_w1"].to(dev).view(-1), ids, e_ids,
+             w.view(-1), n_valid, tokens, inter_dim, model_dim, blocks, st)
+    torch.cuda.synchronize()
+    close_enough(out1.view(tokens, topk, -1), ref_stage1(d, inter_dim), "int4 stage 1")
+    # the packed form and the plain int8 image give bit-identical results
+    plain = run_stage1(dev, d, **SHAPE, tile_m=tile_m, in_dtype="int8", out_dtype="bf16")
+    assert torch.equal(plain, out1)
+    # stage 2
+    w2_packed = pack_shuffled_int8_to_packed_int4(shuffle_weight(d["w2_q"].to(dev)))
+    out2 = torch.zeros((tokens * topk, model_dim), dtype=torch.bfloat16, device=dev)
+    exe2 = compile_moe_gemm2(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, tile_n=64,
+                             tile_k=128, doweight_stage2=True, out_dtype="bf16", accumulate=False, in_dtype="int4")
+    exe2(out2, d["a2_q"].to(dev).view(-1), w2_packed, d["scale_a2"].to(dev).view(-1), d["scale_w2"].to(dev).view(-1), ids, e_ids,
+         w.view(-1), n_valid, tokens, model_dim, inter_dim, blocks, st)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    close_enough(out2.view(tokens, topk, -1).float().sum(dim=1), ref_stage2(d, model_dim), "int4 stage 2")
+
+
+def test_int4_nibble_order_matters(dev):
+    """Swapping the nibble halves of the packed weights must change the result (the reference guards the
+    same property, tests/kernels/test_moe_gemm_2stage.py:411-460): the unpacking order is really used."""
+    from flydsl_b200.kernels.moe.moe_gemm_2stage import pack_shuffled_int8_to_packed_int4
+
+    tokens, tile_m = 64, 32
+    d = moe_oracle.make_inputs(tokens, seed=5, in_dtype="int4", **SHAPE)
+    experts, topk, model_dim, inter_dim = SHAPE["experts"], SHAPE["topk"], SHAPE["model_dim"], SHAPE["inter_dim"]
+    ids, w, e_ids, n_valid, blocks = routing_on(dev, d, experts, tile_m)
+    good = pack_shuffled_int8_to_packed_int4(shuffle_weight(d["w1_q"].to(dev)))
+    u = good.view(torch.uint8)
+    swapped = ((u << 4) | (u >> 4)).view(torch.int8).contiguous()
+    outs = []
+    for packed in (good, swapped):
+        out = torch.zeros((tokens * topk, inter_dim), dtype=torch.bfloat16, device=dev)
+        exe = compile_moe_gemm1(model_dim=model_dim, inter_dim=inter_dim, experts=experts, topk=topk, tile_m=tile_m, tile_n=64,
+                                tile_k=128, doweight_stage1=False, out_dtype="bf16", in_dtype="int4")
+        exe(out, d["x_q"].to(dev).view(-1), packed, d["scale_x"].to(dev).view(-1), d["scale_w1"].to(dev).view(-1), ids, e_ids,
+            w.view(-1), n_valid, tokens, inter_dim, model_dim, blocks, torch.cuda.current_stream())
+        torch.cuda.synchronize()
+        outs.append(out.float().cpu())
+    ref = ref_stage1(d, inter_dim)
+    assert moe_oracle.cosine_sim(outs[0].view(tokens, topk, -1), ref) > 0.99
+    assert moe_oracle.cosine_sim(outs[1].view(tokens, topk, -1), ref) < 0.9

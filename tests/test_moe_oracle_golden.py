@@ -117,8 +117,7 @@ def test_builders_validate_like_the_reference():
         compile_moe_gemm1(**kw, doweight_stage1=False, out_dtype="f32")
     with pytest.raises(ValueError, match="in_dtype"):
         compile_moe_gemm1(**kw, doweight_stage1=False, in_dtype="fp4")
-    with pytest.raises(ValueError, match="not built"):
-        compile_moe_gemm1(**kw, doweight_stage1=False, in_dtype="int4")
+    compile_moe_gemm1(**kw, doweight_stage1=False, in_dtype="int4")  # W4A8: packed weights, expanded to the int8 image once
     with pytest.raises(ValueError, match="accumulate=False"):
         compile_moe_gemm2(**kw, doweight_stage2=True, out_dtype="f32", accumulate=False)
     with pytest.raises(ValueError, match="tile_m"):
@@ -128,3 +127,14 @@ def test_builders_validate_like_the_reference():
     with pytest.raises(ValueError, match="num_experts"):
         compile_moe_reduction(topk=2, model_dim=256, use_mask=True)
     compile_moe_reduction(topk=2, model_dim=256, use_mask=True, num_experts=8)
+
+
+def test_int4_pack_helper_round_trip():
+    from flydsl_b200.kernels.moe.moe_gemm_2stage import pack_shuffled_int8_to_packed_int4, unpack_packed_int4_to_shuffled_int8
+
+    x = torch.arange(-8, 8, dtype=torch.int8).repeat(64)
+    packed = pack_shuffled_int8_to_packed_int4(x)
+    assert packed.numel() == x.numel() // 2
+    # byte j of every 4-byte group holds v_j in the low and v_{j+4} in the high nibble
+    assert int(packed.view(torch.uint8)[0]) == ((-8 & 15) | ((-4 & 15) << 4))
+    assert torch.equal(unpack_packed_int4_to_shuffled_int8(packed), x)
