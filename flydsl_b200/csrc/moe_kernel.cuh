@@ -65,12 +65,6 @@ __host__ __device__ inline MoeLayout moe_layout(int bn, int stages) {
   return l;
 }
 
-__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-
 // x * sigmoid(x), with the fast exponential and reciprocal as in the reference's
 // epilogue (exp2 and rcp, kernels/moe/moe_gemm_2stage/layout_helpers.py:247-248)
 __device__ __forceinline__ float silu_f32(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
