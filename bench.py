@@ -846,6 +846,7 @@ def main():
             torch.cuda.empty_cache()
         roofline["cublaslt_fp8_tflops"] = lib_fp8
         # the MXFP8 block-scaled GEMM on the prefill shape of configuration 3 (halved N to bound the run)
+        settle()
         extras["mxfp8_8192x14336x8192"] = time_mx(8192, 14336, 8192, dev, iters=5)
         # ... and on the reference's own MXFP8 test shapes (tests/kernels/test_preshuffle_gemm.py:590-598)
         for mm in (32, 64, 128, 1024):
@@ -854,12 +855,14 @@ def main():
             r["hbm_frac_of_measured"] = round(r["hbm_gbs"] / peaks["hbm_gbs"], 3)
             extras[f"mxfp8_{mm}x8192x8192"] = r
         # the MXFP4 block-scaled GEMM (two codes per byte): prefill shape and two of the reference's test shapes
+        settle()
         extras["mxfp4_8192x14336x8192"] = time_mx(8192, 14336, 8192, dev, iters=5, fp4=True)
         for mm in (64, 1024):
             settle()
             r = time_mx(mm, 8192, 8192, dev, iters=20, fp4=True)
             r["hbm_frac_of_measured"] = round(r["hbm_gbs"] / peaks["hbm_gbs"], 3)
             extras[f"mxfp4_{mm}x8192x8192"] = r
+        settle()
         extras["mxfp6_x_mxfp4_4096x8192x8192"] = time_mx_mixed(4096, 8192, 8192, dev)
         # the grouped (mixture-of-experts) stages: a decode-sized and a prefill-sized batch
         for name, mt, mtile in (("moe_fp8_decode_32tok", 32, 16), ("moe_fp8_prefill_4096tok", 4096, 128)):
