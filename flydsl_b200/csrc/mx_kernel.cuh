@@ -268,21 +268,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) mx_gemm_kernel(const __grid_co
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      // 64 columns per TMEM wait, and each lane then writes one full 128-byte line of its output row
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_x32(t_row + c0, r);
+      for (int c0 = 0; c0 < BN; c0 += 64) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_x32(t_row + c0, r0);
+        tmem_ld_x32(t_row + c0 + 32, r1);
         tmem_ld_wait();
-        if (c0 + 32 >= BN) {  // last read of this accumulator: hand it back to the MMA warp
+        if (c0 + 64 >= BN) {  // last read of this accumulator: hand it back to the MMA warp
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
         }
-        float y[32];
+        if (row < p.M) {
+          float y[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(r[j]);
-        if (row < p.M)
+          for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(r0[j]);
           moe_store_row32<OUTMODE, false>(p.c, static_cast<size_t>(row) * p.N + n_blk * BN + c0, y, 32);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(r1[j]);
+          moe_store_row32<OUTMODE, false>(p.c, static_cast<size_t>(row) * p.N + n_blk * BN + c0 + 32, y, 32);
+        }
       }
       acc = (acc + 1) % NACC;
       if (acc == 0) acc_phase ^= 1u;
