@@ -45,8 +45,9 @@ def _cases(count=80, seed=20241125):
     return out
 
 
-# FLYB200_FUZZ_CASES=<n> widens the sweep (same seed: the first 80 cases stay the same)
-@pytest.mark.parametrize("in_dtype,m,n,k,out_dtype,epilogue,hint", _cases(int(os.environ.get("FLYB200_FUZZ_CASES", "80"))),
+# FLYB200_FUZZ_CASES=<n> widens the sweep (same seed: the first 80 cases stay the same); FLYB200_FUZZ_SEED=<s> draws another one
+@pytest.mark.parametrize("in_dtype,m,n,k,out_dtype,epilogue,hint",
+                         _cases(int(os.environ.get("FLYB200_FUZZ_CASES", "80")), int(os.environ.get("FLYB200_FUZZ_SEED", "20241125"))),
                          ids=lambda v: hex(v) if isinstance(v, int) and v > 4096 else str(v))
 def test_random_configuration(in_dtype, m, n, k, out_dtype, epilogue, hint):
     dev = torch.device("cuda:0")
