@@ -48,6 +48,23 @@ __host__ __device__ inline DecodeLayout decode_layout(int bn, int stages, int w_
   return l;
 }
 
+// Carve-up of the CTA-pair form of the kernel (decode2_kernel.cuh).
+struct Decode2Layout {
+  int off_w, off_a, off_bar, off_misc, off_sa, total;
+};
+// bn: tokens of the pair's tile (each CTA stages bn / 2 of them per k-block)
+__host__ __device__ inline Decode2Layout decode2_layout(int bn, int stages) {
+  Decode2Layout l;
+  l.off_w = 0;
+  l.off_a = stages * BLOCK_ROWS * KBLOCK_BYTES;
+  l.off_bar = l.off_a + stages * (bn / 2) * KBLOCK_BYTES;
+  l.off_misc = l.off_bar + 8 * (3 * stages + 1);  // full, empty, pfull per stage; tfull
+  l.off_misc = (l.off_misc + 15) & ~15;
+  l.off_sa = l.off_misc + 32;
+  l.total = l.off_sa + bn * 4;
+  return l;
+}
+
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -115,19 +132,21 @@ __device__ __forceinline__ void store_reduced(const GemmParams& p, const uint4& 
 // Sum, in the fixed order s = 0..S-1, the partial tiles of the S CTAs of the
 // cluster for the tokens m_first, m_first+4, ... < m_end and four consecutive
 // channels, apply the epilogue and store.  All S*U peer reads of an iteration
-// are issued before the first is used.
+// are issued before the first is used.  The S CTAs are the cluster ranks
+// rank_base, rank_base + rank_stride, ...
 template <int KIND, int OUTMODE, int SMAX, int U>
 __device__ __forceinline__ void cluster_reduce_slice(const GemmParams& p, uint32_t red_mine, uint32_t my_rank, int S,
                                                      int m_first, int m_end, int m_base, int n4, bool col_ok,
                                                      const float* sa_s, const float (&sb4)[4], const float (&bias4)[4],
-                                                     bool scaled) {
+                                                     bool scaled, uint32_t rank_base = 0, uint32_t rank_stride = 1) {
   using KT = KindTraits<KIND>;
   // Every load below is unconditional (addresses are clamped to a valid token
   // and unused peers alias peer 0), so the compiler can keep all SMAX*U of them
   // in flight; results outside the range are simply not used.
   uint32_t peer[SMAX];
 #pragma unroll
-  for (int s = 0; s < SMAX; ++s) peer[s] = map_to_cta(red_mine, static_cast<uint32_t>(s < S ? s : 0));
+  for (int s = 0; s < SMAX; ++s)  // split s of this tile lives in cluster rank rank_base + s * rank_stride
+    peer[s] = map_to_cta(red_mine, rank_base + rank_stride * static_cast<uint32_t>(s < S ? s : 0));
   (void)my_rank;
 #pragma unroll 1
   for (int mb = m_first; mb < m_end; mb += 4 * U) {

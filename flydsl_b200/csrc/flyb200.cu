@@ -156,6 +156,9 @@ inline int default_decode_stages(int bn, int w_rows = BLOCK_ROWS) {
   return n > 12 ? 12 : (n < 2 ? 2 : n);
 }
 
+// Ring depth of the pair form (a stage is 16 KiB of weights + bn / 2 tokens).
+inline int default_decode2_stages(int bn) { return bn <= 128 ? 8 : 6; }
+
 inline int decode_bn_for(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
 // Split-K factor that simply covers the SMs, with at least four k-blocks per
@@ -188,8 +191,9 @@ int fill_sms_split_k(int N, int K_bytes, int sms, int token_blocks = 1) {
 // Reproduces the measured ranking: split 2 at 64 channel tiles (14.5 us against
 // 21 us unsplit and 15 us for split 4), split 4 at 32 tiles of 128 tokens (9.8 us
 // against 12.1 / 19.0 / 21.4 us for 2 / 1 / 8).
-double split_cost_ns(int split, int n_tiles, int kb, int bn, int sms, bool cluster) {
-  const double stage_bytes = static_cast<double>(BLOCK_ROWS * KBLOCK_BYTES + bn * KBLOCK_BYTES);
+// `pair`: CTA pairs, each CTA stages half of the tokens and the cluster is twice the split.
+double split_cost_ns(int split, int n_tiles, int kb, int bn, int sms, bool cluster, bool pair = false) {
+  const double stage_bytes = static_cast<double>(BLOCK_ROWS * KBLOCK_BYTES + (pair ? bn / 2 : bn) * KBLOCK_BYTES);
   const int rounds = (n_tiles * split + sms - 1) / sms;
   const int kbs = (kb + split - 1) / split;
   double stream = rounds * kbs * stage_bytes / 71.0;
@@ -198,7 +202,7 @@ double split_cost_ns(int split, int n_tiles, int kb, int bn, int sms, bool clust
   double reduce = 0.0;
   if (split > 1) {
     const double partial = bn * 512.0;
-    reduce = cluster ? 1500.0 + (split - 1.0) / split * partial / 15.0 + (split > 4 ? 10000.0 : 0.0)
+    reduce = cluster ? 1500.0 + (split - 1.0) / split * partial / 15.0 + ((pair ? 2 * split : split) > 4 ? 10000.0 : 0.0)
                      : 3000.0 + split * partial / 100.0;
   }
   return 3000.0 + stream + reduce;
@@ -208,25 +212,30 @@ double split_cost_ns(int split, int n_tiles, int kb, int bn, int sms, bool clust
 // cheapest by split_cost_ns over cluster splits 1..8 and, where a workspace of
 // the needed size was passed, workspace splits 9..32.  Every split keeps at
 // least two k-blocks per CTA.
-int auto_split_k(int N, int K_bytes, int sms, int bn, int token_blocks, size_t workspace_bytes, bool have_ws) {
+int auto_split_k(int N, int K_bytes, int sms, int bn, int token_blocks, size_t workspace_bytes, bool have_ws,
+                 bool pair = false, double* cost_out = nullptr) {
   const int n_tiles = ((N + BLOCK_ROWS - 1) / BLOCK_ROWS) * token_blocks;
   const int kb = K_bytes / KBLOCK_BYTES;
-  if (n_tiles >= sms) return 1;
   int best = 1;
-  double best_cost = split_cost_ns(1, n_tiles, kb, bn, sms, true);
-  for (int s = 2; s <= MAX_SPLIT_K && 2 * s <= kb; ++s) {
+  double best_cost = split_cost_ns(1, n_tiles, kb, bn, sms, true, pair);
+  // Only splits that keep the launch within one round of CTAs: with more CTAs than SMs the
+  // later rounds wait for whole CTAs to retire (measured at 64 tiles, K = 28672, 64 tokens:
+  // split 9 = four rounds 77 us, split 2 = one round 40 us, where the model's rates said 9).
+  for (int s = 2; n_tiles * s <= sms && s <= MAX_SPLIT_K && 2 * s <= kb; ++s) {
+    if (pair && 2 * s > MAX_CLUSTER_SPLIT) break;  // pairs combine their K splits inside one cluster only
     const bool cluster = s <= MAX_CLUSTER_SPLIT;
     if (!cluster) {
       if (!have_ws || n_tiles > static_cast<int>(TICKET_BYTES / sizeof(int))) break;
       const size_t need = TICKET_BYTES + static_cast<size_t>(s) * n_tiles * bn * BLOCK_ROWS * sizeof(uint32_t);
       if (workspace_bytes < need) break;
     }
-    const double c = split_cost_ns(s, n_tiles, kb, bn, sms, cluster);
+    const double c = split_cost_ns(s, n_tiles, kb, bn, sms, cluster, pair);
     if (c < best_cost) {
       best_cost = c;
       best = s;
     }
   }
+  if (cost_out) *cost_out = best_cost;
   return best;
 }
 
@@ -240,6 +249,7 @@ struct Plan {
   bool two_sm;  // large-M kernel as CTA pairs (tcgen05 cta_group::2)
   int token_blocks;  // small-M kernel: the tokens are split into this many blocks of bn (grid.z)
   int w_rows;        // small-M kernel: output channels per CTA (128, or 64 without any K split)
+  bool pair;         // small-M kernel as CTA pairs (256 channels per pair, half of the tokens staged per CTA)
   int bn;
   int split_k;
   int kb_per_split;
@@ -278,6 +288,19 @@ bool w64_default() {
     // measured 21 us against 14.5 us for 128-channel tiles with split-K 2
     // (M = 32, N = K = 8192).
     const char* e = getenv("FLYB200_DECODE_W64");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+
+// FLYB200_DECODE_PAIR=1: CTA pairs wherever the small-M kernel has more than 32 tokens.  Off unless asked
+// for (also per call: kernel field 5 of the hint): each CTA then takes in a third fewer bytes, but a
+// k-block is consumed only once both CTAs hold their halves and freed by a commit that has to reach the
+// peer, and graph-replayed launches measured within -5 % .. +4 % of the one-CTA form (FP8, N = K = 8192,
+// 256 tokens: 25.4 against 24.4 us; K = 28672: 55.0 against 56.9 us; N = 16384: 42.3 against 44.5 us).
+bool decode_pair_default() {
+  static const bool on = []() {
+    const char* e = getenv("FLYB200_DECODE_PAIR");
     return e && e[0] == '1';
   }();
   return on;
@@ -345,17 +368,29 @@ int auto_rows_bn(int M, int N, int K_bytes, int sms) {
   return best;
 }
 
-int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t workspace_bytes, bool have_ws, int sms) {
+// `allow_pair`: the caller's kind has the CTA-pair form of the small-M kernel (the plain kinds do)
+int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t workspace_bytes, bool have_ws, int sms,
+              bool allow_pair = true) {
   const int want_kernel = hint_kernel(variant_hint);
   const int want_split = hint_split(variant_hint);
   const int want_reduce = hint_reduce(variant_hint);
-  if (want_kernel > 4) return FLYB200_E_BAD_ARG;
-  plan->decode = (want_kernel == 1 || want_kernel == 4) ? true : want_kernel >= 2 ? false : (M <= 256);
+  if (want_kernel > 5) return FLYB200_E_BAD_ARG;
+  plan->decode = (want_kernel == 1 || want_kernel == 4 || want_kernel == 5) ? true : want_kernel >= 2 ? false : (M <= 256);
+  if (want_kernel == 0 && plan->decode) {
+    // Wide outputs: the small-M kernel launches one CTA per 128 channels, so with more channel
+    // tiles than SMs it runs in rounds and the last one is part empty; the large-M kernel is
+    // persistent and walks 256-channel tiles.  Measured (FP8, K = 8192, us, small-M / large-M):
+    // N = 28672: M = 32 46/49, 64 52/49, 128 62/50, 256 86/67; N = 57344: M = 32 94/83, 128 123/86,
+    // 256 168/126; N = 18944 (exactly one round), K = 4096: M = 64 19/22, 128 24/22, 256 36/31.
+    const int tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
+    if ((tiles >= sms && M > 64) || (tiles > sms && M > 32) || (tiles >= 3 * sms && M > 16)) plan->decode = false;
+  }
   plan->two_sm = want_kernel == 3 ? true : want_kernel == 2 ? false : rows_two_sm_default();
   if (plan->decode && M > 256) return FLYB200_E_UNSUPPORTED;
   if (want_reduce > REDUCE_CLUSTER) return FLYB200_E_BAD_ARG;
   plan->token_blocks = 1;
   plan->w_rows = BLOCK_ROWS;
+  plan->pair = false;
   if (!plan->decode) {
     // large-M kernel: the split field carries the tile width in units of 32 channels
     if (plan->two_sm) {
@@ -372,6 +407,11 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     int t = ht == 0 ? auto_token_blocks(M, N, sms) : (ht == 1 ? 1 : ht == 2 ? 2 : 4);
     plan->bn = decode_bn_for((M + t - 1) / t);
     plan->token_blocks = (M + plan->bn - 1) / plan->bn;  // no empty block
+    // CTA pairs: from 64-token tiles up, where the token tile is a large part of what an SM takes in
+    const int tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
+    const bool pair_ok = plan->bn >= 64 && (tiles & 1) == 0 && want_reduce != REDUCE_WORKSPACE && want_split <= MAX_CLUSTER_SPLIT / 2;
+    if (want_kernel == 5 && !pair_ok) return FLYB200_E_UNSUPPORTED;
+    plan->pair = pair_ok && (want_kernel == 5 || (want_kernel == 0 && allow_pair && decode_pair_default()));
   }
   // 32 row tiles (32 MiB of 8-bit activations at K = 8192) stay in L2 while a group walks the channels:
   // measured DRAM reads 1.17 x the operands against 1.67 x with groups of 16, at equal time
@@ -382,21 +422,25 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     // 64-channel tiles: when they alone put one CTA on (nearly) every SM, no K
     // split and therefore no reduction step is needed.
     const int tiles64 = (N + 63) / 64;
-    const bool fits = plan->bn <= 64 && plan->token_blocks == 1;
+    const bool fits = plan->bn <= 64 && plan->token_blocks == 1 && !plan->pair;
     const bool wanted = want_kernel == 4;
     const bool automatic = want_kernel == 0 && want_split == 0 && want_reduce == 0 && tiles64 <= sms &&
                            4 * tiles64 >= 3 * sms && w64_default();
     if (wanted && (!fits || want_split > 1 || want_reduce != 0)) return FLYB200_E_UNSUPPORTED;
     if (fits && (wanted || automatic)) plan->w_rows = 64;
   }
-  plan->stages = hint_stages(variant_hint) >= 2 ? hint_stages(variant_hint) : default_decode_stages(plan->bn, plan->w_rows);
+  plan->stages = hint_stages(variant_hint) >= 2 ? hint_stages(variant_hint)
+                 : plan->pair                   ? default_decode2_stages(plan->bn)
+                                                : default_decode_stages(plan->bn, plan->w_rows);
   // The two MMA issuers take alternate k-blocks.  With an even ring depth a stage
   // always belongs to the same issuer, so its full-barrier is never more than
   // one phase ahead of the thread waiting on it (a parity wait cannot tell
   // phase n from phase n + 2).  An odd depth becomes the next even one, or the
   // one below when that does not fit into shared memory.
   if (plan->stages & 1) {
-    plan->stages += decode_layout(plan->bn, plan->stages + 1, plan->w_rows).total <= SMEM_LIMIT ? 1 : -1;
+    const int deeper = plan->pair ? decode2_layout(plan->bn, plan->stages + 1).total
+                                  : decode_layout(plan->bn, plan->stages + 1, plan->w_rows).total;
+    plan->stages += deeper <= SMEM_LIMIT ? 1 : -1;
   }
   // Weights requested into L2 ahead of the ring.  Small-M kernel: four k-blocks
   // beyond the depth of the ring measured best (INT8 32 x 8192 x 8192 on one GPU:
@@ -412,7 +456,7 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   plan->kb_per_split = kb;
   if (plan->decode) {
     int split = want_split > 0 ? want_split
-                               : auto_split_k(N, K_bytes, sms, plan->bn, plan->token_blocks, workspace_bytes, have_ws);
+                               : auto_split_k(N, K_bytes, sms, plan->bn, plan->token_blocks, workspace_bytes, have_ws, plan->pair);
     if (plan->w_rows == 64) split = 1;
     if (split > kb) split = kb;
     int mode = REDUCE_NONE;
@@ -495,7 +539,7 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
     if (rc) return rc;
   }
   rc = make_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, static_cast<uint64_t>(K_bytes), static_cast<uint64_t>(M),
-                KBLOCK_BYTES, plan.decode ? plan.bn : BLOCK_ROWS);
+                KBLOCK_BYTES, plan.decode ? (plan.pair ? plan.bn / 2 : plan.bn) : BLOCK_ROWS);
   if (rc) return rc;
   if (!plan.decode && outmode != OUT_RAW32) {
     rc = make_map(&tmC, outmode == OUT_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c,
@@ -505,6 +549,7 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int kind = kind_of(in_dtype);
+  if (plan.decode && plan.pair) return host::launch_decode2_kind(kind, outmode, plan.bn, tmA, p, s);
   if (plan.decode) return host::launch_decode_kind(kind, outmode, plan.bn, plan.w_rows, tmA, p, s);
   return host::launch_rows_kind(kind, outmode, plan.two_sm, tmA, tmW, tmC, p, st->sms, s);
 }
@@ -897,7 +942,7 @@ int flyb200_describe_plan(int M, int N, int K, int in_dtype, int variant_hint, i
   // planned as with an unlimited workspace: the answer says what would be needed
   int rc = make_plan(&plan, M, N, K * eb, variant_hint, static_cast<size_t>(-1) >> 1, true, sm_count);
   if (rc) return rc;
-  out8[0] = plan.decode ? (plan.w_rows == 64 ? 4 : 1) : (plan.two_sm ? 3 : 2);
+  out8[0] = plan.decode ? (plan.pair ? 5 : plan.w_rows == 64 ? 4 : 1) : (plan.two_sm ? 3 : 2);
   out8[1] = plan.bn;
   out8[2] = plan.split_k;
   out8[3] = plan.kb_per_split;

@@ -50,5 +50,9 @@ int launch_rows_scatter_kind(int kind, int outmode, const CUtensorMap& tmA, cons
 int launch_decode_kind(int kind, int outmode, int bn, int w_rows, const CUtensorMap& tmA, const GemmParams& p,
                        cudaStream_t s);
 
+// Small-M kernel as CTA pairs (256 channels x `bn` tokens per pair, `bn` = 64, 128 or 256); `tmA` has boxes of bn / 2
+// tokens.  Needs an even number of channel tiles and an even ring depth.
+int launch_decode2_kind(int kind, int outmode, int bn, const CUtensorMap& tmA, const GemmParams& p, cudaStream_t s);
+
 }  // namespace host
 }  // namespace flyb200

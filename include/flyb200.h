@@ -63,9 +63,16 @@ extern "C" {
  *              3 = large-M persistent kernel, CTA pairs on 256x256 tiles
  *              4 = small-M kernel with 64-channel weight tiles and no K split
  *              (M <= 64 per token block; twice the CTAs, no reduction step)
- *              (automatic: M <= 256 -> 1, or 4 when FLYB200_DECODE_W64=1 and the
- *              N/64 tiles fill 75-100 % of the SMs; else 2, or 3 when
- *              FLYB200_ROWS_2SM=1)
+ *              5 = small-M kernel as CTA pairs (tcgen05 cta_group::2: 256 channels
+ *              per pair, each CTA stages half of the token tile; token tiles of
+ *              64..256, an even number of 128-channel tiles, K splits <= 4 inside
+ *              the pair's cluster)
+ *              (automatic: M <= 256 -> 1 [5 when FLYB200_DECODE_PAIR=1 and the shape
+ *              allows it; 4 when FLYB200_DECODE_W64=1 and the N/64 tiles fill
+ *              75-100 % of the SMs], except for outputs so wide that the small-M
+ *              kernel would run in several rounds of CTAs: with S SMs and
+ *              T = ceil(N/128), M > 64 and T >= S, M > 32 and T > S, or M > 16 and
+ *              T >= 3 S go to 2; M > 256 -> 2, or 3 when FLYB200_ROWS_2SM=1)
  *   bits 12-15 how K splits are combined: 1 = global workspace + ticket,
  *              2 = thread-block cluster + distributed shared memory (split <= 8)
  *   bits 16-23 rasterisation group (row tiles per group, large-M kernel)

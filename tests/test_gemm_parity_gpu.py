@@ -21,6 +21,7 @@ pytestmark = pytest.mark.gpu
 RTOL = ATOL = 1e-2  # stated tolerance for fp8 / scaled outputs against the fp32 reference
 SENTINEL = -8192.0
 DEC, ROWS, ROWS2, W64 = 1 << 8, 2 << 8, 3 << 8, 4 << 8  # variant_hint: kernel field (small-M, large-M, large-M as CTA pairs, small-M with 64-channel tiles)
+PAIR = 5 << 8  # variant_hint: kernel field, small-M kernel as CTA pairs
 WS, CL = 1 << 12, 2 << 12  # variant_hint: split-K reduction through a global workspace / a cluster
 PDL = 1 << 28  # variant_hint: programmatic dependent launch
 TOK1, TOK2, TOK4 = 1 << 30, 2 << 30, (3 << 30) - (1 << 32)  # variant_hint: token blocks (as signed 32-bit)
@@ -108,6 +109,27 @@ def test_every_kernel_variant_small_m(dev, hint, m):
     check_scaled(c, a_q, b_q, sa, sb, m)
 
 
+@pytest.mark.parametrize(
+    "hint",
+    [PAIR | 1, PAIR | CL | 2, PAIR | CL | 3, PAIR | CL | 4, PAIR | 2 | STAGES(4), PAIR | 2 | PDL, PAIR | 2 | (2 << 28),
+     PAIR | TOK2, PAIR | TOK4 | CL | 2, PAIR],
+    ids=["nosplit", "cluster2", "cluster3", "cluster4", "stages4", "pdl", "nopdl", "tok2", "tok4_cluster2", "auto_split"],
+)
+@pytest.mark.parametrize("m", [33, 64, 100, 128, 129, 200, 256])
+def test_small_m_kernel_as_cta_pairs(dev, hint, m):
+    """Two CTAs on neighbouring channel tiles share the token tile (half each); N = 1936 gives 16
+    channel tiles, the last one 16 channels wide."""
+    n, k = 1936, 2048
+    blocks = {1: 1, 2: 2, 3: 4}.get((hint >> 30) & 3, 1)
+    if -(-m // blocks) <= 32:
+        pytest.skip("pairs are built for token tiles of 64 and more")
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "fp8", seed=99 + m)
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=128, tile_n=128, tile_k=128, in_dtype="fp8", variant_hint=hint)
+    assert fn.plan(m)["kernel"] == 5
+    c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, "fp8", hint=hint)
+    check_scaled(c, a_q, b_q, sa, sb, m)
+
+
 @pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
 @pytest.mark.parametrize("m,n,k", [(257, 1024, 1152), (513, 2064, 2048), (2048, 4096, 4096)])
 def test_cta_pair_kernel_scaled_output(dev, in_dtype, m, n, k):
@@ -176,6 +198,11 @@ def test_first_captured_call_allocates_nothing_when_compiled(dev):
         (200, 512, 1024, DEC | WS | 2),
         (200, 512, 1024, DEC | TOK4 | WS | 2),
         (33, 1040, 1024, DEC | TOK2 | CL | 4),
+        (64, 256, 128, PAIR | 1),  # CTA pairs, a single k-block
+        (64, 256, 384, PAIR | CL | 3),  # one k-block per split
+        (130, 1936, 640, PAIR | CL | 4),
+        (200, 512, 1024, PAIR | CL | 2),
+        (256, 2048, 4096, PAIR),
         (8, 57344, 256, 0),  # very wide: more channel tiles than SMs
         (300, 784, 1024, ROWS),
         (1024, 2048, 8320, ROWS),  # K = 65 * 128 as in the reference's large shapes
@@ -347,7 +374,8 @@ def run_gemm_generic(dev, a, b, sa, sb, bias, m, n, k, in_dtype, out_dtype="bf16
 
 
 @pytest.mark.parametrize("in_dtype", ["fp16", "bf16"])
-@pytest.mark.parametrize("m,n,k,hint", [(16, 5120, 8192, 0), (33, 1024, 2048, 0), (513, 1024, 2048, 0), (513, 1024, 2048, ROWS2), (200, 528, 1280, DEC | WS | 3)])
+@pytest.mark.parametrize("m,n,k,hint", [(16, 5120, 8192, 0), (33, 1024, 2048, 0), (513, 1024, 2048, 0), (513, 1024, 2048, ROWS2), (200, 528, 1280, DEC | WS | 3),
+                                        (200, 512, 1280, PAIR | CL | 2), (72, 1024, 2048, PAIR)])
 def test_half_precision_inputs(dev, in_dtype, m, n, k, hint):
     g = torch.Generator().manual_seed(m + n)
     a = torch.randn(m, k, generator=g).to(TORCH_DT[in_dtype])
@@ -358,7 +386,7 @@ def test_half_precision_inputs(dev, in_dtype, m, n, k, hint):
 
 
 @pytest.mark.parametrize("epilogue", ["bias", "bias_relu", "bias_silu", "bias_gelu"])
-@pytest.mark.parametrize("in_dtype,m", [("bf16", 16), ("fp8", 16), ("fp8", 300), ("int8", 40)])
+@pytest.mark.parametrize("in_dtype,m", [("bf16", 16), ("fp8", 16), ("fp8", 300), ("int8", 40), ("bf16", 136), ("fp8", 250)])
 def test_fused_epilogues(dev, epilogue, in_dtype, m):
     n, k = 5120, 2048
     g = torch.Generator().manual_seed(7)

@@ -193,3 +193,22 @@ def test_variant_selection_is_a_pure_host_function():
     assert d(16, 1024, 128)["split_k"] == 1
     # fewer SMs -> smaller split
     assert d(32, 8192, 8192, sm_count=64, variant_hint=1 << 8)["split_k"] == 1
+    # the automatic split keeps the launch within one round of CTAs also where K is long
+    p = d(64, 8192, 28672)
+    assert (p["kernel"], p["split_k"], p["reduce"]) == (1, 2, 2)
+    # wide outputs (more channel tiles than SMs) go to the persistent kernel from 64 tokens up,
+    # very wide ones from 32 up; narrow ones stay on the small-M kernel
+    assert d(32, 28672, 8192)["kernel"] == 1 and d(64, 28672, 8192)["kernel"] == 2 and d(256, 28672, 8192)["kernel"] == 2
+    assert d(64, 18944, 4096)["kernel"] == 1 and d(128, 18944, 4096)["kernel"] == 2
+    assert d(16, 57344, 8192)["kernel"] == 1 and d(32, 57344, 8192)["kernel"] == 2
+    assert d(256, 16384, 8192)["kernel"] == 1
+    assert d(128, 28672, 8192, variant_hint=1 << 8)["kernel"] == 1  # a request for the small-M kernel stands
+    # small-M kernel as CTA pairs: on request, for token tiles of 64 and more and an even number of channel tiles
+    p = d(256, 8192, 8192, variant_hint=5 << 8)
+    assert (p["kernel"], p["bn"], p["split_k"], p["reduce"], p["stages"]) == (5, 256, 2, 2, 6)
+    assert d(64, 8192, 8192, variant_hint=5 << 8)["stages"] == 8
+    for m, n in ((32, 8192), (64, 1040)):  # too few tokens; nine channel tiles
+        with pytest.raises(_lib.FlyB200Error):
+            d(m, n, 8192, variant_hint=5 << 8)
+    with pytest.raises(_lib.FlyB200Error):
+        d(64, 8192, 8192, variant_hint=(5 << 8) | (1 << 12) | 2)  # pairs reduce inside their cluster only
