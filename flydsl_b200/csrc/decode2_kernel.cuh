@@ -13,16 +13,25 @@
 // the one-CTA kernel, among the CTAs of the cluster that hold the same channels
 // (ranks r, r + 2, r + 4, ...).
 //
-// Signalling inside a pair:
+// Signalling inside a pair (the thread that issues the MMAs does per k-block
+// exactly what it does in the one-CTA kernel: one wait, four MMAs, one commit;
+// everything that crosses to the other CTA is done by otherwise idle threads):
 //   full[s]   one per CTA, completed by that CTA's own loads, so the weight
-//             stream starts before the two CTAs have met;
-//   pfull[s]  in the leader (even cluster rank): the follower forwards the
-//             completion of its full[s] with a remote arrive;
-//   empty[s]  one per CTA, each released by a tcgen05.commit of the leader;
+//             stream starts before the two CTAs have met; the leader's (even
+//             cluster rank) takes one more arrival, with which the follower's
+//             warp 6 forwards the completion of its own full[s];
+//   empty[s]  the leader's is released by the tcgen05.commit of the MMAs that
+//             read the stage (in both CTAs); the leader's producer, which waits
+//             on it before refilling, passes the release on to the follower's
+//             empty[s] with a remote arrive;
 //   tfull     one per CTA, one commit per MMA-issuing warp of the leader.
 #pragma once
 #include "decode_kernel.cuh"
 #include "rows2_kernel.cuh"
+
+#ifndef FLYB200_PAIR_ISSUERS
+#define FLYB200_PAIR_ISSUERS 2
+#endif
 
 namespace flyb200 {
 
@@ -39,6 +48,7 @@ template <int KIND, int BN, int OUTMODE>
 __global__ void __launch_bounds__(DECODE_THREADS, 1)
 gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p) {
   static_assert(BN >= 32 && BN <= 256 && BN % 32 == 0, "token tile of the pair: 32..256, half of it per CTA");
+  constexpr int ISSUERS = FLYB200_PAIR_ISSUERS;  // MMA-issuing warps of the leader (k-blocks dealt round-robin)
   using KT = KindTraits<KIND>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = smem_u32(smem_raw);
@@ -58,8 +68,7 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
   const uint32_t leader = crank & ~1u;    // cluster rank of this pair's leader
   const uint32_t bar_full = smem_base + L.off_bar;
   const uint32_t bar_empty = bar_full + 8 * stages;
-  const uint32_t bar_pfull = bar_empty + 8 * stages;
-  const uint32_t bar_tfull = bar_pfull + 8 * stages;
+  const uint32_t bar_tfull = bar_empty + 8 * stages;
 
   if ((smem_base & 1023u) != 0) {  // same answer in every CTA of the grid
     if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_SMEM_ALIGN);
@@ -85,11 +94,10 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
   if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, prank == 0 ? 2 : 1);  // leader: its loads and the follower's word
       mbar_init(bar_empty + 8 * s, 1);
-      mbar_init(bar_pfull + 8 * s, 1);
     }
-    mbar_init(bar_tfull, num_kb >= 2 ? 2 : 1);  // one commit per MMA issuer that has k-blocks
+    mbar_init(bar_tfull, (ISSUERS == 2 && num_kb >= 2) ? 2 : 1);  // one commit per MMA issuer that has k-blocks
     abort_flag[0] = 0;
     abort_flag[1] = 0;  // stays zero: lets the drain below wait on time alone
     fence_mbar_init();
@@ -122,6 +130,22 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (p.pdl && threadIdx.x != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Who sums the K splits after the mainloop: from 64 tokens up all seven warps (the producer and
+  // the MMA issuers have nothing left to do by then; measured 2-7 % on the whole kernel at 64-256
+  // tokens), below that the four epilogue warps (with so few tokens the extra warps only cost).
+  constexpr bool ALL_WARPS_REDUCE = BN >= 64;
+  constexpr int REDUCE_WARPS = ALL_WARPS_REDUCE ? DECODE_THREADS / 32 : 4;
+  const bool reduces = ALL_WARPS_REDUCE || (warp >= 2 && warp <= 5);
+  // Per-channel operands of the four consecutive channels a thread owns in that sum, asked for now
+  // and met after the mainloop.
+  float sb4[4] = {0.f, 0.f, 0.f, 0.f}, bias4[4] = {0.f, 0.f, 0.f, 0.f};
+  if (p.reduce_mode == REDUCE_CLUSTER && reduces && n0 + lane * 4 < p.N) {  // (thread 0 has passed its griddepcontrol.wait above)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (p.sa != nullptr && p.sb != nullptr) sb4[e] = __ldg(p.sb + n0 + lane * 4 + e);
+      if (p.epilogue != EPI_NONE) bias4[e] = load_bias<OUTMODE>(p.bias, n0 + lane * 4 + e);
+    }
+  }
 
   if (warp == 0) {
     // ---------------- producer (both CTAs): own 128 channels, own half of the tokens ----------------
@@ -140,6 +164,7 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
           ok = false;
           break;
         }
+        if (prank == 0) mbar_arrive_peer(mapa_u32(bar_empty + 8 * stage, leader + 1));  // the follower may refill too
         const uint32_t fb = bar_full + 8 * stage;
         mbar_expect_tx(fb, A_STAGE + w_bytes);
         bulk_load_1d(smem_base + L.off_w + stage * W_STAGE, p.w + (static_cast<size_t>(kb) * p.N + n0) * KBLOCK_BYTES, w_bytes,
@@ -169,14 +194,14 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
   } else if (warp == 1 || warp == 6) {
     // ---------------- MMA issue (leader only, two issuing warps) ----------------
     const int which = warp == 1 ? 0 : 1;  // issuer 0: k-blocks 0, 2, 4, ...; issuer 1: 1, 3, 5, ...
-    if (lane == 0 && prank == 0 && which < num_kb) {
+    if (lane == 0 && prank == 0 && which < num_kb && which < ISSUERS) {
       constexpr uint32_t idesc = umma_idesc(KT::dfmt, KT::abfmt, 2 * BLOCK_ROWS, BN);
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(which * BN);
-      for (int kb = which; kb < num_kb; kb += 2) {
+      for (int kb = which; kb < num_kb; kb += ISSUERS) {
         const int stage = kb % stages;
         const uint32_t phase = static_cast<uint32_t>(kb / stages) & 1u;
-        // this CTA's halves, then the follower's (forwarded by its warp 6)
-        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag) || !mbar_wait(bar_pfull + 8 * stage, phase, abort_flag)) {
+        // this CTA's halves have landed and the follower has said the same of its own
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
           report_failure(p.status, ST_TIMEOUT, abort_flag);
           ok = false;
           break;
@@ -187,11 +212,10 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
 #pragma unroll
         for (int k = 0; k < KBLOCK_BYTES / UMMA_K_BYTES; ++k) {
           umma_ss_2sm<KIND>(d_tmem, wdesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)),
-                            adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb >= 2 || k != 0) ? 1u : 0u);
+                            adesc + static_cast<uint64_t>(k * (UMMA_K_BYTES >> 4)), idesc, (kb >= ISSUERS || k != 0) ? 1u : 0u);
         }
-        // the stage is free in both CTAs once these MMAs have read it
+        // the stage is free in both CTAs once these MMAs have read it (the producer tells the follower)
         umma_commit_2sm(bar_empty + 8 * stage);
-        umma_commit_2sm(mapa_u32(bar_empty + 8 * stage, leader + 1));
       }
       if (ok) {
         umma_commit_2sm(bar_tfull);
@@ -206,7 +230,7 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
           report_failure(p.status, ST_TIMEOUT, abort_flag);
           break;
         }
-        mbar_arrive_peer(mapa_u32(bar_pfull + 8 * stage, leader));
+        mbar_arrive_peer(mapa_u32(bar_full + 8 * stage, leader));
       }
     }
     __syncwarp();
@@ -218,14 +242,17 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
   const int n = n0 + ch_local;
   const uint32_t red_base = smem_base;  // partial tile [BN][128] words, reuses the (by then idle) ring
   float sb_v = 0.0f, bias_v = 0.0f;
-  float sb4[4] = {0.f, 0.f, 0.f, 0.f}, bias4[4] = {0.f, 0.f, 0.f, 0.f};
-  constexpr int CH = 16;  // tokens per TMEM load
-  const bool two_acc = num_kb >= 2;
+  // tokens per TMEM wait: all loads of a chunk (both accumulators) are issued before the one wait
+  constexpr int CH = BN >= 64 ? 32 : 16;
+  const bool two_acc = ISSUERS == 2 && num_kb >= 2;
   auto load_acc = [&](uint32_t t_row, int c0, uint32_t (&r)[CH]) {
-    tmem_ld_x16(t_row + c0, r);
+#pragma unroll
+    for (int i = 0; i < CH / 16; ++i) tmem_ld_x16(t_row + c0 + 16 * i, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * i]));
     if (two_acc) {
       uint32_t r2[CH];
-      tmem_ld_x16(t_row + BN + c0, r2);
+#pragma unroll
+      for (int i = 0; i < CH / 16; ++i)
+        tmem_ld_x16(t_row + BN + c0 + 16 * i, *reinterpret_cast<uint32_t(*)[16]>(&r2[16 * i]));
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < CH; ++j) r[j] = add_raw<KT::is_int>(r[j], r2[j]);
@@ -233,6 +260,7 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
       tmem_ld_wait();
     }
   };
+
   auto emit = [&](int m, uint32_t raw) {
     if (m < M_loc && n < p.N) {
       if constexpr (OUTMODE == OUT_RAW32) {
@@ -249,13 +277,6 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
     for (int i = et; i < BN; i += 128) sa_s[i] = (scaled && i < M_loc) ? __ldg(p.sa + m_base + i) : 0.0f;
     sb_v = (scaled && n < p.N) ? __ldg(p.sb + n) : 0.0f;
     bias_v = (p.epilogue != EPI_NONE && n < p.N) ? load_bias<OUTMODE>(p.bias, n) : 0.0f;
-    if (p.reduce_mode == REDUCE_CLUSTER && n0 + lane * 4 < p.N) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (scaled) sb4[e] = __ldg(p.sb + n0 + lane * 4 + e);
-        if (p.epilogue != EPI_NONE) bias4[e] = load_bias<OUTMODE>(p.bias, n0 + lane * 4 + e);
-      }
-    }
     named_bar_sync(1, 128);
 
     ok = mbar_wait(bar_tfull, 0, abort_flag);
@@ -291,8 +312,8 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
     // wait (all waits above are bounded), so the cluster barriers always complete.
     tc_fence_before();
     cluster_barrier_all();
-    if (warp >= 2 && warp <= 5 && ok) {
-      // reduce-scatter over the K splits of this CTA's channels: cluster ranks prank, prank + 2, ...
+    if (reduces && abort_flag[0] == 0) {  // abort_flag: the same answer in every thread of the CTA (no role has given up)
+      // reduce-scatter over the K splits of this CTA's channels (cluster ranks prank, prank + 2, ...)
       const int S = p.split_k;
       const int chunk = (M_loc + S - 1) / S;
       const int m_begin = static_cast<int>(blockIdx.y) * chunk;
@@ -301,11 +322,11 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
       const int n4 = n0 + ch4;
       const bool col_ok = n4 < p.N;  // N is a multiple of 4: the four channels are in or out together
       const uint32_t red_mine = red_base + static_cast<uint32_t>(ch4 * 4);
-      const int m_first = m_begin + (warp - 2);
+      const int m_first = m_begin + (ALL_WARPS_REDUCE ? warp : warp - 2);
       if (S <= 2) {
-        cluster_reduce_slice<KIND, OUTMODE, 2, 8>(p, red_mine, crank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled, prank, 2);
+        cluster_reduce_slice<KIND, OUTMODE, 2, ALL_WARPS_REDUCE ? 10 : 8, REDUCE_WARPS>(p, red_mine, crank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled, prank, 2);
       } else {
-        cluster_reduce_slice<KIND, OUTMODE, 4, 4>(p, red_mine, crank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled, prank, 2);
+        cluster_reduce_slice<KIND, OUTMODE, 4, ALL_WARPS_REDUCE ? 5 : 4, REDUCE_WARPS>(p, red_mine, crank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled, prank, 2);
       }
     }
   }

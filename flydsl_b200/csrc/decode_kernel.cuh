@@ -58,7 +58,7 @@ __host__ __device__ inline Decode2Layout decode2_layout(int bn, int stages) {
   l.off_w = 0;
   l.off_a = stages * BLOCK_ROWS * KBLOCK_BYTES;
   l.off_bar = l.off_a + stages * (bn / 2) * KBLOCK_BYTES;
-  l.off_misc = l.off_bar + 8 * (3 * stages + 1);  // full, empty, pfull per stage; tfull
+  l.off_misc = l.off_bar + 8 * (2 * stages + 1);  // full, empty per stage; tfull
   l.off_misc = (l.off_misc + 15) & ~15;
   l.off_sa = l.off_misc + 32;
   l.total = l.off_sa + bn * 4;
@@ -97,6 +97,24 @@ __device__ __forceinline__ uint4 ld_smem_v4(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
 }
+// The same two loads, executed only where `on` is set (v keeps its value otherwise): a predicated
+// instruction, not a branch, so a run of them stays in flight together.
+__device__ __forceinline__ void ld_dsmem_v4_if(uint4& v, uint32_t addr, bool on) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "@p ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}\n"
+      : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+      : "r"(addr), "r"(static_cast<uint32_t>(on))
+      : "memory");
+}
+__device__ __forceinline__ void ld_smem_v4_if(uint4& v, uint32_t addr, bool on) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+      "@p ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}\n"
+      : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+      : "r"(addr), "r"(static_cast<uint32_t>(on))
+      : "memory");
+}
 // sum of two raw 32-bit accumulators (int32 or fp32 bit patterns)
 template <bool IS_INT>
 __device__ __forceinline__ uint32_t add_raw(uint32_t a, uint32_t b) {
@@ -130,38 +148,42 @@ __device__ __forceinline__ void store_reduced(const GemmParams& p, const uint4& 
 }
 
 // Sum, in the fixed order s = 0..S-1, the partial tiles of the S CTAs of the
-// cluster for the tokens m_first, m_first+4, ... < m_end and four consecutive
-// channels, apply the epilogue and store.  All S*U peer reads of an iteration
+// cluster for the tokens m_first, m_first + WARPS, ... < m_end (WARPS warps share a slice,
+// one token each at a time) and four consecutive channels, apply the epilogue and store.  All S*U peer reads of an iteration
 // are issued before the first is used.  The S CTAs are the cluster ranks
 // rank_base, rank_base + rank_stride, ...
-template <int KIND, int OUTMODE, int SMAX, int U>
+template <int KIND, int OUTMODE, int SMAX, int U, int WARPS = 4>
 __device__ __forceinline__ void cluster_reduce_slice(const GemmParams& p, uint32_t red_mine, uint32_t my_rank, int S,
                                                      int m_first, int m_end, int m_base, int n4, bool col_ok,
                                                      const float* sa_s, const float (&sb4)[4], const float (&bias4)[4],
                                                      bool scaled, uint32_t rank_base = 0, uint32_t rank_stride = 1) {
   using KT = KindTraits<KIND>;
-  // Every load below is unconditional (addresses are clamped to a valid token
-  // and unused peers alias peer 0), so the compiler can keep all SMAX*U of them
-  // in flight; results outside the range are simply not used.
+  // The loads below are predicated, not branched around (tokens past the slice and unused peers
+  // are skipped), so all SMAX*U of an iteration are in flight together.
   uint32_t peer[SMAX];
 #pragma unroll
   for (int s = 0; s < SMAX; ++s)  // split s of this tile lives in cluster rank rank_base + s * rank_stride
     peer[s] = map_to_cta(red_mine, rank_base + rank_stride * static_cast<uint32_t>(s < S ? s : 0));
-  (void)my_rank;
+  const int mine = rank_stride == 0 ? 0 : static_cast<int>((my_rank - rank_base) / rank_stride);  // this CTA's split
 #pragma unroll 1
-  for (int mb = m_first; mb < m_end; mb += 4 * U) {
+  for (int mb = m_first; mb < m_end; mb += WARPS * U) {
     uint4 v[SMAX][U];
 #pragma unroll
     for (int s = 0; s < SMAX; ++s) {
 #pragma unroll
       for (int j = 0; j < U; ++j) {
-        const int mc = min(mb + 4 * j, m_end - 1);
-        v[s][j] = ld_dsmem_v4(peer[s] + static_cast<uint32_t>(mc * BLOCK_ROWS * 4));
+        const int mc = mb + WARPS * j;
+        const bool on = mc < m_end && s < S;
+        const uint32_t off = static_cast<uint32_t>(mc * BLOCK_ROWS * 4);
+        v[s][j] = make_uint4(0u, 0u, 0u, 0u);
+        // this CTA's own partial tile is read as plain shared memory, the peers' over the cluster network
+        ld_smem_v4_if(v[s][j], red_mine + off, on && s == mine);
+        ld_dsmem_v4_if(v[s][j], peer[s] + off, on && s != mine);
       }
     }
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-      const int m = mb + 4 * j;
+      const int m = mb + WARPS * j;
       uint4 acc = v[0][j];
 #pragma unroll
       for (int s = 1; s < SMAX; ++s) {
@@ -183,7 +205,7 @@ __device__ __forceinline__ void cluster_reduce_slice(const GemmParams& p, uint32
 // 32-lane quadrant (row r of the tile sits in lane (r % 16) + 32 * (r / 16)),
 // and it supports REDUCE_NONE only.
 template <int KIND, int BN, int OUTMODE, int WROWS = BLOCK_ROWS>
-__global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA,
+__global__ void __launch_bounds__(DECODE_THREADS, 1) gemm_decode_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const GemmParams p) {
   static_assert(WROWS == 128 || WROWS == 64, "weight tile of 128 or 64 channels");
   using KT = KindTraits<KIND>;
@@ -323,6 +345,22 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (p.pdl && threadIdx.x != 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Who sums the K splits after the mainloop: from 64 tokens up all seven warps (the producer and
+  // the MMA issuers have nothing left to do by then; measured 2-7 % on the whole kernel at 64-256
+  // tokens), below that the four epilogue warps (with so few tokens the extra warps only cost).
+  constexpr bool ALL_WARPS_REDUCE = BN >= 64;
+  constexpr int REDUCE_WARPS = ALL_WARPS_REDUCE ? DECODE_THREADS / 32 : 4;
+  const bool reduces = ALL_WARPS_REDUCE || (warp >= 2 && warp <= 5);
+  // Per-channel operands of the four consecutive channels a thread owns in that sum, asked for now
+  // and met after the mainloop.
+  float sb4[4] = {0.f, 0.f, 0.f, 0.f}, bias4[4] = {0.f, 0.f, 0.f, 0.f};
+  if (p.reduce_mode == REDUCE_CLUSTER && reduces && n0 + lane * 4 < p.N) {  // (thread 0 has passed its griddepcontrol.wait above)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (p.sa != nullptr && p.sb != nullptr) sb4[e] = __ldg(p.sb + n0 + lane * 4 + e);
+      if (p.epilogue != EPI_NONE) bias4[e] = load_bias<OUTMODE>(p.bias, n0 + lane * 4 + e);
+    }
+  }
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
@@ -440,16 +478,18 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
   const int n = lane_has_row ? n0 + ch_local : p.N;  // p.N: out of range, never stored
   const uint32_t red_base = smem_base;  // partial tile [BN][128] words, reuses the (by then idle) ring
   float sb_v = 0.0f, bias_v = 0.0f;
-  // the same operands for the four consecutive channels a thread owns in the cluster reduce
-  float sb4[4] = {0.f, 0.f, 0.f, 0.f}, bias4[4] = {0.f, 0.f, 0.f, 0.f};
-  constexpr int CH = 16;  // tokens per TMEM load
+  // tokens per TMEM wait: all loads of a chunk (both accumulators) are issued before the one wait
+  constexpr int CH = BN >= 64 ? 32 : 16;
   const bool two_acc = num_kb >= 2;
   // accumulator columns [c0, c0 + 16) of this thread's lane: first plus (if used) second accumulator
   auto load_acc = [&](uint32_t t_row, int c0, uint32_t (&r)[CH]) {
-    tmem_ld_x16(t_row + c0, r);
+#pragma unroll
+    for (int i = 0; i < CH / 16; ++i) tmem_ld_x16(t_row + c0 + 16 * i, *reinterpret_cast<uint32_t(*)[16]>(&r[16 * i]));
     if (two_acc) {
       uint32_t r2[CH];
-      tmem_ld_x16(t_row + BN + c0, r2);
+#pragma unroll
+      for (int i = 0; i < CH / 16; ++i)
+        tmem_ld_x16(t_row + BN + c0 + 16 * i, *reinterpret_cast<uint32_t(*)[16]>(&r2[16 * i]));
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < CH; ++j) r[j] = add_raw<KT::is_int>(r[j], r2[j]);
@@ -457,6 +497,7 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
       tmem_ld_wait();
     }
   };
+
 
   auto emit = [&](int m, uint32_t raw) {
     if (m < M_loc && n < p.N) {
@@ -475,13 +516,6 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
     for (int i = et; i < BN; i += 128) sa_s[i] = (scaled && i < M_loc) ? __ldg(p.sa + m_base + i) : 0.0f;
     sb_v = (scaled && n < p.N) ? __ldg(p.sb + n) : 0.0f;
     bias_v = (p.epilogue != EPI_NONE && n < p.N) ? load_bias<OUTMODE>(p.bias, n) : 0.0f;
-    if (p.reduce_mode == REDUCE_CLUSTER && n0 + lane * 4 < p.N) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (scaled) sb4[e] = __ldg(p.sb + n0 + lane * 4 + e);
-        if (p.epilogue != EPI_NONE) bias4[e] = load_bias<OUTMODE>(p.bias, n0 + lane * 4 + e);
-      }
-    }
     named_bar_sync(1, 128);
 
     ok = mbar_wait(bar_tfull, 0, abort_flag);
@@ -572,7 +606,7 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
     // wait (all waits above are bounded), so the cluster barriers always complete.
     tc_fence_before();
     cluster_sync_all();
-    if (warp >= 2 && warp <= 5 && ok) {
+    if (reduces && abort_flag[0] == 0) {  // abort_flag: the same answer in every thread of the CTA (no role has given up)
       // Reduce-scatter over the cluster: this CTA owns a slice of the tokens.
       // A warp takes one token at a time and each lane four consecutive
       // channels, so every peer read is one 16-byte load and every output row
@@ -587,14 +621,15 @@ __global__ void __launch_bounds__(DECODE_THREADS) gemm_decode_kernel(const __gri
       const int n4 = n0 + ch4;
       const bool col_ok = n4 < p.N;  // N is a multiple of 4: the four channels are in or out together
       const uint32_t red_mine = red_base + static_cast<uint32_t>(ch4 * 4);
-      const int m_first = m_begin + (warp - 2);
-      // sixteen 16-byte loads in flight per thread whatever the split
+      const int m_first = m_begin + (ALL_WARPS_REDUCE ? warp : warp - 2);
+      // twenty or more 16-byte loads in flight per thread whatever the split; up to 128 tokens at split 2 (64 at
+      // split 4) are done in one or two rounds of loads
       if (S <= 2) {
-        cluster_reduce_slice<KIND, OUTMODE, 2, 8>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
+        cluster_reduce_slice<KIND, OUTMODE, 2, ALL_WARPS_REDUCE ? 10 : 8, REDUCE_WARPS>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
       } else if (S <= 4) {
-        cluster_reduce_slice<KIND, OUTMODE, 4, 4>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
+        cluster_reduce_slice<KIND, OUTMODE, 4, ALL_WARPS_REDUCE ? 5 : 4, REDUCE_WARPS>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
       } else {
-        cluster_reduce_slice<KIND, OUTMODE, 8, 2>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
+        cluster_reduce_slice<KIND, OUTMODE, 8, ALL_WARPS_REDUCE ? 3 : 2, REDUCE_WARPS>(p, red_mine, rank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled);
       }
     }
     if (threadIdx.x == 64) FLYB200_STAMP(4);  // this CTA's slice of the output written
