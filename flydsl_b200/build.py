@@ -37,6 +37,7 @@ HEADERS = [
     "gemm_kernels.cuh",
     "decode_kernel.cuh",
     "rows2_kernel.cuh",
+    "rows_tall_kernel.cuh",
     "decode2_kernel.cuh",
     "quant_kernel.cuh",
     "moe_kernel.cuh",

@@ -247,6 +247,7 @@ size_t partial_bytes(int split, int N, int bn, int token_blocks = 1) {
 struct Plan {
   bool decode;
   bool two_sm;  // large-M kernel as CTA pairs (tcgen05 cta_group::2)
+  bool tall;    // large-M kernel with 256-row tiles (two accumulators per CTA)
   int token_blocks;  // small-M kernel: the tokens are split into this many blocks of bn (grid.z)
   int w_rows;        // small-M kernel: output channels per CTA (128, or 64 without any K split)
   bool pair;         // small-M kernel as CTA pairs (256 channels per pair, half of the tokens staged per CTA)
@@ -301,6 +302,15 @@ bool w64_default() {
 bool decode_pair_default() {
   static const bool on = []() {
     const char* e = getenv("FLYB200_DECODE_PAIR");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+
+// FLYB200_ROWS_TALL=1: 256-row tiles for the large-M kernel wherever no other form is asked for
+bool rows_tall_default() {
+  static const bool on = []() {
+    const char* e = getenv("FLYB200_ROWS_TALL");
     return e && e[0] == '1';
   }();
   return on;
@@ -374,7 +384,7 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   const int want_kernel = hint_kernel(variant_hint);
   const int want_split = hint_split(variant_hint);
   const int want_reduce = hint_reduce(variant_hint);
-  if (want_kernel > 5) return FLYB200_E_BAD_ARG;
+  if (want_kernel > 6) return FLYB200_E_BAD_ARG;
   plan->decode = (want_kernel == 1 || want_kernel == 4 || want_kernel == 5) ? true : want_kernel >= 2 ? false : (M <= 256);
   if (want_kernel == 0 && plan->decode) {
     // Wide outputs: the small-M kernel launches one CTA per 128 channels, so with more channel
@@ -385,7 +395,18 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     const int tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
     if ((tiles >= sms && M > 64) || (tiles > sms && M > 32) || (tiles >= 3 * sms && M > 16)) plan->decode = false;
   }
-  plan->two_sm = want_kernel == 3 ? true : want_kernel == 2 ? false : rows_two_sm_default();
+  plan->two_sm = want_kernel == 3 ? true : (want_kernel == 2 || want_kernel == 6) ? false : rows_two_sm_default();
+  plan->tall = !plan->decode && !plan->two_sm && (want_kernel == 6 || (want_kernel == 0 && rows_tall_default()));
+  if (want_kernel == 0 && !plan->decode && !plan->two_sm && !plan->tall && want_split == 0) {
+    // 256-row tiles where they cover the output in ONE nearly full round of CTAs: every SM then does
+    // the flops of two 128-row tiles but fetches its weight blocks once (1024 x 8192 x 8192: 59-60 us
+    // against 62-65 us).  With more rounds the 128-row form wins: it overlaps the epilogue of a
+    // tile with the mainloop of the next, which the 256-row form (all of TMEM in one tile) cannot.
+    // (Not where the taller tiles would add a padded half tile of rows, nor for M <= 256.)
+    const long long t = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
+    const bool no_extra_rows = (M + 255) / 256 * 2 == (M + 127) / 128;
+    plan->tall = M > 256 && no_extra_rows && t <= sms && 5 * t >= 4 * sms;
+  }
   if (plan->decode && M > 256) return FLYB200_E_UNSUPPORTED;
   if (want_reduce > REDUCE_CLUSTER) return FLYB200_E_BAD_ARG;
   plan->token_blocks = 1;
@@ -398,6 +419,8 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     } else if (want_split > 0) {
       if (want_split > 8) return FLYB200_E_BAD_ARG;
       plan->bn = 32 * want_split;
+    } else if (plan->tall) {
+      plan->bn = 256;
     } else {
       plan->bn = auto_rows_bn(M, N, K_bytes, sms);
     }
@@ -415,7 +438,7 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   }
   // 32 row tiles (32 MiB of 8-bit activations at K = 8192) stay in L2 while a group walks the channels:
   // measured DRAM reads 1.17 x the operands against 1.67 x with groups of 16, at equal time
-  plan->group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : (plan->two_sm ? 8 : 32);
+  plan->group_m = hint_group(variant_hint) > 0 ? hint_group(variant_hint) : (plan->two_sm ? 8 : plan->tall ? 16 : 32);
   plan->split_k = 1;
   plan->reduce_mode = REDUCE_NONE;
   if (plan->decode) {
@@ -526,7 +549,7 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
   p.prefetch = plan.prefetch;
   p.token_blocks = plan.token_blocks;
   p.bn = plan.bn;
-  p.rows_stages = host::rows_stages_for(plan.bn);
+  p.rows_stages = plan.tall ? host::ROWS_TALL_STAGES : host::rows_stages_for(plan.bn);
   p.ws_tickets = static_cast<int*>(workspace);
   p.ws_partials = workspace ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + TICKET_BYTES) : nullptr;
   p.status = st->status;
@@ -539,7 +562,7 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
     if (rc) return rc;
   }
   rc = make_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, static_cast<uint64_t>(K_bytes), static_cast<uint64_t>(M),
-                KBLOCK_BYTES, plan.decode ? (plan.pair ? plan.bn / 2 : plan.bn) : BLOCK_ROWS);
+                KBLOCK_BYTES, plan.decode ? (plan.pair ? plan.bn / 2 : plan.bn) : plan.tall ? 2 * BLOCK_ROWS : BLOCK_ROWS);
   if (rc) return rc;
   if (!plan.decode && outmode != OUT_RAW32) {
     rc = make_map(&tmC, outmode == OUT_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c,
@@ -551,7 +574,8 @@ int gemm_common(void* c, const void* a, const void* w, const float* sa, const fl
   const int kind = kind_of(in_dtype);
   if (plan.decode && plan.pair) return host::launch_decode2_kind(kind, outmode, plan.bn, tmA, p, s);
   if (plan.decode) return host::launch_decode_kind(kind, outmode, plan.bn, plan.w_rows, tmA, p, s);
-  return host::launch_rows_kind(kind, outmode, plan.two_sm, tmA, tmW, tmC, p, st->sms, s);
+  const int form = plan.two_sm ? host::ROWS_FORM_PAIRS : plan.tall ? host::ROWS_FORM_TALL : host::ROWS_FORM_ONE;
+  return host::launch_rows_kind(kind, outmode, form, tmA, tmW, tmC, p, st->sms, s);
 }
 
 // ---------------------------------------------------------------------------
@@ -942,12 +966,12 @@ int flyb200_describe_plan(int M, int N, int K, int in_dtype, int variant_hint, i
   // planned as with an unlimited workspace: the answer says what would be needed
   int rc = make_plan(&plan, M, N, K * eb, variant_hint, static_cast<size_t>(-1) >> 1, true, sm_count);
   if (rc) return rc;
-  out8[0] = plan.decode ? (plan.pair ? 5 : plan.w_rows == 64 ? 4 : 1) : (plan.two_sm ? 3 : 2);
+  out8[0] = plan.decode ? (plan.pair ? 5 : plan.w_rows == 64 ? 4 : 1) : (plan.two_sm ? 3 : plan.tall ? 6 : 2);
   out8[1] = plan.bn;
   out8[2] = plan.split_k;
   out8[3] = plan.kb_per_split;
   out8[4] = plan.reduce_mode;
-  out8[5] = plan.decode ? plan.stages : (plan.two_sm ? ROWS2_STAGES : host::rows_stages_for(plan.bn));
+  out8[5] = plan.decode ? plan.stages : (plan.two_sm ? ROWS2_STAGES : plan.tall ? host::ROWS_TALL_STAGES : host::rows_stages_for(plan.bn));
   out8[6] = plan.decode ? plan.pdl : 0;
   out8[7] = plan.token_blocks;
   return FLYB200_OK;

@@ -1,9 +1,10 @@
-// libflyb200: launchers of the large-M kernels (one CTA per 128 x bn tile, CTA
-// pairs on 256 x 256 tiles, and the form that stores every tile to several
-// output buffers).
+// libflyb200: launchers of the large-M kernels (one CTA per 128 x bn tile, one
+// CTA per 256 x bn tile, CTA pairs on 256 x 256 tiles, and the form that stores
+// every tile to several output buffers).
 #include "../../include/flyb200.h"
 #include "launch.h"
 #include "rows2_kernel.cuh"
+#include "rows_tall_kernel.cuh"
 
 #include <cstring>
 
@@ -22,6 +23,22 @@ int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams
   const long long tiles = static_cast<long long>((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * ((p.N + p.bn - 1) / p.bn);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   kernel<<<grid, NUM_THREADS, L.total, s>>>(tmA, tmC, p);
+  FLYB200_CUDA_TRY(cudaGetLastError());
+  return FLYB200_OK;
+}
+
+// One CTA per 256 x bn tile (tmA: boxes of 256 rows).
+template <int KIND, int OUTMODE>
+int launch_rows_tall(const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams& p, int sms, cudaStream_t s) {
+  static std::atomic<uint64_t> done{0};
+  auto kernel = gemm_rows_tall_kernel<KIND, OUTMODE>;
+  int rc = ensure_smem(kernel, SMEM_LIMIT, done);
+  if (rc) return rc;
+  const TallLayout L = rows_tall_layout(p.bn, p.rows_stages);
+  if (L.total > SMEM_LIMIT || p.rows_stages < 2 || p.bn < 32 || p.bn > 256 || (p.bn & 31)) return FLYB200_E_UNSUPPORTED;
+  const long long tiles = static_cast<long long>((p.M + TALL_ROWS - 1) / TALL_ROWS) * ((p.N + p.bn - 1) / p.bn);
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  kernel<<<grid, TALL_THREADS, L.total, s>>>(tmA, tmC, p);
   FLYB200_CUDA_TRY(cudaGetLastError());
   return FLYB200_OK;
 }
@@ -81,32 +98,33 @@ int launch_rows_scatter(const CUtensorMap& tmA, const OutputMaps& outs, const Ge
 }
 
 template <int KIND, int OUTMODE>
-int rows_any(bool two_sm, const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmC, const GemmParams& p,
+int rows_any(int form, const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmC, const GemmParams& p,
              int sms, cudaStream_t s) {
-  if (two_sm) return launch_rows2<KIND, OUTMODE>(tmA, tmW, tmC, p, sms, s);
+  if (form == ROWS_FORM_PAIRS) return launch_rows2<KIND, OUTMODE>(tmA, tmW, tmC, p, sms, s);
+  if (form == ROWS_FORM_TALL) return launch_rows_tall<KIND, OUTMODE>(tmA, tmC, p, sms, s);
   return launch_rows<KIND, OUTMODE>(tmA, tmC, p, sms, s);
 }
 
 }  // namespace
 
-int launch_rows_kind(int kind, int outmode, bool two_sm, const CUtensorMap& tmA, const CUtensorMap& tmW,
+int launch_rows_kind(int kind, int outmode, int form, const CUtensorMap& tmA, const CUtensorMap& tmW,
                      const CUtensorMap& tmC, const GemmParams& p, int sms, cudaStream_t s) {
   switch (kind) {
     case KIND_F8:
-      if (outmode == OUT_BF16) return rows_any<KIND_F8, OUT_BF16>(two_sm, tmA, tmW, tmC, p, sms, s);
-      if (outmode == OUT_FP16) return rows_any<KIND_F8, OUT_FP16>(two_sm, tmA, tmW, tmC, p, sms, s);
-      return rows_any<KIND_F8, OUT_RAW32>(two_sm, tmA, tmW, tmC, p, sms, s);
+      if (outmode == OUT_BF16) return rows_any<KIND_F8, OUT_BF16>(form, tmA, tmW, tmC, p, sms, s);
+      if (outmode == OUT_FP16) return rows_any<KIND_F8, OUT_FP16>(form, tmA, tmW, tmC, p, sms, s);
+      return rows_any<KIND_F8, OUT_RAW32>(form, tmA, tmW, tmC, p, sms, s);
     case KIND_I8:
-      if (outmode == OUT_BF16) return rows_any<KIND_I8, OUT_BF16>(two_sm, tmA, tmW, tmC, p, sms, s);
-      if (outmode == OUT_FP16) return rows_any<KIND_I8, OUT_FP16>(two_sm, tmA, tmW, tmC, p, sms, s);
-      return rows_any<KIND_I8, OUT_RAW32>(two_sm, tmA, tmW, tmC, p, sms, s);
+      if (outmode == OUT_BF16) return rows_any<KIND_I8, OUT_BF16>(form, tmA, tmW, tmC, p, sms, s);
+      if (outmode == OUT_FP16) return rows_any<KIND_I8, OUT_FP16>(form, tmA, tmW, tmC, p, sms, s);
+      return rows_any<KIND_I8, OUT_RAW32>(form, tmA, tmW, tmC, p, sms, s);
     case KIND_F16:
-      if (outmode == OUT_BF16) return rows_any<KIND_F16, OUT_BF16>(two_sm, tmA, tmW, tmC, p, sms, s);
-      if (outmode == OUT_FP16) return rows_any<KIND_F16, OUT_FP16>(two_sm, tmA, tmW, tmC, p, sms, s);
+      if (outmode == OUT_BF16) return rows_any<KIND_F16, OUT_BF16>(form, tmA, tmW, tmC, p, sms, s);
+      if (outmode == OUT_FP16) return rows_any<KIND_F16, OUT_FP16>(form, tmA, tmW, tmC, p, sms, s);
       break;
     case KIND_BF16:
-      if (outmode == OUT_BF16) return rows_any<KIND_BF16, OUT_BF16>(two_sm, tmA, tmW, tmC, p, sms, s);
-      if (outmode == OUT_FP16) return rows_any<KIND_BF16, OUT_FP16>(two_sm, tmA, tmW, tmC, p, sms, s);
+      if (outmode == OUT_BF16) return rows_any<KIND_BF16, OUT_BF16>(form, tmA, tmW, tmC, p, sms, s);
+      if (outmode == OUT_FP16) return rows_any<KIND_BF16, OUT_FP16>(form, tmA, tmW, tmC, p, sms, s);
       break;
   }
   return FLYB200_E_UNSUPPORTED;

@@ -162,7 +162,9 @@ __device__ __forceinline__ float load_bias(const void* bias, int col) {
 // several GPUs), starting with map `dst_first` (+ a per-tile, per-warp rotation)
 // so that neither the ranks nor the tiles of one rank all hit the same peer at
 // the same time.
-template <int KIND, int OUTMODE, typename ReleaseFn>
+// CBUFS: staging buffers of this warp at `stage_c` (two: the store of one chunk overlaps the
+// conversion of the next; one: where shared memory is short).
+template <int KIND, int OUTMODE, int CBUFS = 2, typename ReleaseFn>
 __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* tmC, int n_dst, int dst_first,
                                                    uint32_t t_row, int m0, int n0, int BN, int lane, uint32_t stage_c,
                                                    int& cbuf, ReleaseFn release_tmem) {
@@ -231,8 +233,8 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CU
       tmem_ld_x32(t_row + c0 + 32, r1);
       tmem_ld_wait();
       if (c0 + 64 >= BN) release_tmem();  // accumulator fully read: hand the TMEM buffer back
-      // the store issued two chunks ago has to be done reading this buffer
-      if (lane == 0) bulk_wait_group_read<1>();
+      // the store that last used this buffer (two chunks ago with two buffers) has to be done reading it
+      if (lane == 0) bulk_wait_group_read<CBUFS - 1>();
       __syncwarp();
       const uint32_t cdst = stage_c + cbuf * C_BUF + lane * 128;
 #pragma unroll
@@ -274,7 +276,7 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CU
         }
         bulk_commit_group();
       }
-      cbuf ^= 1;
+      cbuf = (cbuf + 1) % CBUFS;
     }
   }
 }

@@ -39,9 +39,12 @@ inline int rows_stages_for(int bn) {
   return s;
 }
 
-// Large-M kernel (p.bn, p.rows_stages set): one CTA per tile, or CTA pairs (`two_sm`, 256 x 256 tiles).
+// Large-M kernel (p.bn, p.rows_stages set) in one of three forms: one CTA per 128 x bn tile, CTA pairs
+// on 256 x 256 tiles (needs tmW), one CTA per 256 x bn tile (tmA with boxes of 256 rows, three stages).
 // `kind` is KIND_*, `outmode` OUT_*.
-int launch_rows_kind(int kind, int outmode, bool two_sm, const CUtensorMap& tmA, const CUtensorMap& tmW,
+enum : int { ROWS_FORM_ONE = 0, ROWS_FORM_PAIRS = 1, ROWS_FORM_TALL = 2 };
+constexpr int ROWS_TALL_STAGES = 3;
+int launch_rows_kind(int kind, int outmode, int form, const CUtensorMap& tmA, const CUtensorMap& tmW,
                      const CUtensorMap& tmC, const GemmParams& p, int sms, cudaStream_t s);
 // Large-M kernel storing every tile through p.n_dst output maps.
 int launch_rows_scatter_kind(int kind, int outmode, const CUtensorMap& tmA, const OutputMaps& outs, const GemmParams& p,

@@ -55,8 +55,8 @@ extern "C" {
 /* variant_hint: 0 = choose automatically.  Otherwise a bit field used for
  * tuning sweeps (each field: 0 = automatic):
  *   bits 0-7   small-M kernel: split-K factor; large-M kernel (one CTA per
- *              tile): tile width in units of 32 output channels (1..8, i.e.
- *              128 x 32 ... 128 x 256 tiles).  Automatic for the large-M kernel:
+ *              tile, kernels 2 and 6): tile width in units of 32 output channels
+ *              (1..8, i.e. 128 x 32 ... 128 x 256 tiles; 256 rows for kernel 6).  Automatic for the large-M kernel:
  *              the width whose tiles fill the SMs in the fewest, fullest rounds.
  *   bits 8-11  kernel: 1 = small-M weight-stationary kernel (M <= 256),
  *              2 = large-M persistent kernel, one CTA per 128 x (32..256) tile,
@@ -67,12 +67,16 @@ extern "C" {
  *              per pair, each CTA stages half of the token tile; token tiles of
  *              64..256, an even number of 128-channel tiles, K splits <= 4 inside
  *              the pair's cluster)
+ *              6 = large-M persistent kernel, one CTA per 256 x (32..256) tile (two
+ *              accumulators that share every weight block; three-stage ring)
  *              (automatic: M <= 256 -> 1 [5 when FLYB200_DECODE_PAIR=1 and the shape
  *              allows it; 4 when FLYB200_DECODE_W64=1 and the N/64 tiles fill
  *              75-100 % of the SMs], except for outputs so wide that the small-M
  *              kernel would run in several rounds of CTAs: with S SMs and
  *              T = ceil(N/128), M > 64 and T >= S, M > 32 and T > S, or M > 16 and
- *              T >= 3 S go to 2; M > 256 -> 2, or 3 when FLYB200_ROWS_2SM=1)
+ *              T >= 3 S go to 2; M > 256 -> 2, or 3 when FLYB200_ROWS_2SM=1, or 6
+ *              when FLYB200_ROWS_TALL=1 or when ceil(M/256) * ceil(N/256) tiles
+ *              cover the output in one round that fills at least 80 % of the SMs)
  *   bits 12-15 how K splits are combined: 1 = global workspace + ticket,
  *              2 = thread-block cluster + distributed shared memory (split <= 8)
  *   bits 16-23 rasterisation group (row tiles per group, large-M kernel)

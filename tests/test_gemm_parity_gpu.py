@@ -22,6 +22,7 @@ RTOL = ATOL = 1e-2  # stated tolerance for fp8 / scaled outputs against the fp32
 SENTINEL = -8192.0
 DEC, ROWS, ROWS2, W64 = 1 << 8, 2 << 8, 3 << 8, 4 << 8  # variant_hint: kernel field (small-M, large-M, large-M as CTA pairs, small-M with 64-channel tiles)
 PAIR = 5 << 8  # variant_hint: kernel field, small-M kernel as CTA pairs
+TALL = 6 << 8  # variant_hint: kernel field, large-M kernel with 256-row tiles
 WS, CL = 1 << 12, 2 << 12  # variant_hint: split-K reduction through a global workspace / a cluster
 PDL = 1 << 28  # variant_hint: programmatic dependent launch
 TOK1, TOK2, TOK4 = 1 << 30, 2 << 30, (3 << 30) - (1 << 32)  # variant_hint: token blocks (as signed 32-bit)
@@ -95,9 +96,9 @@ def test_scaled_output_matches_reference_check(dev, in_dtype, m, n, k, tile):
 @pytest.mark.parametrize(
     "hint",
     [DEC | 1, DEC | CL | 2, DEC | CL | 5, DEC | CL | 8, DEC | WS | 3, DEC | WS | 16, DEC | 2 | STAGES(3), DEC | 2 | PDL,
-     DEC | 2 | (2 << 28), W64, W64 | STAGES(3), DEC | TOK1 | 2, DEC | TOK2, DEC | TOK4, DEC | TOK2 | CL | 2, DEC | TOK4 | WS | 3, ROWS, ROWS2],
+     DEC | 2 | (2 << 28), W64, W64 | STAGES(3), DEC | TOK1 | 2, DEC | TOK2, DEC | TOK4, DEC | TOK2 | CL | 2, DEC | TOK4 | WS | 3, ROWS, ROWS2, TALL],
     ids=["nosplit", "cluster2", "cluster5", "cluster8", "ws3", "ws16", "stages3", "pdl", "nopdl", "w64", "w64_stages3", "tok1", "tok2", "tok4",
-         "tok2_cluster2", "tok4_ws3", "rows", "rows2"],
+         "tok2_cluster2", "tok4_ws3", "rows", "rows2", "tall"],
 )
 @pytest.mark.parametrize("m", [1, 16, 17, 64, 100, 256])
 def test_every_kernel_variant_small_m(dev, hint, m):
@@ -135,6 +136,17 @@ def test_small_m_kernel_as_cta_pairs(dev, hint, m):
 def test_cta_pair_kernel_scaled_output(dev, in_dtype, m, n, k):
     a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=31 + m)
     c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, in_dtype, hint=ROWS2)
+    check_scaled(c, a_q, b_q, sa, sb, m)
+
+
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
+@pytest.mark.parametrize("m,n,k", [(257, 1024, 1152), (513, 2064, 2048), (2048, 4096, 4096), (130, 528, 256)])
+def test_tall_tile_kernel_scaled_output(dev, in_dtype, m, n, k):
+    """256-row tiles: two accumulators per CTA share every weight block."""
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=37 + m)
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=128, tile_n=128, tile_k=128, in_dtype=in_dtype, variant_hint=TALL)
+    assert fn.plan(m)["kernel"] == 6
+    c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, in_dtype, hint=TALL)
     check_scaled(c, a_q, b_q, sa, sb, m)
 
 
@@ -209,6 +221,11 @@ def test_first_captured_call_allocates_nothing_when_compiled(dev):
         (300, 784, 1024, ROWS2),
         (100, 272, 256, ROWS2),
         (1024, 2048, 8320, ROWS2),
+        (300, 784, 1024, TALL),
+        (100, 272, 256, TALL),
+        (1024, 2048, 8320, TALL),
+        (700, 1040, 640, TALL | 5),  # 160-channel tiles: a 32-column tail in every tile
+        (2049, 512, 384, TALL | (3 << 16)),  # nine row tiles in groups of three
     ],
 )
 def test_int8_accumulators_bit_exact(dev, m, n, k, hint):
@@ -374,7 +391,7 @@ def run_gemm_generic(dev, a, b, sa, sb, bias, m, n, k, in_dtype, out_dtype="bf16
 
 
 @pytest.mark.parametrize("in_dtype", ["fp16", "bf16"])
-@pytest.mark.parametrize("m,n,k,hint", [(16, 5120, 8192, 0), (33, 1024, 2048, 0), (513, 1024, 2048, 0), (513, 1024, 2048, ROWS2), (200, 528, 1280, DEC | WS | 3),
+@pytest.mark.parametrize("m,n,k,hint", [(16, 5120, 8192, 0), (33, 1024, 2048, 0), (513, 1024, 2048, 0), (513, 1024, 2048, ROWS2), (513, 1024, 2048, TALL), (200, 528, 1280, DEC | WS | 3),
                                         (200, 512, 1280, PAIR | CL | 2), (72, 1024, 2048, PAIR)])
 def test_half_precision_inputs(dev, in_dtype, m, n, k, hint):
     g = torch.Generator().manual_seed(m + n)
@@ -440,7 +457,7 @@ def test_large_m_kernel_every_tile_width(dev, width, m, n, k):
     assert torch.equal(acc.cpu(), oracle.int32_acc(a_i, b_i))
 
 
-@pytest.mark.parametrize("width", [3, 7])
+@pytest.mark.parametrize("width", [3, 7, TALL | 3, TALL | 8])
 @pytest.mark.parametrize("in_dtype", ["fp8", "bf16"])
 def test_large_m_kernel_tile_tail_with_fused_epilogue(dev, width, in_dtype):
     m, n, k = 200, 1040, 1024
@@ -452,16 +469,22 @@ def test_large_m_kernel_tile_tail_with_fused_epilogue(dev, width, in_dtype):
         sa = sb = None
     else:
         a, b, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=width)
-    got = run_gemm_generic(dev, a, b, sa, sb, bias, m, n, k, in_dtype, epilogue="bias_silu", hint=ROWS | width)
+    got = run_gemm_generic(dev, a, b, sa, sb, bias, m, n, k, in_dtype, epilogue="bias_silu",
+                           hint=width if width > 8 else ROWS | width)  # a bare width: the one-CTA 128-row form
     ref = oracle.epilogue(a.float() @ b.float().T, sa, sb, bias, "bias_silu", out_dtype=torch.float32)
     assert oracle.strict_mismatches(got, ref, RTOL, ATOL) == 0
 
 
 def test_automatic_tile_width_fills_whole_rounds():
-    """The planner picks the width whose tiles cover the 148 SMs in full rounds: 1024 x 8192 gives
-    8 x 37 = 296 tiles of 224 channels (two rounds) instead of 256 tiles of 256 (1.73 rounds)."""
-    plan = _lib.describe_plan(1024, 8192, 8192, "fp8", 0, 148)
+    """The planner picks the width whose tiles cover the 148 SMs in full rounds: 2048 x 8192 gives
+    16 x 37 = 592 tiles of 224 channels (four rounds) instead of 512 tiles of 256 (3.46 rounds); and
+    where 256-row tiles cover the output in one nearly full round (1024 x 8192: 128 tiles) it takes those."""
+    plan = _lib.describe_plan(2048, 8192, 8192, "fp8", 0, 148)
     assert plan["kernel"] == 2 and plan["bn"] == 224
+    plan = _lib.describe_plan(1024, 8192, 8192, "fp8", 2 << 8, 148)  # the 128-row form on request
+    assert plan["kernel"] == 2 and plan["bn"] == 224
+    plan = _lib.describe_plan(1024, 8192, 8192, "fp8", 0, 148)
+    assert plan["kernel"] == 6 and plan["bn"] == 256
     assert _lib.describe_plan(16384, 57344, 8192, "fp8", 0, 148)["bn"] == 256
 
 

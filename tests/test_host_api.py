@@ -203,6 +203,13 @@ def test_variant_selection_is_a_pure_host_function():
     assert d(16, 57344, 8192)["kernel"] == 1 and d(32, 57344, 8192)["kernel"] == 2
     assert d(256, 16384, 8192)["kernel"] == 1
     assert d(128, 28672, 8192, variant_hint=1 << 8)["kernel"] == 1  # a request for the small-M kernel stands
+    # 256-row tiles: on request, and by themselves where they cover the output in one nearly full round
+    assert d(4096, 8192, 8192, variant_hint=6 << 8)["kernel"] == 6 and d(4096, 8192, 8192)["kernel"] == 2
+    p = d(1024, 8192, 8192)
+    assert (p["kernel"], p["bn"], p["stages"]) == (6, 256, 3)
+    assert d(1024, 4096, 8192)["kernel"] == 2 and d(2048, 8192, 8192)["kernel"] == 2
+    assert d(300, 16384, 8192)["kernel"] == 2  # 2 x 64 tiles would fit, but rows 384..511 would be padding
+    assert d(128, 37888, 8192)["kernel"] == 2  # wide output routed to the large-M kernel: 128-row tiles
     # small-M kernel as CTA pairs: on request, for token tiles of 64 and more and an even number of channel tiles
     p = d(256, 8192, 8192, variant_hint=5 << 8)
     assert (p["kernel"], p["bn"], p["split_k"], p["reduce"], p["stages"]) == (5, 256, 2, 2, 6)
