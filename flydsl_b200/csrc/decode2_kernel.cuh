@@ -139,7 +139,9 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
   // Per-channel operands of the four consecutive channels a thread owns in that sum, asked for now
   // and met after the mainloop.
   float sb4[4] = {0.f, 0.f, 0.f, 0.f}, bias4[4] = {0.f, 0.f, 0.f, 0.f};
-  if (p.reduce_mode == REDUCE_CLUSTER && reduces && n0 + lane * 4 < p.N) {  // (thread 0 has passed its griddepcontrol.wait above)
+  // an unsplit tile of 64 tokens or more leaves through shared memory too (whole token rows per warp)
+  const bool staged_out = p.reduce_mode == REDUCE_NONE && ALL_WARPS_REDUCE;
+  if ((p.reduce_mode == REDUCE_CLUSTER || staged_out) && reduces && n0 + lane * 4 < p.N) {  // (thread 0 has passed its griddepcontrol.wait above)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       if (p.sa != nullptr && p.sb != nullptr) sb4[e] = __ldg(p.sb + n0 + lane * 4 + e);
@@ -285,7 +287,7 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
     if (ok) {
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      if (p.reduce_mode == REDUCE_NONE) {
+      if (p.reduce_mode == REDUCE_NONE && !staged_out) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CH) {
           if (c0 >= M_loc) break;
@@ -328,6 +330,16 @@ gemm_decode2_kernel(const __grid_constant__ CUtensorMap tmA, const GemmParams p)
       } else {
         cluster_reduce_slice<KIND, OUTMODE, 4, ALL_WARPS_REDUCE ? 5 : 4, REDUCE_WARPS>(p, red_mine, crank, S, m_first, m_end, m_base, n4, col_ok, sa_s, sb4, bias4, scaled, prank, 2);
       }
+    }
+  }
+
+  if (staged_out) {
+    __syncthreads();  // the tile is in shared memory (every thread comes here: all waits above are bounded)
+    if (abort_flag[0] == 0) {
+      const int ch4 = lane * 4;
+      const int n4 = n0 + ch4;
+      cluster_reduce_slice<KIND, OUTMODE, 1, 16, REDUCE_WARPS>(p, red_base + static_cast<uint32_t>(ch4 * 4), crank, 1, warp, M_loc,
+                                                               m_base, n4, n4 < p.N, sa_s, sb4, bias4, scaled, crank, 1);
     }
   }
 

@@ -390,10 +390,10 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     // Wide outputs: the small-M kernel launches one CTA per 128 channels, so with more channel
     // tiles than SMs it runs in rounds and the last one is part empty; the large-M kernel is
     // persistent and walks 256-channel tiles.  Measured (FP8, K = 8192, us, small-M / large-M):
-    // N = 28672: M = 32 46/49, 64 52/49, 128 62/50, 256 86/67; N = 57344: M = 32 94/83, 128 123/86,
-    // 256 168/126; N = 18944 (exactly one round), K = 4096: M = 64 19/22, 128 24/22, 256 36/31.
+    // N = 28672: M = 32 46/49, 64 48/49, 128 58/50, 256 73/68; N = 57344: M = 32 94/83, 128 123/86,
+    // 256 168/126; N = 18944 (exactly one round), K = 4096: M = 64 17/21, 128 23/22, 256 31/30.
     const int tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
-    if ((tiles >= sms && M > 64) || (tiles > sms && M > 32) || (tiles >= 3 * sms && M > 16)) plan->decode = false;
+    if ((tiles >= sms && M > 64) || (tiles >= 3 * sms && M > 16)) plan->decode = false;
   }
   plan->two_sm = want_kernel == 3 ? true : (want_kernel == 2 || want_kernel == 6) ? false : rows_two_sm_default();
   plan->tall = !plan->decode && !plan->two_sm && (want_kernel == 6 || (want_kernel == 0 && rows_tall_default()));

@@ -73,8 +73,7 @@ extern "C" {
  *              allows it; 4 when FLYB200_DECODE_W64=1 and the N/64 tiles fill
  *              75-100 % of the SMs], except for outputs so wide that the small-M
  *              kernel would run in several rounds of CTAs: with S SMs and
- *              T = ceil(N/128), M > 64 and T >= S, M > 32 and T > S, or M > 16 and
- *              T >= 3 S go to 2; M > 256 -> 2, or 3 when FLYB200_ROWS_2SM=1, or 6
+ *              T = ceil(N/128), M > 64 and T >= S, or M > 16 and T >= 3 S go to 2; M > 256 -> 2, or 3 when FLYB200_ROWS_2SM=1, or 6
  *              when FLYB200_ROWS_TALL=1 or when ceil(M/256) * ceil(N/256) tiles
  *              cover the output in one round that fills at least 80 % of the SMs)
  *   bits 12-15 how K splits are combined: 1 = global workspace + ticket,

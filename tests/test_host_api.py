@@ -196,9 +196,9 @@ def test_variant_selection_is_a_pure_host_function():
     # the automatic split keeps the launch within one round of CTAs also where K is long
     p = d(64, 8192, 28672)
     assert (p["kernel"], p["split_k"], p["reduce"]) == (1, 2, 2)
-    # wide outputs (more channel tiles than SMs) go to the persistent kernel from 64 tokens up,
-    # very wide ones from 32 up; narrow ones stay on the small-M kernel
-    assert d(32, 28672, 8192)["kernel"] == 1 and d(64, 28672, 8192)["kernel"] == 2 and d(256, 28672, 8192)["kernel"] == 2
+    # wide outputs (at least as many channel tiles as SMs) go to the persistent kernel above 64 tokens,
+    # very wide ones above 16; narrow ones stay on the small-M kernel
+    assert d(64, 28672, 8192)["kernel"] == 1 and d(65, 28672, 8192)["kernel"] == 2 and d(256, 28672, 8192)["kernel"] == 2
     assert d(64, 18944, 4096)["kernel"] == 1 and d(128, 18944, 4096)["kernel"] == 2
     assert d(16, 57344, 8192)["kernel"] == 1 and d(32, 57344, 8192)["kernel"] == 2
     assert d(256, 16384, 8192)["kernel"] == 1
