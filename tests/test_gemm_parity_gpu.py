@@ -8,6 +8,8 @@ Shapes follow the reference's test matrix
 configurations.
 """
 
+import os
+
 import pytest
 import torch
 
@@ -479,6 +481,8 @@ def test_automatic_tile_width_fills_whole_rounds():
     """The planner picks the width whose tiles cover the 148 SMs in full rounds: 2048 x 8192 gives
     16 x 37 = 592 tiles of 224 channels (four rounds) instead of 512 tiles of 256 (3.46 rounds); and
     where 256-row tiles cover the output in one nearly full round (1024 x 8192: 128 tiles) it takes those."""
+    if os.environ.get("FLYB200_ROWS_TALL") == "1" or os.environ.get("FLYB200_ROWS_2SM") == "1":
+        pytest.skip("the environment overrides the automatic choice")
     plan = _lib.describe_plan(2048, 8192, 8192, "fp8", 0, 148)
     assert plan["kernel"] == 2 and plan["bn"] == 224
     plan = _lib.describe_plan(1024, 8192, 8192, "fp8", 2 << 8, 148)  # the 128-row form on request
