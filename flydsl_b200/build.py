@@ -29,6 +29,8 @@ SOURCES = [
     "flyb200.cu",
     "flyb200_rows.cu",
     "flyb200_decode.cu",
+    "flyb200_decode_wide.cu",
+    "flyb200_decode2.cu",
     "flyb200_moe.cu",
     "flyb200_mx.cu",
 ]
@@ -43,6 +45,7 @@ HEADERS = [
     "moe_kernel.cuh",
     "mx_kernel.cuh",
     "launch.h",
+    "decode_launch.h",
     "host_common.h",
     os.path.join("..", "..", "include", "flyb200.h"),
 ]
