@@ -38,8 +38,10 @@ namespace flyb200 {
 // Arrive on a barrier of the peer CTA without a cluster-scope fence.  What the
 // arrival announces was written into THIS CTA's shared memory by its own TMA
 // loads and is read by this SM's own tensor core once the leader issues the
-// pair's MMA, so nothing has to become visible to the other SM; a
-// release at cluster scope here costs about half a microsecond per k-block.
+// pair's MMA, so nothing has to become visible to the other SM (in the other
+// direction, "stage free", the arrival follows a tcgen05.commit that already
+// covers the peer SM's reads of its own shared memory); a release at cluster
+// scope here costs about half a microsecond per k-block.
 __device__ __forceinline__ void mbar_arrive_peer(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
