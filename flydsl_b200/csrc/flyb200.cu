@@ -395,6 +395,16 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     const int tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
     if ((tiles >= sms && M > 64) || (tiles >= 3 * sms && M > 16)) plan->decode = false;
   }
+  if (want_kernel == 0 && M > 256 && M <= 1024) {
+    // Narrow outputs with 257..1024 tokens and a long K: the large-M kernel has too few tiles for the
+    // SMs and no K split; the small-M kernel takes the tokens in blocks of 256 (grid.z) and splits K
+    // over a cluster.  Taken where (channel tiles x token blocks) leave room for a split of two or
+    // more in one round of CTAs.  Measured, small-M / large-M, us: 512 x 2048 x 8192 16.3 / 23.5,
+    // 512 x 4096 x 8192 24.1 / 26.5, 1024 x 2048 x 8192 24.1 / 26.9; with 128 unsplit CTAs the
+    // large-M kernel wins (512 x 8192 x 8192 41.9 / 38.5).
+    const int ctas = ((N + BLOCK_ROWS - 1) / BLOCK_ROWS) * ((M + 255) / 256);
+    plan->decode = 2 * ctas <= sms && K_bytes / KBLOCK_BYTES >= 32;
+  }
   plan->two_sm = want_kernel == 3 ? true : (want_kernel == 2 || want_kernel == 6) ? false : rows_two_sm_default();
   plan->tall = !plan->decode && !plan->two_sm && (want_kernel == 6 || (want_kernel == 0 && rows_tall_default()));
   if (want_kernel == 0 && !plan->decode && !plan->two_sm && !plan->tall && want_split == 0) {
@@ -407,7 +417,7 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     const bool no_extra_rows = (M + 255) / 256 * 2 == (M + 127) / 128;
     plan->tall = M > 256 && no_extra_rows && t <= sms && 5 * t >= 4 * sms;
   }
-  if (plan->decode && M > 256) return FLYB200_E_UNSUPPORTED;
+  if (plan->decode && M > 1024) return FLYB200_E_UNSUPPORTED;  // up to four token blocks of 256
   if (want_reduce > REDUCE_CLUSTER) return FLYB200_E_BAD_ARG;
   plan->token_blocks = 1;
   plan->w_rows = BLOCK_ROWS;
@@ -478,8 +488,10 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
   const int kb = K_bytes / KBLOCK_BYTES;
   plan->kb_per_split = kb;
   if (plan->decode) {
+    // (more than 256 tokens: cluster splits only, so that no such call ever needs a workspace)
     int split = want_split > 0 ? want_split
-                               : auto_split_k(N, K_bytes, sms, plan->bn, plan->token_blocks, workspace_bytes, have_ws, plan->pair);
+                               : auto_split_k(N, K_bytes, sms, plan->bn, plan->token_blocks, workspace_bytes,
+                                              have_ws && M <= 256, plan->pair);
     if (plan->w_rows == 64) split = 1;
     if (split > kb) split = kb;
     int mode = REDUCE_NONE;

@@ -9,8 +9,9 @@ The builder specialises on (N, K, dtypes, epilogue) and validates its
 arguments exactly where the reference raises ``ValueError``.  ``tile_*`` and
 the AMD scheduling knobs are accepted and validated but are hints only: the
 library picks the kernel variant per call from M (weight-stationary split-K
-kernel for M <= 256, persistent 128x256 tile kernel above), so one launcher
-serves every M without recompiling, as the reference's runtime ``M`` does.
+kernel for M <= 256 and for narrow outputs up to M = 1024, persistent tile
+kernels above), so one launcher serves every M without recompiling, as the
+reference's runtime ``M`` does.
 """
 
 from __future__ import annotations
@@ -34,7 +35,7 @@ _TORCH_OUT = {"bf16": torch.bfloat16, "fp16": torch.float16}
 _workspaces: dict = {}
 _retired: list = []
 _TICKET_BYTES = 16384
-_WORST_CASE_M = (16, 32, 64, 128, 256)  # one M per token-block width of the small-M kernel
+_WORST_CASE_M = (16, 32, 64, 128, 256, 512, 768, 1024)  # every token-block width and count of the small-M kernel
 
 
 def _stream_handle(stream) -> int:

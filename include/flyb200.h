@@ -58,7 +58,8 @@ extern "C" {
  *              tile, kernels 2 and 6): tile width in units of 32 output channels
  *              (1..8, i.e. 128 x 32 ... 128 x 256 tiles; 256 rows for kernel 6).  Automatic for the large-M kernel:
  *              the width whose tiles fill the SMs in the fewest, fullest rounds.
- *   bits 8-11  kernel: 1 = small-M weight-stationary kernel (M <= 256),
+ *   bits 8-11  kernel: 1 = small-M weight-stationary kernel (M <= 1024: up to 256
+ *              tokens per CTA, more as token blocks of 256 in grid.z),
  *              2 = large-M persistent kernel, one CTA per 128 x (32..256) tile,
  *              3 = large-M persistent kernel, CTA pairs on 256x256 tiles
  *              4 = small-M kernel with 64-channel weight tiles and no K split
@@ -73,7 +74,9 @@ extern "C" {
  *              allows it; 4 when FLYB200_DECODE_W64=1 and the N/64 tiles fill
  *              75-100 % of the SMs], except for outputs so wide that the small-M
  *              kernel would run in several rounds of CTAs: with S SMs and
- *              T = ceil(N/128), M > 64 and T >= S, or M > 16 and T >= 3 S go to 2; M > 256 -> 2, or 3 when FLYB200_ROWS_2SM=1, or 6
+ *              T = ceil(N/128), M > 64 and T >= S, or M > 16 and T >= 3 S go to 2;
+ *              256 < M <= 1024 -> 1 when 2 * T * ceil(M/256) <= S and K spans at
+ *              least 32 blocks of 128 bytes; else M > 256 -> 2, or 3 when FLYB200_ROWS_2SM=1, or 6
  *              when FLYB200_ROWS_TALL=1 or when ceil(M/256) * ceil(N/256) tiles
  *              cover the output in one round that fills at least 80 % of the SMs)
  *   bits 12-15 how K splits are combined: 1 = global workspace + ticket,

@@ -141,6 +141,24 @@ def test_cta_pair_kernel_scaled_output(dev, in_dtype, m, n, k):
     check_scaled(c, a_q, b_q, sa, sb, m)
 
 
+@pytest.mark.parametrize("in_dtype", ["fp8", "int8", "bf16"])
+@pytest.mark.parametrize("m,n,k", [(300, 2048, 4096), (512, 1024, 8192), (1024, 2048, 4096), (777, 1040, 4096)])
+def test_narrow_output_mid_m_runs_on_the_small_m_kernel(dev, in_dtype, m, n, k):
+    """257..1024 tokens, few channel tiles, long K: token blocks of 256 on the small-M kernel (automatic)."""
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=128, tile_n=128, tile_k=128, in_dtype=in_dtype)
+    assert fn.plan(m)["kernel"] in (1, 5) and fn.plan(m)["token_blocks"] == -(-m // 256)  # 5: pairs, if the environment asks
+    if in_dtype == "bf16":
+        g = torch.Generator().manual_seed(m)
+        a = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16)
+        b = (torch.randn(n, k, generator=g) * 0.5).to(torch.bfloat16)
+        got = run_gemm_generic(dev, a, b, None, None, None, m, n, k, in_dtype)
+        assert oracle.strict_mismatches(got, oracle.run_torch(a, b, None, None), RTOL, ATOL) == 0
+        return
+    a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, in_dtype, seed=41 + m)
+    c = run_gemm(dev, a_q, b_q, sa, sb, m, n, k, in_dtype)
+    check_scaled(c, a_q, b_q, sa, sb, m)
+
+
 @pytest.mark.parametrize("in_dtype", ["fp8", "int8"])
 @pytest.mark.parametrize("m,n,k", [(257, 1024, 1152), (513, 2064, 2048), (2048, 4096, 4096), (130, 528, 256)])
 def test_tall_tile_kernel_scaled_output(dev, in_dtype, m, n, k):
@@ -217,6 +235,10 @@ def test_first_captured_call_allocates_nothing_when_compiled(dev):
         (130, 1936, 640, PAIR | CL | 4),
         (200, 512, 1024, PAIR | CL | 2),
         (256, 2048, 4096, PAIR),
+        (512, 1024, 2048, DEC),  # more than 256 tokens: token blocks of 256 (grid.z), K split over a cluster
+        (700, 2048, 1024, DEC | CL | 2),  # three token blocks, the last one part empty
+        (1000, 512, 4096, DEC),
+        (300, 2048, 4096, 0),  # the automatic choice for a narrow output: small-M kernel, two token blocks
         (8, 57344, 256, 0),  # very wide: more channel tiles than SMs
         (300, 784, 1024, ROWS),
         (1024, 2048, 8320, ROWS),  # K = 65 * 128 as in the reference's large shapes

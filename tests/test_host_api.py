@@ -187,8 +187,7 @@ def test_variant_selection_is_a_pure_host_function():
     assert d(32, 8192, 8192, variant_hint=(1 << 8) | (1 << 12) | 16)["reduce"] == 1
     with pytest.raises(_lib.FlyB200Error):
         d(32, 8192, 8192, variant_hint=(1 << 8) | (2 << 12) | 16)  # a cluster cannot hold 16 splits
-    with pytest.raises(_lib.FlyB200Error):
-        d(300, 8192, 8192, variant_hint=1 << 8)  # small-M kernel beyond 256 tokens
+    assert d(300, 8192, 8192, variant_hint=1 << 8)["token_blocks"] == 2  # beyond 256 tokens: blocks of 256
     # a single k-block cannot be split
     assert d(16, 1024, 128)["split_k"] == 1
     # fewer SMs -> smaller split
@@ -210,6 +209,13 @@ def test_variant_selection_is_a_pure_host_function():
     assert d(1024, 4096, 8192)["kernel"] == 2 and d(2048, 8192, 8192)["kernel"] == 2
     assert d(300, 16384, 8192)["kernel"] == 2  # 2 x 64 tiles would fit, but rows 384..511 would be padding
     assert d(128, 37888, 8192)["kernel"] == 2  # wide output routed to the large-M kernel: 128-row tiles
+    # 257..1024 tokens on a narrow output with a long K: token blocks of 256 on the small-M kernel
+    p = d(512, 2048, 8192)
+    assert (p["kernel"], p["bn"], p["token_blocks"], p["split_k"], p["reduce"]) == (1, 256, 2, 4, 2)
+    assert d(1024, 2048, 8192)["token_blocks"] == 4 and d(1025, 2048, 8192)["kernel"] == 2
+    assert d(512, 8192, 8192)["kernel"] == 2 and d(512, 4096, 2048)["kernel"] == 2  # too many tiles; K too short
+    with pytest.raises(_lib.FlyB200Error):
+        d(1025, 2048, 8192, variant_hint=1 << 8)  # four token blocks of 256 are the limit
     # small-M kernel as CTA pairs: on request, for token tiles of 64 and more and an even number of channel tiles
     p = d(256, 8192, 8192, variant_hint=5 << 8)
     assert (p["kernel"], p["bn"], p["split_k"], p["reduce"], p["stages"]) == (5, 256, 2, 2, 6)
