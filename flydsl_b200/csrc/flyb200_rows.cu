@@ -12,6 +12,24 @@ namespace flyb200 {
 namespace host {
 namespace {
 
+// One-dimensional launch, optionally with the programmatic-stream-serialisation attribute.
+template <typename KernelT, typename... Args>
+int launch_plain_or_pdl(KernelT kernel, int grid, int threads, int smem, cudaStream_t s, bool pdl, const Args&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  FLYB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, args...));
+  return FLYB200_OK;
+}
+
 template <int KIND, int OUTMODE>
 int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams& p, int sms, cudaStream_t s) {
   static std::atomic<uint64_t> done{0};
@@ -22,9 +40,7 @@ int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmParams
   if (L.total > SMEM_LIMIT || p.bn < 32 || p.bn > 256 || (p.bn & 31)) return FLYB200_E_UNSUPPORTED;
   const long long tiles = static_cast<long long>((p.M + BLOCK_ROWS - 1) / BLOCK_ROWS) * ((p.N + p.bn - 1) / p.bn);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, NUM_THREADS, L.total, s>>>(tmA, tmC, p);
-  FLYB200_CUDA_TRY(cudaGetLastError());
-  return FLYB200_OK;
+  return launch_plain_or_pdl(kernel, grid, NUM_THREADS, L.total, s, p.pdl != 0, tmA, tmC, p);
 }
 
 // One CTA per 256 x bn tile (tmA: boxes of 256 rows).
@@ -38,9 +54,7 @@ int launch_rows_tall(const CUtensorMap& tmA, const CUtensorMap& tmC, const GemmP
   if (L.total > SMEM_LIMIT || p.rows_stages < 2 || p.bn < 32 || p.bn > 256 || (p.bn & 31)) return FLYB200_E_UNSUPPORTED;
   const long long tiles = static_cast<long long>((p.M + TALL_ROWS - 1) / TALL_ROWS) * ((p.N + p.bn - 1) / p.bn);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  kernel<<<grid, TALL_THREADS, L.total, s>>>(tmA, tmC, p);
-  FLYB200_CUDA_TRY(cudaGetLastError());
-  return FLYB200_OK;
+  return launch_plain_or_pdl(kernel, grid, TALL_THREADS, L.total, s, p.pdl != 0, tmA, tmC, p);
 }
 
 template <int KIND, int OUTMODE>

@@ -340,6 +340,10 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
     if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_SMEM_ALIGN);
     return;
   }
+  // Programmatic dependent launch (p.pdl != 0): the next kernel on the stream may be scheduled onto
+  // SMs as this one frees them, and this one runs its set-up (barriers, TMEM) while the previous
+  // kernel finishes; no global memory is read or written before griddepcontrol.wait below.
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -367,6 +371,7 @@ __device__ __forceinline__ void gemm_rows_body(const CUtensorMap& tmA, const CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has completed
 
   const int num_m = (p.M + BLOCK_ROWS - 1) / BLOCK_ROWS;
   const int num_n = (p.N + BN - 1) / BN;

@@ -57,6 +57,8 @@ gemm_rows_tall_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (threadIdx.x == 0) atomicCAS(p.status, 0, ST_SMEM_ALIGN);
     return;
   }
+  // programmatic dependent launch: set-up below overlaps the previous kernel's tail; no global access before the wait
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -79,6 +81,7 @@ gemm_rows_tall_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous kernel has completed
 
   const int num_m = (p.M + TALL_ROWS - 1) / TALL_ROWS;
   const int num_n = (p.N + BN - 1) / BN;

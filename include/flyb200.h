@@ -85,7 +85,8 @@ extern "C" {
  *   bits 24-27 depth of the shared-memory ring of the small-M kernel (an odd
  *              depth becomes the next even one, or the one below when that
  *              does not fit into shared memory)
- *   bits 28-29 programmatic dependent launch of the small-M kernel: 1 = on (its
+ *   bits 28-29 programmatic dependent launch (small-M kernel; large-M kernels when
+ *              the launch has at most two rounds of tiles): 1 = on (its
  *              set-up overlaps the tail of the previous kernel on the stream; no
  *              global memory is touched before that kernel has completed),
  *              3 = on, and additionally the first weight loads are issued before
