@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) gemm_decode_kernel(const __
   // channels per lane).  Storing straight from the accumulator layout (one channel per thread) is
   // kept for smaller tiles: it costs ~45 ns per token (6 us at 128 tokens, 14 us at 256).
   const bool staged_out = p.reduce_mode == REDUCE_NONE && ALL_WARPS_REDUCE && WROWS == BLOCK_ROWS;
-  if ((p.reduce_mode == REDUCE_CLUSTER || staged_out) && reduces && n0 + lane * 4 < p.N) {  // (thread 0 has passed its griddepcontrol.wait above)
+  if ((p.reduce_mode != REDUCE_NONE || staged_out) && reduces && n0 + lane * 4 < p.N) {  // (thread 0 has passed its griddepcontrol.wait above)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       if (p.sa != nullptr && p.sb != nullptr) sb4[e] = __ldg(p.sb + n0 + lane * 4 + e);
@@ -574,32 +574,62 @@ __global__ void __launch_bounds__(DECODE_THREADS, 1) gemm_decode_kernel(const __
         named_bar_sync(1, 128);
         if (*last_flag) {
           __threadfence();
-          const uint32_t* src = part + tile_id * tile_elems + ch_local;
+          // Sum the splits in the fixed order k = 0, 1, ... (the result does not depend on which CTA
+          // happened to arrive last).  The partial tiles are [token][channel] like the staged tiles of
+          // the cluster path, so the same split of work applies: a warp takes one token at a time and
+          // each lane four consecutive channels; sixteen 16-byte loads are in flight per thread.
+          const int ew4 = warp - 2;  // 0..3
+          const int ch4 = lane * 4;
+          const int n4 = n0 + ch4;
+          const bool col_ok = n4 < p.N;  // N is a multiple of 4
+          const uint32_t* src = part + tile_id * tile_elems + ch4;
           const int m_lim = M_loc;
-          constexpr int U = 8;  // tokens in flight per thread
+          constexpr int U = 4, KU = 4;  // tokens x splits in flight
 #pragma unroll 1
-          for (int m0 = 0; m0 < m_lim; m0 += U) {
-            // fixed summation order over the splits: the result does not
-            // depend on which CTA happened to arrive last
-            uint32_t acc[U];
+          for (int mb = ew4; mb < m_lim; mb += 4 * U) {
+            uint4 acc[U];
 #pragma unroll
-            for (int j = 0; j < U; ++j) acc[j] = 0u;
-            for (int k = 0; k < p.split_k; ++k) {
-              uint32_t v[U];
-#pragma unroll
-              for (int j = 0; j < U; ++j)
-                v[j] = (m0 + j < m_lim) ? __ldcg(src + k * split_stride + static_cast<size_t>(m0 + j) * BLOCK_ROWS) : 0u;
+            for (int j = 0; j < U; ++j) acc[j] = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 1
+            for (int k0 = 0; k0 < p.split_k; k0 += KU) {
+              uint4 v[U][KU];
 #pragma unroll
               for (int j = 0; j < U; ++j) {
-                if constexpr (KT::is_int) {
-                  acc[j] = static_cast<uint32_t>(static_cast<int32_t>(acc[j]) + static_cast<int32_t>(v[j]));
-                } else {
-                  acc[j] = __float_as_uint((k == 0 ? 0.0f : __uint_as_float(acc[j])) + __uint_as_float(v[j]));
+#pragma unroll
+                for (int kk = 0; kk < KU; ++kk) {
+                  const int m = mb + 4 * j, k = k0 + kk;
+                  v[j][kk] = (m < m_lim && k < p.split_k)
+                                 ? __ldcg(reinterpret_cast<const uint4*>(src + k * split_stride + static_cast<size_t>(m) * BLOCK_ROWS))
+                                 : make_uint4(0u, 0u, 0u, 0u);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < U; ++j) {
+#pragma unroll
+                for (int kk = 0; kk < KU; ++kk) {
+                  if (k0 + kk < p.split_k) {
+                    if constexpr (KT::is_int) {
+                      acc[j].x = add_raw<true>(acc[j].x, v[j][kk].x);
+                      acc[j].y = add_raw<true>(acc[j].y, v[j][kk].y);
+                      acc[j].z = add_raw<true>(acc[j].z, v[j][kk].z);
+                      acc[j].w = add_raw<true>(acc[j].w, v[j][kk].w);
+                    } else if (k0 + kk == 0) {
+                      acc[j] = v[j][kk];  // the first partial as it is, as in the cluster path
+                    } else {
+                      acc[j].x = add_raw<false>(acc[j].x, v[j][kk].x);
+                      acc[j].y = add_raw<false>(acc[j].y, v[j][kk].y);
+                      acc[j].z = add_raw<false>(acc[j].z, v[j][kk].z);
+                      acc[j].w = add_raw<false>(acc[j].w, v[j][kk].w);
+                    }
+                  }
                 }
               }
             }
 #pragma unroll
-            for (int j = 0; j < U; ++j) emit(m0 + j, acc[j]);
+            for (int j = 0; j < U; ++j) {
+              const int m = mb + 4 * j;
+              if (m < m_lim && col_ok) store_reduced<KIND, OUTMODE>(p, acc[j], m, m_base, n4, sa_s, sb4, bias4, scaled);
+            }
           }
         }
       }

@@ -184,10 +184,14 @@ int fill_sms_split_k(int N, int K_bytes, int sms, int token_blocks = 1) {
 //   reduction  cluster: two cluster barriers and a remote round trip (~1.5 us)
 //              plus the (split-1)/split of a partial tile (bn x 512 B) every CTA
 //              reads from its peers at ~15 B/ns; clusters of more than four CTAs
-//              measured ~10 us slower than the model (scheduling of large clusters
-//              that each need a whole SM's shared memory).  Workspace: ~3 us
+//              measured ~10 us slower than the model when they cover more than
+//              half of the SMs (scheduling of large clusters that each need a
+//              whole SM's shared memory; eight clusters of eight are fine: 16 x
+//              1024 x 8192 5.7 us, 32 x 1024 x 28672 11.1 us).  Workspace: ~3 us
 //              (ticket, fences) plus the last CTA reading `split` partial tiles
-//              from L2 at ~100 B/ns.
+//              from L2, latency-bound at ~14 B/ns (16 x 1024 x 8192 with 13
+//              splits: 12.4 us), so it is what remains when a cluster cannot
+//              supply enough CTAs.
 // Reproduces the measured ranking: split 2 at 64 channel tiles (14.5 us against
 // 21 us unsplit and 15 us for split 4), split 4 at 32 tiles of 128 tokens (9.8 us
 // against 12.1 / 19.0 / 21.4 us for 2 / 1 / 8).
@@ -202,8 +206,10 @@ double split_cost_ns(int split, int n_tiles, int kb, int bn, int sms, bool clust
   double reduce = 0.0;
   if (split > 1) {
     const double partial = bn * 512.0;
-    reduce = cluster ? 1500.0 + (split - 1.0) / split * partial / 15.0 + ((pair ? 2 * split : split) > 4 ? 10000.0 : 0.0)
-                     : 3000.0 + split * partial / 100.0;
+    // clusters of more than four CTAs are slow to place when they cover more than half of the SMs
+    const bool crowded = (pair ? 2 * split : split) > 4 && 2 * n_tiles * split > sms;
+    reduce = cluster ? 1500.0 + (split - 1.0) / split * partial / 15.0 + (crowded ? 10000.0 : 0.0)
+                     : 3000.0 + split * partial / 14.0;
   }
   return 3000.0 + stream + reduce;
 }

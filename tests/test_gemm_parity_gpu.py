@@ -171,14 +171,15 @@ def test_tall_tile_kernel_scaled_output(dev, in_dtype, m, n, k):
 
 
 def test_first_captured_call_allocates_nothing_when_compiled(dev):
-    """A narrow-N shape reduces its K splits through a global workspace.  flyc.compile allocates
+    """A launcher asked to reduce its K splits through a global workspace.  flyc.compile allocates
     that workspace for the stream it is given, so the launcher's very first call may be a captured
     one; without compile a first call inside a capture is refused with a clear message instead of
     allocating behind the capture."""
     m, n, k = 16, 1024, 8192
     a_q, b_q, sa, sb = oracle.make_inputs(m, n, k, "fp8", seed=77)
     s = torch.cuda.Stream()
-    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype="fp8")
+    hint = DEC | WS | 16
+    fn = compile_preshuffle_gemm(N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype="fp8", variant_hint=hint)
     assert fn.plan(m)["reduce"] == 1 and fn.workspace_bytes(dev) > 16384  # the workspace path
     c = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
     args = (c.view(-1), as_i8(a_q.to(dev)).view(-1), as_i8(shuffle_weight(b_q.to(dev))).view(-1), sa.to(dev), sb.to(dev),
@@ -191,7 +192,7 @@ def test_first_captured_call_allocates_nothing_when_compiled(dev):
             fn(*args)
     torch.cuda.synchronize()
     # (2) compiled on the capture stream: the first call is the captured one and allocates nothing
-    fn2 = compile_preshuffle_gemm(N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype="fp8")
+    fn2 = compile_preshuffle_gemm(N=n, K=k, tile_m=16, tile_n=64, tile_k=256, in_dtype="fp8", variant_hint=hint)
     cf = flyc.compile(fn2, *args)
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated(dev)
