@@ -206,8 +206,12 @@ double split_cost_ns(int split, int n_tiles, int kb, int bn, int sms, bool clust
   double reduce = 0.0;
   if (split > 1) {
     const double partial = bn * 512.0;
-    // clusters of more than four CTAs are slow to place when they cover more than half of the SMs
-    const bool crowded = (pair ? 2 * split : split) > 4 && 2 * n_tiles * split > sms;
+    // Clusters have to be placed whole inside a GPC, so fewer CTAs are resident at once than there are
+    // SMs: clusters of more than four CTAs are slow to place when they cover more than two thirds of
+    // the SMs (16 x 8 CTAs: 12.2 us against 7.3 us for 16 x 4; 12 x 8 is fine), clusters of three or
+    // more when they cover more than 90 % (48 x 3 = 144 CTAs: 18.3 us against 12.0 us for 48 x 2).
+    const int csize = pair ? 2 * split : split;
+    const bool crowded = (csize > 4 && 3 * n_tiles * split > 2 * sms) || (csize >= 3 && 10 * n_tiles * split > 9 * sms);
     reduce = cluster ? 1500.0 + (split - 1.0) / split * partial / 15.0 + (crowded ? 10000.0 : 0.0)
                      : 3000.0 + split * partial / 14.0;
   }
