@@ -400,10 +400,15 @@ int make_plan(Plan* plan, int M, int N, int K_bytes, int variant_hint, size_t wo
     // Wide outputs: the small-M kernel launches one CTA per 128 channels, so with more channel
     // tiles than SMs it runs in rounds and the last one is part empty; the large-M kernel is
     // persistent and walks 256-channel tiles.  Measured (FP8, K = 8192, us, small-M / large-M):
-    // N = 28672: M = 32 46/49, 64 48/49, 128 58/50, 256 73/68; N = 57344: M = 32 94/83, 128 123/86,
-    // 256 168/126; N = 18944 (exactly one round), K = 4096: M = 64 17/21, 128 23/22, 256 31/30.
+    // N = 28672 (224 tiles): M = 32 47/48, 64 49/49, 96 55/49, 200 71/66; N = 24576 (192 tiles, the
+    // second round 30 % full): M = 16 43/41, 32 46/41, 64 48/41, 96 53/42; N = 57344 (448 tiles):
+    // M = 16 89/81, 32 95/83, 96 104/85; N = 18944 (exactly one round): M = 96 31/32, 200 41/43.
     const int tiles = (N + BLOCK_ROWS - 1) / BLOCK_ROWS;
-    if ((tiles >= sms && M > 64) || (tiles >= 3 * sms && M > 16)) plan->decode = false;
+    const int rounds = (tiles + sms - 1) / sms;
+    const bool poor_fill = 10 * tiles < 7 * rounds * sms;  // the rounds are less than 70 % full
+    // (16 tokens on a very wide output: 89/81 at K = 8192, but 52/62 at K = 4096)
+    const bool very_wide = tiles >= 3 * sms && (M > 16 || (M == 16 && K_bytes >= 8192));
+    if (tiles > sms && (M > 64 || (poor_fill && M >= 32) || very_wide)) plan->decode = false;
   }
   if (want_kernel == 0 && M > 256 && M <= 1024) {
     // Narrow outputs with 257..1024 tokens and a long K: the large-M kernel has too few tiles for the

@@ -74,7 +74,8 @@ extern "C" {
  *              allows it; 4 when FLYB200_DECODE_W64=1 and the N/64 tiles fill
  *              75-100 % of the SMs], except for outputs so wide that the small-M
  *              kernel would run in several rounds of CTAs: with S SMs and
- *              T = ceil(N/128), M > 64 and T >= S, or M > 16 and T >= 3 S go to 2;
+ *              T = ceil(N/128) > S, M > 64, or M >= 32 when the rounds are less than
+ *              70 % full, or M > 16 (M = 16 with K >= 8192 bytes) when T >= 3 S, go to 2;
  *              256 < M <= 1024 -> 1 when 2 * T * ceil(M/256) <= S and K spans at
  *              least 32 blocks of 128 bytes; else M > 256 -> 2, or 3 when FLYB200_ROWS_2SM=1, or 6
  *              when FLYB200_ROWS_TALL=1 or when ceil(M/256) * ceil(N/256) tiles

@@ -195,11 +195,12 @@ def test_variant_selection_is_a_pure_host_function():
     # the automatic split keeps the launch within one round of CTAs also where K is long
     p = d(64, 8192, 28672)
     assert (p["kernel"], p["split_k"], p["reduce"]) == (1, 2, 2)
-    # wide outputs (at least as many channel tiles as SMs) go to the persistent kernel above 64 tokens,
-    # very wide ones above 16; narrow ones stay on the small-M kernel
+    # wide outputs (more channel tiles than SMs) go to the persistent kernel above 64 tokens, badly
+    # filled rounds from 32, very wide ones from 16; narrow ones stay on the small-M kernel
     assert d(64, 28672, 8192)["kernel"] == 1 and d(65, 28672, 8192)["kernel"] == 2 and d(256, 28672, 8192)["kernel"] == 2
-    assert d(64, 18944, 4096)["kernel"] == 1 and d(128, 18944, 4096)["kernel"] == 2
-    assert d(16, 57344, 8192)["kernel"] == 1 and d(32, 57344, 8192)["kernel"] == 2
+    assert d(64, 18944, 4096)["kernel"] == 1 and d(200, 18944, 4096)["kernel"] == 1  # exactly one round of CTAs
+    assert d(16, 24576, 8192)["kernel"] == 1 and d(32, 24576, 8192)["kernel"] == 2  # second round 30 % full
+    assert d(8, 57344, 8192)["kernel"] == 1 and d(16, 57344, 8192)["kernel"] == 2
     assert d(256, 16384, 8192)["kernel"] == 1
     assert d(128, 28672, 8192, variant_hint=1 << 8)["kernel"] == 1  # a request for the small-M kernel stands
     # 256-row tiles: on request, and by themselves where they cover the output in one nearly full round
