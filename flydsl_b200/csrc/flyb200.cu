@@ -794,6 +794,13 @@ int status_word(int** out) {
   return FLYB200_OK;
 }
 int record_cuda_error(cudaError_t e, const char* what) { return cuda_fail(e, what); }
+int sm_count(int* out) {
+  DeviceState* st = nullptr;
+  const int rc = device_state(&st);
+  if (rc) return rc;
+  *out = st->sms;
+  return FLYB200_OK;
+}
 }  // namespace host
 }  // namespace flyb200
 

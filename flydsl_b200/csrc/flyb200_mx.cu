@@ -63,6 +63,23 @@ int flyb200_mx_scale_image(void* dst, const void* src, int rows, int K, void* st
   return FLYB200_OK;
 }
 
+namespace {
+// Up to 128 tokens are a weight stream for the small-M kernel in its block-scaled kind - as long as its
+// CTAs (one per 128 channels) fit one round: on wider outputs its later rounds run part empty and the
+// persistent large-M kernel is 20-45 % faster (MXFP8 128 x 28672 x 8192: 43 against 66 us; MXFP4 128 x
+// 57344 x 8192: 51 against 90 us).  FLYB200_MX_SMALL=0 / 1 forces the choice.
+bool mx_small_m(int M, int N) {
+  if (M > 128) return false;
+  if (const char* e = getenv("FLYB200_MX_SMALL")) {
+    if (e[0] == '0') return false;
+    if (e[0] == '1') return true;
+  }
+  int sms = 0;
+  if (flyb200::host::sm_count(&sms) != FLYB200_OK) return true;
+  return (N + 127) / 128 <= sms;
+}
+}  // namespace
+
 int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
                        int M, int N, int K, int out_dtype, void* stream) {
   if (!c || !a || !w_shuf || !scale_a_image || !scale_w_image || M < 0 || N <= 0 || K <= 0) return FLYB200_E_BAD_ARG;
@@ -72,12 +89,9 @@ int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* s
     return FLYB200_E_BAD_ALIGN;
   if (M == 0) return FLYB200_OK;
   // up to 128 tokens: a weight stream, run by the small-M kernel in its block-scaled kind
-  {
-    const char* e = getenv("FLYB200_MX_SMALL");
-    if (M <= 128 && !(e && e[0] == '0'))
-      return host::gemm_mx_small(c, a, w_shuf, scale_a_image, scale_w_image, M, N, K,
-                                 out_dtype == FLYB200_OUT_FP16 ? 1 : 0, false, stream);
-  }
+  if (mx_small_m(M, N))
+    return host::gemm_mx_small(c, a, w_shuf, scale_a_image, scale_w_image, M, N, K, out_dtype == FLYB200_OUT_FP16 ? 1 : 0,
+                               false, stream);
   MxParams p;
   memset(&p, 0, sizeof(p));
   p.w = static_cast<const uint8_t*>(w_shuf);
@@ -157,12 +171,9 @@ int flyb200_gemm_mxfp4(void* c, const void* a, const void* w_shuf, const void* s
     return FLYB200_E_BAD_ALIGN;
   if (M == 0) return FLYB200_OK;
   // up to 128 tokens: a weight stream (half the bytes of 8-bit codes), run by the small-M kernel
-  {
-    const char* e = getenv("FLYB200_MX_SMALL");
-    if (M <= 128 && !(e && e[0] == '0'))
-      return host::gemm_mx_small(c, a, w_shuf, scale_a_image, scale_w_image, M, N, K / 2,
-                                 out_dtype == FLYB200_OUT_FP16 ? 1 : 0, true, stream);
-  }
+  if (mx_small_m(M, N))
+    return host::gemm_mx_small(c, a, w_shuf, scale_a_image, scale_w_image, M, N, K / 2,
+                               out_dtype == FLYB200_OUT_FP16 ? 1 : 0, true, stream);
   MxParams p;
   memset(&p, 0, sizeof(p));
   p.w = static_cast<const uint8_t*>(w_shuf);

@@ -16,6 +16,8 @@ int gemm_mx_small(void* c, const void* a, const void* w, const void* sf_a, const
                   int outmode, bool fp4, void* stream);
 // Pointer to the current device's status word (first failed bounded wait wins).
 int status_word(int** out);
+// SM count of the current device.
+int sm_count(int* out);
 // Remember a CUDA error for flyb200_last_cuda_error(); returns FLYB200_E_CUDA.
 int record_cuda_error(cudaError_t e, const char* what);
 

@@ -119,10 +119,13 @@ def test_both_tile_shapes(dev, monkeypatch, shape, m, n, k):
     check(run(dev, a_q, sa, b_q, sb), mx_oracle.mx4_gemm(a_q, sa, b_q, sb))
 
 
-@pytest.mark.parametrize("m,n,k", [(32, 1024, 2048), (128, 512, 1024), (5, 256, 256), (64, 8192, 8192), (100, 384, 4096)])
+@pytest.mark.parametrize("m,n,k", [(32, 1024, 2048), (128, 512, 1024), (5, 256, 256), (64, 8192, 8192), (100, 384, 4096), (24, 19200, 256)])
 def test_small_m_kernel_and_large_m_kernel_agree(dev, monkeypatch, m, n, k):
-    """Up to 128 tokens run the weight-streaming kernel (FLYB200_MX_SMALL=0 forces the other one)."""
+    """Up to 128 tokens run the weight-streaming kernel where its CTAs fit one round (the last shape, 150
+    channel tiles, goes to the large-M kernel by itself); FLYB200_MX_SMALL=1 / 0 forces one or the other."""
     a_q, sa, b_q, sb = mx_oracle.make_inputs_fp4(m, n, k, seed=3 * m + k)
+    check(run(dev, a_q, sa, b_q, sb), mx_oracle.mx4_gemm(a_q, sa, b_q, sb))  # the automatic choice
+    monkeypatch.setenv("FLYB200_MX_SMALL", "1")
     small = run(dev, a_q, sa, b_q, sb)
     monkeypatch.setenv("FLYB200_MX_SMALL", "0")
     large = run(dev, a_q, sa, b_q, sb)
