@@ -78,6 +78,18 @@ bool mx_small_m(int M, int N) {
   if (flyb200::host::sm_count(&sms) != FLYB200_OK) return true;
   return (N + 127) / 128 <= sms;
 }
+// Tile shape of the large-M kernel: 128 x 256 tiles (one accumulator, exposed epilogue) win once a
+// tile's mainloop is a few times longer than its epilogue (2.44-2.47 against 1.82-1.88 PFLOP/s at
+// K = 8192, M >= 4096) - unless the 128 x 128 tiles cover the output in one round of CTAs: then
+// they put twice as many SMs to work (MXFP8 256 x 8192 x 8192: 27.9 against 31.4 us; MXFP4:
+// 18.4 against 20.9 us).  `k_bytes`: bytes of codes per row.
+bool mx_wide_tiles(int M, int N, int k_bytes) {
+  if (N % 256 != 0 || k_bytes < 1024) return false;
+  int sms = 0;
+  if (flyb200::host::sm_count(&sms) != FLYB200_OK) return true;
+  const long long tiles128 = static_cast<long long>((M + 127) / 128) * (N / 128);
+  return tiles128 > sms;
+}
 }  // namespace
 
 int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* scale_a_image, const void* scale_w_image,
@@ -108,11 +120,8 @@ int flyb200_gemm_mxfp8(void* c, const void* a, const void* w_shuf, const void* s
   rc = host::byte_matrix_map(&tmA, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M), BLOCK_ROWS);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // 256-channel tiles (one accumulator, exposed epilogue) win as soon as a tile's
-  // mainloop is a few times longer than its epilogue: measured 2.44-2.47 against
-  // 1.82-1.88 PFLOP/s at K = 8192, M >= 4096, and level at M = 128.  FLYB200_MX_BN
-  // forces a shape (tuning and tests).
-  bool wide = N % 256 == 0 && K >= 2048;
+  // FLYB200_MX_BN forces a tile shape (tuning and tests)
+  bool wide = mx_wide_tiles(M, N, K);
   if (const char* e = getenv("FLYB200_MX_BN")) {
     if (e[0] == '1') wide = false;
     if (e[0] == '2' && N % 256 == 0) wide = true;
@@ -153,7 +162,7 @@ int flyb200_gemm_mx_mixed(void* c, const void* a, const void* w_shuf, const void
   rc = host::byte_matrix_map(&tmA, a, static_cast<uint64_t>(K), static_cast<uint64_t>(M), BLOCK_ROWS);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool wide = N % 256 == 0 && K >= 2048;
+  const bool wide = mx_wide_tiles(M, N, K);  // byte containers: K bytes per row
   if (wide) {
     if (out_dtype == FLYB200_OUT_BF16) return launch_mx<MOE_OUT_BF16, 256>(tmA, p, s);
     return launch_mx<MOE_OUT_FP16, 256>(tmA, p, s);
@@ -190,7 +199,7 @@ int flyb200_gemm_mxfp4(void* c, const void* a, const void* w_shuf, const void* s
   rc = host::byte_matrix_map(&tmA, a, static_cast<uint64_t>(K / 2), static_cast<uint64_t>(M), BLOCK_ROWS);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  bool wide = N % 256 == 0 && K >= 4096;  // as for 8-bit codes: wide tiles once a tile's mainloop dwarfs its epilogue
+  bool wide = mx_wide_tiles(M, N, K / 2);
   if (const char* e = getenv("FLYB200_MX_BN")) {
     if (e[0] == '1') wide = false;
     if (e[0] == '2' && N % 256 == 0) wide = true;
