@@ -17,7 +17,7 @@ from tests.helpers import as_i8, device_status
 pytestmark = pytest.mark.gpu
 RTOL = ATOL = 1e-2
 TORCH_DT = {"fp16": torch.float16, "bf16": torch.bfloat16}
-DEC, ROWS, ROWS2 = 1 << 8, 2 << 8, 3 << 8
+DEC, ROWS, ROWS2, PAIR, TALL = 1 << 8, 2 << 8, 3 << 8, 5 << 8, 6 << 8
 WS, CL = 1 << 12, 2 << 12
 
 
@@ -27,18 +27,21 @@ def _cases(count=80, seed=20241125):
     while len(out) < count:
         in_dtype = rnd.choice(["fp8", "int8", "fp16", "bf16"])
         eb = 1 if in_dtype in ("fp8", "int8") else 2
-        m = rnd.choice([1, 2, 15, 16, 17, 31, 33, 64, 65, 127, 128, 129, 200, 255, 256, 257, 300, 511, 640, 700])
+        m = rnd.choice([1, 2, 15, 16, 17, 31, 33, 64, 65, 127, 128, 129, 200, 255, 256, 257, 300, 511, 640, 700, 1000, 1024])
         n = 16 * rnd.randint(1, 190)
         k = (128 // eb) * rnd.randint(1, 32)
         out_dtype = rnd.choice(["bf16", "fp16"])
         epilogue = rnd.choice(["none", "none", "bias", "bias_relu", "bias_silu", "bias_gelu"])
         kb = k * eb // 128
-        if m <= 256 and rnd.random() < 0.6:  # small-M kernel with a forced split / reduction
-            split = rnd.choice([1, 2, 3, 4, 5, 8])
+        if 32 < m <= 256 and -(-n // 128) % 2 == 0 and rnd.random() < 0.25:  # small-M kernel as CTA pairs
+            split = min(rnd.choice([1, 2, 3, 4]), kb)
+            hint = PAIR | split | (0 if split == 1 else CL)
+        elif m <= 1024 and rnd.random() < (0.6 if m <= 256 else 0.3):  # small-M kernel (token blocks of 256 above 256
+            split = rnd.choice([1, 2, 3, 4, 5, 8])                      # tokens) with a forced split / reduction
             split = min(split, kb)
             hint = DEC | split | (0 if split == 1 else rnd.choice([CL, WS]))
-        elif rnd.random() < 0.7:  # large-M kernel, forced tile width (also for small M)
-            hint = ROWS | rnd.randint(1, 8)
+        elif rnd.random() < 0.7:  # large-M kernels, forced tile width (also for small M)
+            hint = rnd.choice([ROWS, ROWS, TALL]) | rnd.randint(1, 8)
         else:
             hint = rnd.choice([0, 0, ROWS2])
         out.append((in_dtype, m, n, k, out_dtype, epilogue, hint))
